@@ -1,0 +1,11 @@
+from flashqla_b200.api import (
+    chunk_gated_delta_rule,
+    chunk_gated_delta_rule_bwd,
+    chunk_gated_delta_rule_fwd,
+)
+
+__all__ = [
+    "chunk_gated_delta_rule_fwd",
+    "chunk_gated_delta_rule_bwd",
+    "chunk_gated_delta_rule",
+]

@@ -1,0 +1,151 @@
+"""Intra-GPU context parallelism along T ("gate-driven auto-CP").
+
+Long sequences are cut into chunk-aligned segments that run as independent streams.  Every
+segment's start state is obtained without running the sequence serially:
+
+1. per (segment, head) a scan of the chunk gate totals finds how many trailing chunks matter
+   before the accumulated log gate falls below ``THRESHOLD`` (earlier history is attenuated by
+   more than ``exp(THRESHOLD)``);
+2. a state-only pass over just those chunks, from a zero state, gives the segment's local end
+   state; where the threshold is never reached inside the segment, the whole segment is walked
+   and its exact transition matrix ``M`` is produced as well;
+3. a merge kernel chains the segments of each sequence:
+   ``start[i+1] = local[i] + fallback[i] * M[i] @ start[i]``.
+
+The backward pass mirrors this for the state gradient with ``M^T``.  This follows the scheme of
+the reference's ``flash_qla/ops/gated_delta_rule/chunk/cp_context.py:47-321``; the segment
+length policy is this package's own (sized for the 148 SMs of a B200, also applied to batched
+fixed-length input, which the reference never splits).
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+from . import ops
+from .ops import CHUNK_SIZE, SeqTables
+from .utils import tensor_cache
+
+THRESHOLD = -10.0
+MIN_SEGMENT_CHUNKS = 8
+TARGET_WAVES = 2.0
+VALUE_SLICES = 2  # CTAs per (segment, head) in the sequential kernels
+
+
+def sm_count(device) -> int:
+    return torch.cuda.get_device_properties(device).multi_processor_count
+
+
+@dataclass
+class SegmentPlan:
+    seg_tables: SeqTables          # the segments seen as a packed batch
+    seg_begin: torch.Tensor        # int32 [n_raw+1]: first segment of every raw sequence
+    first_seg_of_raw: torch.Tensor  # int64 [n_raw]
+    last_seg_of_raw: torch.Tensor   # int64 [n_raw]
+    n_seg: int
+
+
+def split_sequences(bounds: list[int], num_heads: int, n_sm: int,
+                    min_chunks: int = MIN_SEGMENT_CHUNKS, waves: float = TARGET_WAVES):
+    """Host-side segment planner.  ``bounds`` are the raw cumulative sequence lengths.
+
+    Returns ``None`` when splitting does not pay (the raw sequences already fill the GPU, or no
+    sequence is longer than one segment), else ``(seg_bounds, seg_begin)``: the cumulative
+    lengths of the segments and, per raw sequence, the index of its first segment.
+    """
+    lens = [e - s for s, e in zip(bounds[:-1], bounds[1:])]
+    chunks = [(n + CHUNK_SIZE - 1) // CHUNK_SIZE for n in lens]
+    total = sum(chunks)
+    if total == 0:
+        return None
+    want_ctas = waves * n_sm
+    ctas_per_seg = num_heads * VALUE_SLICES
+    if len(lens) * ctas_per_seg >= want_ctas:
+        return None
+    n_seg_target = math.ceil(want_ctas / ctas_per_seg)
+    seg_chunks = max(min_chunks, math.ceil(total / n_seg_target))
+    if max(chunks) <= seg_chunks:
+        return None
+    seg_bounds, seg_begin = [], []
+    for s, n, c in zip(bounds[:-1], lens, chunks):
+        seg_begin.append(len(seg_bounds))
+        parts = math.ceil(c / seg_chunks) if c > 0 else 1
+        per = math.ceil(c / parts) if c > 0 else 0  # balanced, still chunk aligned
+        for i in range(parts):
+            seg_bounds.append(s + i * per * CHUNK_SIZE)
+    seg_begin.append(len(seg_bounds))
+    seg_bounds.append(bounds[-1])
+    return seg_bounds, seg_begin
+
+
+@tensor_cache
+def _host_bounds(cu_seqlens: torch.Tensor) -> list[int]:
+    return [int(x) for x in cu_seqlens.tolist()]
+
+
+_fixed_plan_cache: dict = {}
+
+
+def _build_plan(bounds, Hv, device, idx_dtype, T_rows) -> SegmentPlan | None:
+    res = split_sequences(bounds, Hv, sm_count(device))
+    if res is None:
+        return None
+    seg_bounds, seg_begin = res
+    seg_cu = torch.tensor(seg_bounds, dtype=idx_dtype, device=device)
+    begin = torch.tensor(seg_begin, dtype=torch.int32, device=device)
+    tables = SeqTables(1, T_rows, seg_cu)
+    first = begin[:-1].long()
+    last = begin[1:].long() - 1
+    return SegmentPlan(tables, begin, first, last, len(seg_bounds) - 1)
+
+
+@tensor_cache
+def _plan_for_cu(cu_seqlens: torch.Tensor, Hv: int, T_rows: int):
+    return _build_plan(_host_bounds(cu_seqlens), Hv, cu_seqlens.device, cu_seqlens.dtype, T_rows)
+
+
+def plan_segments(tables: SeqTables, Hv: int, is_bwd: bool = False,
+                  device=None) -> SegmentPlan | None:
+    """Segment plan for a batch, or ``None`` when the batch runs unsplit.  Cached per
+    ``cu_seqlens`` tensor (identity) or per fixed shape, so steady-state calls do no host work."""
+    if tables.cu is not None:
+        return _plan_for_cu(tables.cu, Hv, tables.T)
+    device = device if device is not None else torch.cuda.current_device()
+    key = (tables.B, tables.T, Hv, str(device))
+    if key not in _fixed_plan_cache:
+        bounds = [b * tables.T for b in range(tables.B + 1)]
+        _fixed_plan_cache[key] = _build_plan(bounds, Hv, torch.device("cuda", device)
+                                             if isinstance(device, int) else device,
+                                             torch.int32, tables.B * tables.T)
+    return _fixed_plan_cache[key]
+
+
+def forward_segment_states(plan: SegmentPlan, k, v, A, g_cum, beta, scale, h0):
+    """Start state of every segment, fp32 ``[n_seg, Hv, D, D]``."""
+    seg = plan.seg_tables
+    warm, fallback = ops.warmup_scan(g_cum, seg.cu, THRESHOLD, from_start=False)
+    # the last segment of a sequence hands nothing on
+    warm[plan.last_seg_of_raw] = 0
+    fallback[plan.last_seg_of_raw] = 0
+    res = ops.fwd_seq(None, k, v, A, g_cum, beta, scale, None, output_o=False,
+                      output_final_state=True, output_m=True, warm_chunks=warm,
+                      m_mask=fallback, tables=seg)
+    return ops.merge_states(res["ht"], res["M"], fallback, h0, plan.seg_begin, reverse=False)
+
+
+def backward_segment_states(plan: SegmentPlan, q, k, v, A, g_cum, beta, do, scale, dht):
+    """Gradient of the state leaving every segment, fp32 ``[n_seg, Hv, D, D]``."""
+    seg = plan.seg_tables
+    warm, fallback = ops.warmup_scan(g_cum, seg.cu, THRESHOLD, from_start=True)
+    # the first segment of a sequence receives nothing from before it
+    warm[plan.first_seg_of_raw] = 0
+    fallback[plan.first_seg_of_raw] = 0
+    local = ops.bwd_dh(q, k, A, g_cum, beta, do, scale, None, output_dh=False, output_du=False,
+                       output_dh0=True, warm_chunks=warm, tables=seg)["dh0"]
+    # exact transition matrices where the gradient does not die out inside the segment
+    m = ops.fwd_seq(None, k, v, A, g_cum, beta, scale, None, output_o=False, output_m=True,
+                    m_mask=fallback, tables=seg)["M"]
+    return ops.merge_states(local, m, fallback, dht, plan.seg_begin, reverse=True)

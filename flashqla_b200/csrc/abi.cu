@@ -1,0 +1,17 @@
+// Version and status text of the C ABI.
+#include <cuda_runtime.h>
+
+#include "fqla_internal.h"
+
+extern "C" int fqla_version(void) { return 1; }
+
+extern "C" const char* fqla_status_string(int status) {
+  switch (status) {
+    case FQLA_OK: return "ok";
+    case FQLA_ERR_INVALID_ARG: return "invalid argument";
+    case FQLA_ERR_UNSUPPORTED_DIM: return "unsupported head dimension (64 or 128 only)";
+    default: break;
+  }
+  if (status > 0) return cudaGetErrorString((cudaError_t)status);
+  return "unknown status";
+}

@@ -1,0 +1,137 @@
+// Context-parallel helpers: when a sequence is cut into segments (inside one GPU, or across GPUs
+// along T), every segment first computes its end state from a zero start ("local" state) and,
+// where the gates do not let the past die out, the exact transition matrix M of the segment, so
+// that   state_end = local + M * state_start.   The kernels here
+//   * decide per (segment, head) how many trailing (forward) or leading (backward) chunks are
+//     needed before the accumulated log-gate drops below a threshold, and
+//   * chain the segments of each sequence:  start[i+1] = local[i] + M[i] start[i]  (forward) or
+//     end[i-1] = local[i] + M[i]^T end[i]  (backward, for the state gradient).
+// They replace the reference's blackwell/cp_fwd.py:10-221 (get_warmup_chunks, _bidi) and
+// :268-480 (correct_h0, also used transposed for dht).
+#include "common.cuh"
+#include "fqla_internal.h"
+
+namespace fqla {
+
+// One thread per (segment, head).  Walks the chunk totals (the cumsum value on each chunk's last
+// row) from the segment end backwards (forward pass) or from its start forwards (backward pass).
+__global__ void warmup_scan_kernel(const float* __restrict__ g_cum, int Hv, SeqLayout lay,
+                                   int n_seg, float threshold, int from_start,
+                                   int* __restrict__ warm, int* __restrict__ fallback) {
+  int seg = blockIdx.x, hv = threadIdx.x;
+  if (seg >= n_seg || hv >= Hv) return;
+  SeqSpan sp = lay.span(seg);
+  float acc = 0.f;
+  int n = 0;
+  bool reached = false;
+  for (int i = 0; i < sp.n_chunks; ++i) {
+    int c = from_start ? i : sp.n_chunks - 1 - i;
+    int last_row = min(sp.len, (c + 1) * CHUNK) - 1;
+    acc += g_cum[(sp.bos + last_row) * Hv + hv];
+    ++n;
+    if (acc < threshold) { reached = true; break; }
+  }
+  warm[seg * Hv + hv] = n;
+  fallback[seg * Hv + hv] = reached ? 0 : 1;
+}
+
+// Chain the segments of one raw sequence for one head and one 32-wide value slice.
+// grid = (D/32, Hv, n_raw), 128 threads for D = 128 (thread a owns row a of the slice).
+//   forward  (reverse = 0): out[first] = start_raw; out[i+1] = local[i] + useM[i] * M[i]   out[i]
+//   backward (reverse = 1): out[last]  = end_raw;   out[i-1] = local[i] + useM[i] * M[i]^T out[i]
+template <int D>
+__global__ void __launch_bounds__(D) merge_kernel(const float* __restrict__ local,
+                                                  const float* __restrict__ M,
+                                                  const int* __restrict__ use_m,
+                                                  const float* __restrict__ raw,
+                                                  const int* __restrict__ seg_begin,
+                                                  float* __restrict__ out, int Hv, int reverse) {
+  constexpr int BV = 32, BK = 32;
+  __shared__ float cur[D][BV];
+  // one staging buffer for a D x BK panel of M: forward [a][j] (row stride BK+1), reverse [j][a]
+  __shared__ float panel[D * (BK + 1)];
+  const int a = threadIdx.x, lane = a & 31, warp = a >> 5;
+  const int v0 = blockIdx.x * BV, hv = blockIdx.y, r = blockIdx.z;
+  const int s0 = seg_begin[r], s1 = seg_begin[r + 1];  // segments [s0, s1)
+  if (s1 <= s0) return;
+  auto state = [&](const float* base, int seg) {
+    return base + (((long long)seg * Hv + hv) * D) * D;
+  };
+  // initial value
+  {
+    const float* src = raw ? state(raw, r) : nullptr;
+    for (int j = 0; j < BV; ++j) cur[a][j] = src ? src[(long long)a * D + v0 + j] : 0.f;
+  }
+  __syncthreads();
+  const int n = s1 - s0;
+  for (int step = 0; step < n; ++step) {
+    const int i = reverse ? s1 - 1 - step : s0 + step;
+    float* dst = const_cast<float*>(state(out, i));
+    for (int j = 0; j < BV; ++j) dst[(long long)a * D + v0 + j] = cur[a][j];
+    if (step == n - 1) break;
+    float acc[BV];
+    const float* loc = state(local, i);
+#pragma unroll
+    for (int j = 0; j < BV; ++j) acc[j] = loc[(long long)a * D + v0 + j];
+    const bool with_m = use_m == nullptr || use_m[i * Hv + hv] != 0;
+    if (with_m) {
+      const float* m = state(M, i);
+      for (int b0 = 0; b0 < D; b0 += BK) {
+        if (!reverse) {
+          // panel[a'][j] = M[a'][b0+j], one warp per row, coalesced
+          for (int row = warp; row < D; row += D / 32)
+            panel[row * (BK + 1) + lane] = m[(long long)row * D + b0 + lane];
+        } else {
+          // panel[j][a'] = M[b0+j][a']
+          for (int j = 0; j < BK; ++j) panel[j * D + a] = m[(long long)(b0 + j) * D + a];
+        }
+        __syncthreads();
+#pragma unroll 4
+        for (int j = 0; j < BK; ++j) {
+          float w = reverse ? panel[j * D + a] : panel[a * (BK + 1) + j];
+#pragma unroll
+          for (int vv = 0; vv < BV; ++vv) acc[vv] += w * cur[b0 + j][vv];
+        }
+        __syncthreads();
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < BV; ++j) cur[a][j] = acc[j];
+    __syncthreads();
+  }
+}
+
+}  // namespace fqla
+
+using namespace fqla;
+
+extern "C" int fqla_warmup_scan(const float* g_cum, int T, int Hv, const void* seg_cu_seqlens,
+                                int idx_is64, int n_seg, float threshold, int from_start,
+                                int* warm, int* fallback, void* stream) {
+  if (!g_cum || !seg_cu_seqlens || !warm || !fallback || Hv <= 0 || Hv > 1024)
+    return FQLA_ERR_INVALID_ARG;
+  if (n_seg <= 0) return FQLA_OK;
+  SeqLayout lay{{seg_cu_seqlens, idx_is64}, {seg_cu_seqlens, idx_is64}, T};
+  warmup_scan_kernel<<<n_seg, ((Hv + 31) / 32) * 32, 0, (cudaStream_t)stream>>>(
+      g_cum, Hv, lay, n_seg, threshold, from_start, warm, fallback);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int fqla_merge_states(const float* local, const float* M, const int* use_m,
+                                 const float* raw, const int* seg_begin, float* out, int n_raw,
+                                 int Hv, int D, int reverse, void* stream) {
+  if (!local || !M || !seg_begin || !out || Hv <= 0) return FQLA_ERR_INVALID_ARG;
+  if (n_raw <= 0) return FQLA_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (D == 128) {
+    merge_kernel<128><<<dim3(128 / 32, Hv, n_raw), 128, 0, st>>>(local, M, use_m, raw, seg_begin,
+                                                                  out, Hv, reverse);
+  } else if (D == 64) {
+    merge_kernel<64><<<dim3(64 / 32, Hv, n_raw), 64, 0, st>>>(local, M, use_m, raw, seg_begin,
+                                                                out, Hv, reverse);
+  } else {
+    return FQLA_ERR_UNSUPPORTED_DIM;
+  }
+  return (int)cudaGetLastError();
+}

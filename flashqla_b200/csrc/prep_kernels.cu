@@ -1,0 +1,232 @@
+// Chunk-parallel preparation kernels of the gated-delta-rule path:
+//   * chunk-local cumulative sum of the log gates (forward, and reversed for the gate gradient)
+//   * A = (I + strict_lower(diag(beta) K K^T * exp(g_s - g_t)))^-1 per (chunk, value head)
+//   * sum of per-value-head dq/dk over each grouped-value-attention group
+// These replace the reference's ops/utils/cumsum.py:14-134, blackwell/kkt_solve.py:19-281 and
+// ops/utils/group_reduce.py:12-57.
+#include "common.cuh"
+#include "fqla_internal.h"
+
+namespace fqla {
+
+// ------------------------------------------------------------------------------------------
+// Chunk-local cumsum.  One CTA per chunk, one warp per head (looping), two rows per lane.
+// HBM-bound: 8 bytes per (token, head).
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128) cumsum_kernel(const float* __restrict__ g,
+                                                     float* __restrict__ out, int H, int T_rows,
+                                                     SeqLayout lay, IndexTable chunk_indices,
+                                                     int N, int reverse) {
+  int seq, ci;
+  if (lay.cu.ptr) {
+    seq = (int)chunk_indices[2 * blockIdx.x];
+    ci = (int)chunk_indices[2 * blockIdx.x + 1];
+  } else {
+    int per = (lay.T + CHUNK - 1) / CHUNK;
+    seq = blockIdx.x / per;
+    ci = blockIdx.x % per;
+  }
+  SeqSpan sp = lay.span(seq);
+  long long row0 = sp.bos + (long long)ci * CHUNK;
+  int valid = min(CHUNK, sp.len - ci * CHUNK);
+  int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int h = warp; h < H; h += 4) {
+    // lane owns rows 2*lane, 2*lane+1 (forward) or their mirror images (reverse)
+    int r0 = 2 * lane, r1 = 2 * lane + 1;
+    if (reverse) { r0 = valid - 1 - r0; r1 = valid - 1 - r1; }
+    bool ok0 = reverse ? r0 >= 0 : r0 < valid;
+    bool ok1 = reverse ? r1 >= 0 : r1 < valid;
+    float a = ok0 ? g[(row0 + r0) * H + h] : 0.f;
+    float b = ok1 ? g[(row0 + r1) * H + h] : 0.f;
+    float pair = a + b, incl = pair;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      float t = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= d) incl += t;
+    }
+    float excl = incl - pair;
+    if (ok0) out[(row0 + r0) * H + h] = excl + a;
+    if (ok1) out[(row0 + r1) * H + h] = excl + a + b;
+  }
+  // Rows past the last sequence's end (packed input shorter than the buffer) come out zero.
+  if (lay.cu.ptr && seq == N - 1 && ci == sp.n_chunks - 1) {
+    long long end = sp.bos + sp.len;
+    for (long long i = end * H + threadIdx.x; i < (long long)T_rows * H; i += blockDim.x)
+      out[i] = 0.f;
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// kkt + solve.  One CTA (128 threads) per (chunk, value head).
+//   1. K K^T (64x64xD) on tensor cores, 2. L = strict_lower(beta_s * KK^T * exp(g_s-g_t)) in fp32,
+//   3. X = (I+L)^-1 by forward substitution, thread c owning column c, 4. bf16 rows out.
+// ------------------------------------------------------------------------------------------
+template <int D>
+__global__ void __launch_bounds__(128) kkt_solve_kernel(
+    const bf16* __restrict__ k, const void* __restrict__ beta, int beta_is_f32,
+    const float* __restrict__ g, bf16* __restrict__ A, int Hq, int Hv, SeqLayout lay,
+    IndexTable chunk_indices) {
+  constexpr int LDK = D + 8;
+  constexpr int LDL = CHUNK + 4;  // floats; rows stay 16-byte aligned
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* sK = reinterpret_cast<bf16*>(smem_raw);
+  float* sL = reinterpret_cast<float*>(smem_raw + CHUNK * LDK * sizeof(bf16));
+  float* sG = sL + CHUNK * LDL;
+  float* sB = sG + CHUNK;
+
+  int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  int hv = blockIdx.y, hq = hv / (Hv / Hq);
+  int seq, ci;
+  if (lay.cu.ptr) {
+    seq = (int)chunk_indices[2 * blockIdx.x];
+    ci = (int)chunk_indices[2 * blockIdx.x + 1];
+  } else {
+    int per = (lay.T + CHUNK - 1) / CHUNK;
+    seq = blockIdx.x / per;
+    ci = blockIdx.x % per;
+  }
+  SeqSpan sp = lay.span(seq);
+  long long row0 = sp.bos + (long long)ci * CHUNK;
+  int valid = min(CHUNK, sp.len - ci * CHUNK);
+
+  load_tile_async<D, LDK, 128>(sK, k + (row0 * Hq + hq) * D, (long long)Hq * D, valid, tid);
+  cp_async_commit();
+  if (tid < CHUNK) {
+    int r = min(tid, valid - 1);
+    sG[tid] = g[(row0 + r) * Hv + hv];
+    sB[tid] = tid < valid ? load_beta(beta, beta_is_f32, (row0 + tid) * Hv + hv) : 0.f;
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+
+  // warp w: rows 16w..16w+15, all 64 columns
+  float acc[1][8][4];
+  zero_acc(acc);
+  warp_gemm<1, 8, D / 16, false, false>(acc, sK + warp * 16 * LDK, LDK, sK, LDK, lane);
+#pragma unroll
+  for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      int r = warp * 16 + (lane >> 2) + (e >> 1) * 8;
+      int c = nt * 8 + (lane & 3) * 2 + (e & 1);
+      float v = 0.f;
+      if (r > c) v = sB[r] * acc[0][nt][e] * fast_exp(sG[r] - sG[c]);
+      sL[r * LDL + c] = v;
+    }
+  __syncthreads();
+
+  // Forward substitution: x_i = e_i - sum_{j<i} L[i][j] x_j, column c in thread c's registers.
+  if (tid < CHUNK) {
+    float x[CHUNK];
+#pragma unroll
+    for (int i = 0; i < CHUNK; ++i) {
+      float s = (i == tid) ? 1.f : 0.f;
+#pragma unroll
+      for (int j4 = 0; j4 < (i + 3) / 4; ++j4) {
+        float4 l = *reinterpret_cast<const float4*>(&sL[i * LDL + j4 * 4]);
+        if (j4 * 4 + 0 < i) s -= l.x * x[j4 * 4 + 0];
+        if (j4 * 4 + 1 < i) s -= l.y * x[j4 * 4 + 1];
+        if (j4 * 4 + 2 < i) s -= l.z * x[j4 * 4 + 2];
+        if (j4 * 4 + 3 < i) s -= l.w * x[j4 * 4 + 3];
+      }
+      x[i] = s;
+    }
+    __syncwarp();
+    // stage as bf16 rows in the (now dead) K tile: sK[i][c]
+#pragma unroll
+    for (int i = 0; i < CHUNK; ++i) sK[i * LDK + tid] = __float2bfloat16(x[i]);
+  }
+  __syncthreads();
+  // coalesced row stores: 64 rows x 128 bytes
+  for (int i = tid; i < CHUNK * 8; i += 128) {
+    int r = i >> 3, c = (i & 7) * 8;
+    if (r < valid)
+      *reinterpret_cast<uint4*>(A + ((row0 + r) * Hv + hv) * CHUNK + c) =
+          *reinterpret_cast<const uint4*>(sK + r * LDK + c);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Grouped-value-attention reduce: out[row, hq, :] = sum_{i<G} in[row, hq*G+i, :], fp32 adds.
+// HBM-bound: reads 2*D*G bytes and writes 2*D bytes per (token, q head).
+// ------------------------------------------------------------------------------------------
+__global__ void group_reduce_kernel(const bf16* __restrict__ in, bf16* __restrict__ out,
+                                    long long n_vec, int G, int D8) {
+  // one thread per 8-element (16-byte) segment of an output row
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_vec) return;
+  long long row_hq = i / D8;
+  int seg = (int)(i % D8);
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  for (int j = 0; j < G; ++j) {
+    uint4 raw = *reinterpret_cast<const uint4*>(in + ((row_hq * G + j) * D8 + seg) * 8);
+    const bf162* p = reinterpret_cast<const bf162*>(&raw);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float2 f = __bfloat1622float2(p[e]);
+      acc[2 * e] += f.x;
+      acc[2 * e + 1] += f.y;
+    }
+  }
+  uint4 res;
+  uint32_t* pr = reinterpret_cast<uint32_t*>(&res);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) pr[e] = pack_bf16(acc[2 * e], acc[2 * e + 1]);
+  *reinterpret_cast<uint4*>(out + i * 8) = res;
+}
+
+}  // namespace fqla
+
+using namespace fqla;
+
+extern "C" int fqla_chunk_local_cumsum(const float* g, float* out, int B, int T, int H,
+                                       const void* cu_seqlens, int idx_is64, int N,
+                                       const void* chunk_indices, long long num_chunks,
+                                       int reverse, void* stream) {
+  if (!g || !out || B <= 0 || T < 0 || H <= 0) return FQLA_ERR_INVALID_ARG;
+  if (cu_seqlens && (!chunk_indices || B != 1)) return FQLA_ERR_INVALID_ARG;
+  SeqLayout lay{{cu_seqlens, idx_is64}, {nullptr, idx_is64}, T};
+  long long n = cu_seqlens ? num_chunks : (long long)B * ((T + CHUNK - 1) / CHUNK);
+  if (n <= 0) return FQLA_OK;
+  cumsum_kernel<<<(unsigned)n, 128, 0, (cudaStream_t)stream>>>(
+      g, out, H, B * T, lay, IndexTable{chunk_indices, idx_is64}, cu_seqlens ? N : B, reverse);
+  return (int)cudaGetLastError();
+}
+
+template <int D>
+static int launch_kkt(const void* k, const void* beta, int beta_is_f32, const float* g, void* A,
+                      int Hq, int Hv, SeqLayout lay, IndexTable ci, long long n,
+                      cudaStream_t st) {
+  constexpr int smem = CHUNK * (D + 8) * 2 + CHUNK * (CHUNK + 4) * 4 + 2 * CHUNK * 4;
+  int rc = configure_smem((const void*)kkt_solve_kernel<D>, smem);
+  if (rc != 0) return rc;
+  kkt_solve_kernel<D><<<dim3((unsigned)n, Hv), 128, smem, st>>>(
+      (const bf16*)k, beta, beta_is_f32, g, (bf16*)A, Hq, Hv, lay, ci);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int fqla_kkt_solve(const void* k, const void* beta, int beta_is_f32,
+                              const float* g_cum, void* A, int B, int T, int Hq, int Hv, int D,
+                              const void* cu_seqlens, int idx_is64, const void* chunk_indices,
+                              long long num_chunks, void* stream) {
+  if (!k || !beta || !g_cum || !A || Hq <= 0 || Hv % Hq) return FQLA_ERR_INVALID_ARG;
+  if (cu_seqlens && (!chunk_indices || B != 1)) return FQLA_ERR_INVALID_ARG;
+  SeqLayout lay{{cu_seqlens, idx_is64}, {nullptr, idx_is64}, T};
+  IndexTable ci{chunk_indices, idx_is64};
+  long long n = cu_seqlens ? num_chunks : (long long)B * ((T + CHUNK - 1) / CHUNK);
+  if (n <= 0) return FQLA_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (D == 128) return launch_kkt<128>(k, beta, beta_is_f32, g_cum, A, Hq, Hv, lay, ci, n, st);
+  if (D == 64) return launch_kkt<64>(k, beta, beta_is_f32, g_cum, A, Hq, Hv, lay, ci, n, st);
+  return FQLA_ERR_UNSUPPORTED_DIM;
+}
+
+extern "C" int fqla_group_reduce(const void* in, void* out, long long rows, int Hq, int G, int D,
+                                 void* stream) {
+  if (!in || !out || G <= 0 || D % 8) return FQLA_ERR_INVALID_ARG;
+  long long n_vec = rows * Hq * (D / 8);
+  if (n_vec <= 0) return FQLA_OK;
+  group_reduce_kernel<<<(unsigned)((n_vec + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      (const bf16*)in, (bf16*)out, n_vec, G, D / 8);
+  return (int)cudaGetLastError();
+}

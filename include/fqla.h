@@ -1,0 +1,118 @@
+/*
+ * libfqla_sm100 - C ABI of the B200 (sm_100a) gated-delta-rule chunked-prefill kernels.
+ *
+ * This is the boundary a host framework binds to.  The reference project (QwenLM/FlashQLA)
+ * has no native boundary: its kernels are TileLang functions called from Python.  Each entry
+ * point below replaces one of those Python-level kernel wrappers; the wrapper it replaces is
+ * cited by its path inside the reference project.
+ *
+ * Conventions
+ *   - All pointers are device pointers unless said otherwise; the caller owns every buffer,
+ *     the library never allocates.  Work is enqueued on `stream` (a cudaStream_t passed as
+ *     void*) of the current device and the call returns at once.
+ *   - Return value: 0 on success, a negative FQLA_ERR_* for arguments rejected on the host
+ *     before any launch, or a positive cudaError_t reported by the launch.
+ *   - Token axis: q, k are [B, T, Hq, D]; v, o, do, dv, vnew, du are [B, T, Hv, D]; g, beta,
+ *     dg, db are [B, T, Hv]; A is [B, T, Hv, 64].  All bf16 except g/dg/db (fp32) and beta
+ *     (bf16, or fp32 when beta_is_f32 != 0).  Hv must be a multiple of Hq; D is 64 or 128.
+ *   - Packed variable-length input: B == 1, `cu_seqlens` [N+1] gives the sequence boundaries,
+ *     `chunk_offsets` [N+1] the exclusive prefix sum of ceil(len/64), `chunk_indices`
+ *     [num_chunks, 2] the (sequence, chunk-in-sequence) of every chunk.  The three tables share
+ *     one integer type: int64 when idx_is64 != 0, else int32.  With cu_seqlens == NULL the
+ *     input is B sequences of T rows and the tables are ignored.
+ *   - States ([N, Hv, D, D], fp32) are indexed [key dim][value dim].  Per-chunk states h/dh are
+ *     [total chunks, Hv, D, D] bf16.
+ *   - g_cum is always the chunk-local cumulative sum of the log gates.
+ */
+#ifndef FQLA_H_
+#define FQLA_H_
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FQLA_OK 0
+#define FQLA_ERR_INVALID_ARG (-1)
+#define FQLA_ERR_UNSUPPORTED_DIM (-2)
+
+/* ABI version, bumped on any signature change. */
+int fqla_version(void);
+/* Human-readable text for a return value of this library (static storage). */
+const char* fqla_status_string(int status);
+
+/* Chunk-local prefix sum (reverse != 0: suffix sum) of g [B,T,H] fp32.
+ * Replaces chunk_local_cumsum, flash_qla/ops/utils/cumsum.py:137-171. */
+int fqla_chunk_local_cumsum(const float* g, float* out, int B, int T, int H,
+                            const void* cu_seqlens, int idx_is64, int N,
+                            const void* chunk_indices, long long num_chunks, int reverse,
+                            void* stream);
+
+/* A = (I + strict_lower(diag(beta) K K^T * exp(g_s - g_t)))^-1 per (chunk, value head); row t of
+ * A holds row (t mod 64) of its chunk's matrix.
+ * Replaces kkt_solve, flash_qla/ops/gated_delta_rule/chunk/blackwell/kkt_solve.py:284-324
+ * (this library folds the gate into A, as the reference's tests/ref_gdr.py:77-140 does). */
+int fqla_kkt_solve(const void* k, const void* beta, int beta_is_f32, const float* g_cum, void* A,
+                   int B, int T, int Hq, int Hv, int D, const void* cu_seqlens, int idx_is64,
+                   const void* chunk_indices, long long num_chunks, void* stream);
+
+/* Sequential forward recurrence.  Optional outputs (NULL to skip): o, per-chunk states h,
+ * vnew (the delta-rule corrected values, needed by the backward), final state ht, and the
+ * transition matrix M (state_end = state_end|zero start + M state_start).  q may be NULL when
+ * o is.  warm_chunks [N,Hv] (int32, optional, state-only calls): walk only the last
+ * warm_chunks[n,hv] chunks of each sequence from a zero state.  m_mask [N,Hv] (int32,
+ * optional): compute M only where non-zero.
+ * Replaces fused_gdr_fwd (blackwell/fused_fwd.py:775-915) and fused_gdr_h
+ * (blackwell/prepare_h.py:669-784). */
+int fqla_fwd_seq(const void* q, const void* k, const void* v, const void* A, const float* g_cum,
+                 const void* beta, int beta_is_f32, const float* h0, float* ht, void* o, void* h,
+                 void* vnew, float* M, const int* warm_chunks, const int* m_mask, int B, int T,
+                 int Hq, int Hv, int D, float scale, const void* cu_seqlens,
+                 const void* chunk_offsets, int idx_is64, int N, void* stream);
+
+/* Sequential reverse recurrence of the state gradient.  Optional outputs: per-chunk dh, du (the
+ * gradient of vnew), dh0.  warm_chunks (optional, dh0-only calls): walk only the first
+ * warm_chunks[n,hv] chunks from a zero gradient.
+ * Replaces fused_gdr_dh_ws (blackwell/cp_bwd.py:592-701) and the dS chain of fused_gdr_bwd
+ * (blackwell/fused_bwd.py:336-474). */
+int fqla_bwd_dh(const void* q, const void* k, const void* A, const float* g_cum, const void* beta,
+                int beta_is_f32, const void* dO, const float* dht, void* dh, void* du, float* dh0,
+                const int* warm_chunks, int B, int T, int Hq, int Hv, int D, float scale,
+                const void* cu_seqlens, const void* chunk_offsets, int idx_is64, int N,
+                void* stream);
+
+/* Chunk-parallel backward: dq, dk (per VALUE head, [B,T,Hv,D] bf16), dv, dbeta and the
+ * pre-cumsum dg (both fp32 [B,T,Hv]) from h, dh, vnew and du.
+ * Replaces the per-chunk body of fused_gdr_bwd (blackwell/fused_bwd.py:1325-1413). */
+int fqla_bwd_main(const void* q, const void* k, const void* v, const void* vnew, const void* A,
+                  const float* g_cum, const void* beta, int beta_is_f32, const void* dO,
+                  const void* du, const void* h, const void* dh, void* dq, void* dk, void* dv,
+                  float* db, float* dg, int B, int T, int Hq, int Hv, int D, float scale,
+                  const void* cu_seqlens, const void* chunk_offsets, const void* chunk_indices,
+                  int idx_is64, long long num_chunks, void* stream);
+
+/* out[row, hq, :] = sum over the G value heads of group hq of in[row, hq*G + i, :] (bf16, fp32
+ * accumulation).  Replaces group_reduce_vector, flash_qla/ops/utils/group_reduce.py:60-79. */
+int fqla_group_reduce(const void* in, void* out, long long rows, int Hq, int G, int D,
+                      void* stream);
+
+/* Per (segment, head): number of chunks, counted from the segment end (from_start == 0) or start
+ * (from_start != 0), after which the accumulated log gate is below `threshold`; fallback = 1
+ * where the whole segment does not get there.  seg_cu_seqlens [n_seg+1].
+ * Replaces get_warmup_chunks / get_warmup_chunks_bidi, blackwell/cp_fwd.py:81-115, :224-264. */
+int fqla_warmup_scan(const float* g_cum, int T, int Hv, const void* seg_cu_seqlens, int idx_is64,
+                     int n_seg, float threshold, int from_start, int* warm, int* fallback,
+                     void* stream);
+
+/* Chain segment states of each raw sequence (segments seg_begin[r] .. seg_begin[r+1]-1):
+ * reverse == 0: out[first] = raw[r] (or 0); out[i+1] = local[i] + use_m[i,hv] * M[i]   out[i]
+ * reverse != 0: out[last]  = raw[r] (or 0); out[i-1] = local[i] + use_m[i,hv] * M[i]^T out[i]
+ * All states fp32 [*, Hv, D, D]; use_m int32 [n_seg, Hv] or NULL (always apply M).
+ * Replaces correct_initial_states / correct_terminal_states, blackwell/cp_fwd.py:483-610. */
+int fqla_merge_states(const float* local, const float* M, const int* use_m, const float* raw,
+                      const int* seg_begin, float* out, int n_raw, int Hv, int D, int reverse,
+                      void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FQLA_H_ */
