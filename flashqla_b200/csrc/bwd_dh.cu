@@ -64,7 +64,8 @@ template <int D, int BV>
 __global__ void __launch_bounds__(256, 1) bwd_dh_kernel(const BwdDhParams p) {
   using L = BwdDhSmem<D, BV>;
   constexpr int LDK = L::LDK, LDV = L::LDV, LDA = L::LDA;
-  constexpr int NTV = BV / 16;
+  constexpr int NTV = BV / 16;  // n-tiles (of 8) per warp for 64 x BV outputs: BV/2 columns
+  constexpr int MTS = D / 64;   // m-tiles (of 16) per warp for the D x BV state: D/4 rows
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* sm = reinterpret_cast<bf16*>(smem_raw);
   float* sG = reinterpret_cast<float*>(smem_raw + L::BF16_ELEMS * 2);
@@ -87,27 +88,27 @@ __global__ void __launch_bounds__(256, 1) bwd_dh_kernel(const BwdDhParams p) {
   int c_end = sp.n_chunks;  // exclusive
   if (p.warm) c_end = min(sp.n_chunks, p.warm[n * p.Hv + hv]);
 
-  float dS[2][NTV][4];
+  float dS[MTS][NTV][4];
   const long long state_off = ((long long)n * p.Hv + hv) * D * D;
 #pragma unroll
-  for (int mt = 0; mt < 2; ++mt)
+  for (int mt = 0; mt < MTS; ++mt)
 #pragma unroll
     for (int nt = 0; nt < NTV; ++nt)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        int r = 32 * wm + mt * 16 + (lane >> 2) + (e >> 1) * 8;
+        int r = (16 * MTS) * wm + mt * 16 + (lane >> 2) + (e >> 1) * 8;
         int c = v0 + (BV / 2) * wn + nt * 8 + (lane & 3) * 2 + (e & 1);
         dS[mt][nt][e] =
             (p.dht && c_end == sp.n_chunks) ? p.dht[state_off + (long long)r * D + c] : 0.f;
       }
   auto store_state_copy = [&]() {
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt)
+    for (int mt = 0; mt < MTS; ++mt)
 #pragma unroll
       for (int nt = 0; nt < NTV; ++nt)
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
-          int r = 32 * wm + mt * 16 + (lane >> 2) + hh * 8;
+          int r = (16 * MTS) * wm + mt * 16 + (lane >> 2) + hh * 8;
           int c = (BV / 2) * wn + nt * 8 + (lane & 3) * 2;
           st_bf16x2(sDS + r * LDV + c, dS[mt][nt][2 * hh], dS[mt][nt][2 * hh + 1]);
         }
@@ -250,14 +251,14 @@ __global__ void __launch_bounds__(256, 1) bwd_dh_kernel(const BwdDhParams p) {
     {
       const float gl = sGam[CHUNK - 1];
 #pragma unroll
-      for (int mt = 0; mt < 2; ++mt)
+      for (int mt = 0; mt < MTS; ++mt)
 #pragma unroll
         for (int nt = 0; nt < NTV; ++nt)
 #pragma unroll
           for (int e = 0; e < 4; ++e) dS[mt][nt][e] *= gl;
-      warp_gemm<2, NTV, CHUNK / 16, true, true>(dS, sQ + 32 * wm, LDK, sDOg + (BV / 2) * wn, LDV,
+      warp_gemm<MTS, NTV, CHUNK / 16, true, true>(dS, sQ + (16 * MTS) * wm, LDK, sDOg + (BV / 2) * wn, LDV,
                                                 lane);
-      warp_gemm<2, NTV, CHUNK / 16, true, true>(dS, sW + 32 * wm, LDK, sNdv + (BV / 2) * wn, LDV,
+      warp_gemm<MTS, NTV, CHUNK / 16, true, true>(dS, sW + (16 * MTS) * wm, LDK, sNdv + (BV / 2) * wn, LDV,
                                                 lane);
     }
     store_state_copy();  // last read in phase A, two barriers ago
@@ -265,12 +266,12 @@ __global__ void __launch_bounds__(256, 1) bwd_dh_kernel(const BwdDhParams p) {
 
   if (p.dh0) {
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt)
+    for (int mt = 0; mt < MTS; ++mt)
 #pragma unroll
       for (int nt = 0; nt < NTV; ++nt)
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
-          int r = 32 * wm + mt * 16 + (lane >> 2) + hh * 8;
+          int r = (16 * MTS) * wm + mt * 16 + (lane >> 2) + hh * 8;
           int c = v0 + (BV / 2) * wn + nt * 8 + (lane & 3) * 2;
           *reinterpret_cast<float2*>(p.dh0 + state_off + (long long)r * D + c) =
               make_float2(dS[mt][nt][2 * hh], dS[mt][nt][2 * hh + 1]);

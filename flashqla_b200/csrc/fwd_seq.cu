@@ -72,6 +72,7 @@ __global__ void __launch_bounds__(256, 1) fwd_seq_kernel(const FwdSeqParams p) {
   using L = FwdSeqSmem<D, BV>;
   constexpr int LDK = L::LDK, LDV = L::LDV, LDA = L::LDA;
   constexpr int NTV = BV / 16;  // n-tiles (of 8) per warp for 64 x BV outputs: BV/2 columns
+  constexpr int MTS = D / 64;   // m-tiles (of 16) per warp for the D x BV state: D/4 rows
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* sm = reinterpret_cast<bf16*>(smem_raw);
   float* sG = reinterpret_cast<float*>(smem_raw + L::BF16_ELEMS * 2);
@@ -100,15 +101,15 @@ __global__ void __launch_bounds__(256, 1) fwd_seq_kernel(const FwdSeqParams p) {
   if (p.warm) c_begin = max(0, sp.n_chunks - p.warm[n * p.Hv + hv]);
 
   // ---- state in registers: rows 32*wm + mt*16 + ..., cols (BV/2)*wn + nt*8 + ...
-  float S[2][NTV][4];
+  float S[MTS][NTV][4];
   const long long state_off = ((long long)n * p.Hv + hv) * D * D;
 #pragma unroll
-  for (int mt = 0; mt < 2; ++mt)
+  for (int mt = 0; mt < MTS; ++mt)
 #pragma unroll
     for (int nt = 0; nt < NTV; ++nt)
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        int r = 32 * wm + mt * 16 + (lane >> 2) + (e >> 1) * 8;
+        int r = (16 * MTS) * wm + mt * 16 + (lane >> 2) + (e >> 1) * 8;
         int c = v0 + (BV / 2) * wn + nt * 8 + (lane & 3) * 2 + (e & 1);
         float x = 0.f;
         if (m_slice) x = (r == c) ? 1.f : 0.f;
@@ -117,12 +118,12 @@ __global__ void __launch_bounds__(256, 1) fwd_seq_kernel(const FwdSeqParams p) {
       }
   auto store_state_copy = [&]() {
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt)
+    for (int mt = 0; mt < MTS; ++mt)
 #pragma unroll
       for (int nt = 0; nt < NTV; ++nt)
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
-          int r = 32 * wm + mt * 16 + (lane >> 2) + hh * 8;
+          int r = (16 * MTS) * wm + mt * 16 + (lane >> 2) + hh * 8;
           int c = (BV / 2) * wn + nt * 8 + (lane & 3) * 2;
           st_bf16x2(sS + r * LDV + c, S[mt][nt][2 * hh], S[mt][nt][2 * hh + 1]);
         }
@@ -278,12 +279,12 @@ __global__ void __launch_bounds__(256, 1) fwd_seq_kernel(const FwdSeqParams p) {
     {
       const float gl = sGam[CHUNK - 1];
 #pragma unroll
-      for (int mt = 0; mt < 2; ++mt)
+      for (int mt = 0; mt < MTS; ++mt)
 #pragma unroll
         for (int nt = 0; nt < NTV; ++nt)
 #pragma unroll
           for (int e = 0; e < 4; ++e) S[mt][nt][e] *= gl;
-      warp_gemm<2, NTV, CHUNK / 16, true, true>(S, sK + 32 * wm, LDK, sVr + (BV / 2) * wn, LDV,
+      warp_gemm<MTS, NTV, CHUNK / 16, true, true>(S, sK + (16 * MTS) * wm, LDK, sVr + (BV / 2) * wn, LDV,
                                                 lane);
     }
     // The old state copy was last read in phase A, two barriers ago: safe to overwrite.
@@ -294,12 +295,12 @@ __global__ void __launch_bounds__(256, 1) fwd_seq_kernel(const FwdSeqParams p) {
   float* dst = m_slice ? p.M : p.ht;
   if (dst) {
 #pragma unroll
-    for (int mt = 0; mt < 2; ++mt)
+    for (int mt = 0; mt < MTS; ++mt)
 #pragma unroll
       for (int nt = 0; nt < NTV; ++nt)
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
-          int r = 32 * wm + mt * 16 + (lane >> 2) + hh * 8;
+          int r = (16 * MTS) * wm + mt * 16 + (lane >> 2) + hh * 8;
           int c = v0 + (BV / 2) * wn + nt * 8 + (lane & 3) * 2;
           *reinterpret_cast<float2*>(dst + state_off + (long long)r * D + c) =
               make_float2(S[mt][nt][2 * hh], S[mt][nt][2 * hh + 1]);

@@ -140,7 +140,7 @@ def fwd_seq(q, k, v, a, g_cum, b, scale, initial_state=None, *, output_final_sta
         _ptr(q) if output_o else None, _ptr(k), _ptr(v), _ptr(a), _ptr(g_cum), _ptr(b),
         _beta_flag(b), _ptr(initial_state), _ptr(out.get("ht")), _ptr(out.get("o")),
         _ptr(out.get("h")), _ptr(out.get("vnew")), _ptr(out.get("M")), _ptr(warm_chunks),
-        _ptr(m_mask), B, T, Hq, Hv, D, float(scale), cu, offs, is64, N, _stream(k))
+        _ptr(m_mask), tb.B, tb.T, Hq, Hv, D, float(scale), cu, offs, is64, N, _stream(k))
     _lib.check(st, "fwd_seq")
     return out
 
@@ -169,7 +169,7 @@ def bwd_dh(q, k, a, g_cum, b, do, scale, dht=None, *, output_dh=True, output_du=
     st = _lib.load().fqla_bwd_dh(
         _ptr(q), _ptr(k), _ptr(a), _ptr(g_cum), _ptr(b), _beta_flag(b), _ptr(do), _ptr(dht),
         _ptr(out.get("dh")), _ptr(out.get("du")), _ptr(out.get("dh0")), _ptr(warm_chunks),
-        B, T, Hq, Hv, D, float(scale), cu, offs, is64, N, _stream(k))
+        tb.B, tb.T, Hq, Hv, D, float(scale), cu, offs, is64, N, _stream(k))
     _lib.check(st, "bwd_dh")
     return out
 
@@ -195,7 +195,7 @@ def bwd_main(q, k, v, vnew, a, g_cum, b, do, du, h, dh, scale, cu_seqlens=None,
     st = _lib.load().fqla_bwd_main(
         _ptr(q), _ptr(k), _ptr(v), _ptr(vnew), _ptr(a), _ptr(g_cum), _ptr(b), _beta_flag(b),
         _ptr(do), _ptr(du), _ptr(h), _ptr(dh), _ptr(dq), _ptr(dk), _ptr(dv), _ptr(db), _ptr(dg),
-        B, T, Hq, Hv, D, float(scale), cu, offs, _ptr(tb.chunk_indices), is64, tb.num_chunks,
+        tb.B, tb.T, Hq, Hv, D, float(scale), cu, offs, _ptr(tb.chunk_indices), is64, tb.num_chunks,
         _stream(k))
     _lib.check(st, "bwd_main")
     return dq, dk, dv, db, dg

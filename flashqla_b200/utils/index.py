@@ -87,8 +87,8 @@ def prepare_chunk_indices(cu_seqlens: torch.Tensor, chunk_size: int) -> torch.Te
             started += c == 0
             seq_ids.append(started)
             chunk_ids.append(c)
-    table = torch.tensor([seq_ids, chunk_ids], dtype=torch.int64).t().reshape(-1, 2)
-    return table.to(cu_seqlens)
+    table = torch.tensor(list(zip(seq_ids, chunk_ids)), dtype=torch.int64).reshape(-1, 2)
+    return table.to(cu_seqlens).contiguous()  # row-major: the kernels index it as [2*i + j]
 
 
 @tensor_cache
