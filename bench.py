@@ -43,6 +43,9 @@ WORKLOADS = {
     "c3_fwdbwd": dict(B=1, T=32768, Hq=16, Hv=32, mode="fwdbwd", varlen="lognormal", h0=True),
     "c4_fwdbwd": dict(B=1, T=262144, Hq=8, Hv=8, mode="fwdbwd", varlen=None, h0=False),
     "c4_fwd": dict(B=1, T=262144, Hq=8, Hv=8, mode="fwd", varlen=None, h0=False),
+    # a quarter of c1 (one sequence): small enough for a full ncu capture, inputs still > L2
+    "c1_quarter_fwd": dict(B=1, T=8192, Hq=16, Hv=16, mode="fwd", varlen=None, h0=False),
+    "c1_quarter_fwdbwd": dict(B=1, T=8192, Hq=16, Hv=16, mode="fwdbwd", varlen=None, h0=False),
 }
 
 
@@ -201,12 +204,24 @@ def run_ours(args):
             ms = float(t.item())
         return ms
 
-    for _ in range(max(args.warmup, 3)):
-        step(x)
-    launches0 = _lib.launch_count
     with ClockSampler(local) as clocks:
+        for _ in range(max(args.warmup, 3)):
+            step(x)
+        if not args.kernel_only:
+            # keep the GPU under the same load until the clock sampler has come up
+            torch.cuda.synchronize()
+            t_up = time.time() + 0.6
+            while time.time() < t_up:
+                step(x)
+                torch.cuda.synchronize()
+        launches0 = _lib.launch_count
         ms = timed(lambda: step(x), args.steps)
-    launches = _lib.launch_count - launches0
+        launches = _lib.launch_count - launches0
+        if not args.kernel_only:
+            t_up = time.time() + 0.3  # a few more samples under load after the timed steps
+            while time.time() < t_up:
+                step(x)
+                torch.cuda.synchronize()
     ms_per_step = ms / args.steps
     value = tokens * world / (ms_per_step * 1e-3)
 
@@ -230,8 +245,11 @@ def run_ours(args):
             dst.copy_(src, non_blocking=True)
 
     e2e_steps = max(2, min(args.steps, 5))
-    e2e_step()
-    e2e_ms = timed(e2e_step, e2e_steps) / e2e_steps
+    if args.kernel_only:
+        e2e_ms = float("nan")
+    else:
+        e2e_step()
+        e2e_ms = timed(e2e_step, e2e_steps) / e2e_steps
     e2e_value = tokens * world / (e2e_ms * 1e-3)
 
     # ---- dominant kernel alone: the sequential forward recurrence, timed with CUDA events
@@ -265,7 +283,7 @@ def run_ours(args):
         if world > 1:
             dist.destroy_process_group()
         return
-    cpu = cpu_baseline(w, seconds=12.0) if world == 1 else None
+    cpu = cpu_baseline(w, seconds=12.0) if world == 1 and not args.kernel_only else None
     flop = (FWDBWD_FLOP if bwd else FWD_FLOP) * tokens * x["Hv"] * world
     line = {
         "metric": f"gdn_{w['mode']}_tokens_per_s", "value": round(value, 1), "unit": "tokens/s",
@@ -362,6 +380,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c1_fwd", choices=sorted(WORKLOADS))
     ap.add_argument("--scaling", default="weak", choices=["weak", "strong"])
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="skip the end-to-end and CPU legs (for profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -31,7 +31,7 @@ from .utils import tensor_cache
 
 THRESHOLD = -10.0
 MIN_SEGMENT_CHUNKS = 8
-TARGET_WAVES = 2.0
+FILL_FRACTION = 0.75  # split only when the raw streams fill less than this share of the SMs
 VALUE_SLICES = 2  # CTAs per (segment, head) in the sequential kernels
 
 
@@ -49,7 +49,7 @@ class SegmentPlan:
 
 
 def split_sequences(bounds: list[int], num_heads: int, n_sm: int,
-                    min_chunks: int = MIN_SEGMENT_CHUNKS, waves: float = TARGET_WAVES):
+                    min_chunks: int = MIN_SEGMENT_CHUNKS, fill: float = FILL_FRACTION):
     """Host-side segment planner.  ``bounds`` are the raw cumulative sequence lengths.
 
     Returns ``None`` when splitting does not pay (the raw sequences already fill the GPU, or no
@@ -61,11 +61,12 @@ def split_sequences(bounds: list[int], num_heads: int, n_sm: int,
     total = sum(chunks)
     if total == 0:
         return None
-    want_ctas = waves * n_sm
+    # The sequential kernels keep one CTA per SM, so the best schedule is a single wave of
+    # equally long streams: splitting pays only while the raw streams leave SMs idle.
     ctas_per_seg = num_heads * VALUE_SLICES
-    if len(lens) * ctas_per_seg >= want_ctas:
+    if len(lens) * ctas_per_seg >= fill * n_sm:
         return None
-    n_seg_target = math.ceil(want_ctas / ctas_per_seg)
+    n_seg_target = max(len(lens), n_sm // ctas_per_seg)
     seg_chunks = max(min_chunks, math.ceil(total / n_seg_target))
     if max(chunks) <= seg_chunks:
         return None

@@ -164,7 +164,7 @@ def chunk_gdr_bwd(q, k, v, g, beta, do, dht=None, scale=None, initial_state=None
     h0 = None if initial_state is None else initial_state.detach().clone().requires_grad_(True)
     ql, kl, vl, bl, gl = leaves
     _, _, o, _, ht = chunk_gdr_fwd(ql, kl, vl, gl, bl, scale, h0, cu_seqlens, chunk_size)
-    loss = (o * do).sum()
+    loss = (o * do[:, : o.shape[1]]).sum()  # rows past the last packed sequence carry no loss
     if dht is not None:
         loss = loss + (ht * dht).sum()
     wanted = leaves + ([h0] if h0 is not None else [])
