@@ -23,6 +23,7 @@ SIGNATURES = {
     "fqla_group_reduce": [P, P, LL, I, I, I, P],
     "fqla_warmup_scan": [P, I, I, P, I, I, F, I, P, P, P],
     "fqla_merge_states": [P, P, P, P, P, P, I, I, I, I, P],
+    "fqla_device_status": [P, I],
 }
 
 _lib = None

@@ -16,10 +16,18 @@
 // This translation unit is the mma.sync (legacy tensor core) implementation: all eight warps
 // cooperate on each product in turn, operands staged by cp.async with the next chunk's tiles in
 // flight.  It supports D = 64 and D = 128.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "fqla_internal.h"
 
 namespace fqla {
+
+// tcgen05 implementation of the full forward (fwd_tc.cu)
+int launch_fwd_tc(const void* q, const void* k, const void* v, const void* A, const float* g,
+                  const void* beta, int beta_is_f32, const float* h0, float* ht, void* o, void* h,
+                  void* vnew, int N, int Hq, int Hv, long long T_rows, float scale, SeqLayout lay,
+                  cudaStream_t st);
 
 struct FwdSeqParams {
   const bf16* q;      // may be null (state-only pass)
@@ -355,6 +363,12 @@ extern "C" int fqla_fwd_seq(const void* q, const void* k, const void* v, const v
   p.lay = SeqLayout{{cu_seqlens, idx_is64}, {chunk_offsets, idx_is64}, T};
   if (p.N <= 0) return FQLA_OK;
   cudaStream_t st = (cudaStream_t)stream;
+  // The full forward (q and o present, K = V = 128) runs on the tcgen05 kernel; state-only
+  // passes, transition matrices and D = 64 run on the mma.sync kernel in this file.
+  static const bool force_legacy = getenv("FQLA_FORCE_MMA_SYNC") != nullptr;
+  if (D == 128 && q && o && !M && !warm_chunks && !m_mask && !force_legacy)
+    return launch_fwd_tc(q, k, v, A, g_cum, beta, beta_is_f32, h0, ht, o, h, vnew, p.N, Hq, Hv,
+                         p.T_rows, scale, p.lay, st);
   if (D == 128) return launch_fwd_seq<128>(p, st);
   if (D == 64) return launch_fwd_seq<64>(p, st);
   return FQLA_ERR_UNSUPPORTED_DIM;

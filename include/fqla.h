@@ -112,6 +112,12 @@ int fqla_merge_states(const float* local, const float* M, const int* use_m, cons
                       const int* seg_begin, float* out, int n_raw, int Hv, int D, int reverse,
                       void* stream);
 
+/* Host call: reads (and with reset != 0 clears) the device-side status word of the current
+ * device.  It is non-zero after a kernel abandoned a bounded wait on one of its barriers; the
+ * outputs of that launch are then invalid.  Synchronises the device.  No counterpart in the
+ * reference (its kernels wait without bound). */
+int fqla_device_status(int* out, int reset);
+
 #ifdef __cplusplus
 }
 #endif
