@@ -32,7 +32,8 @@ from .utils import tensor_cache
 THRESHOLD = -10.0
 MIN_SEGMENT_CHUNKS = 8
 FILL_FRACTION = 0.75  # split only when the raw streams fill less than this share of the SMs
-VALUE_SLICES = 2  # CTAs per (segment, head) in the sequential kernels
+VALUE_SLICES = 1  # CTAs per (segment, head) of the tcgen05 forward kernel
+SEGMENT_OVERHEAD_CHUNKS = 3  # cost of a hand-off, in chunk steps of the main kernel
 
 
 def sm_count(device) -> int:
@@ -49,34 +50,52 @@ class SegmentPlan:
 
 
 def split_sequences(bounds: list[int], num_heads: int, n_sm: int,
-                    min_chunks: int = MIN_SEGMENT_CHUNKS, fill: float = FILL_FRACTION):
+                    min_chunks: int = MIN_SEGMENT_CHUNKS, fill: float = FILL_FRACTION,
+                    slices: int = VALUE_SLICES):
     """Host-side segment planner.  ``bounds`` are the raw cumulative sequence lengths.
 
+    The sequential kernels keep one CTA per SM and walk their chunks in order, so a launch
+    takes about ``waves * longest_segment`` chunk steps, ``waves = ceil(CTAs / SMs)``.  The
+    planner tries every maximum segment length ``ceil(longest / p)`` and keeps the cheapest,
+    charging ``SEGMENT_OVERHEAD_CHUNKS`` per wave for the hand-off (warm-up pass and merge).
+
     Returns ``None`` when splitting does not pay (the raw sequences already fill the GPU, or no
-    sequence is longer than one segment), else ``(seg_bounds, seg_begin)``: the cumulative
-    lengths of the segments and, per raw sequence, the index of its first segment.
+    split beats the unsplit schedule), else ``(seg_bounds, seg_begin)``: the cumulative lengths
+    of the segments and, per raw sequence, the index of its first segment.
     """
     lens = [e - s for s, e in zip(bounds[:-1], bounds[1:])]
     chunks = [(n + CHUNK_SIZE - 1) // CHUNK_SIZE for n in lens]
-    total = sum(chunks)
-    if total == 0:
+    longest = max(chunks) if chunks else 0
+    if longest == 0:
         return None
-    # The sequential kernels keep one CTA per SM, so the best schedule is a single wave of
-    # equally long streams: splitting pays only while the raw streams leave SMs idle.
-    ctas_per_seg = num_heads * VALUE_SLICES
+    ctas_per_seg = num_heads * slices
     if len(lens) * ctas_per_seg >= fill * n_sm:
         return None
-    n_seg_target = max(len(lens), n_sm // ctas_per_seg)
-    seg_chunks = max(min_chunks, math.ceil(total / n_seg_target))
-    if max(chunks) <= seg_chunks:
+
+    def layout(limit):
+        parts = [max(1, math.ceil(c / limit)) for c in chunks]
+        per = [math.ceil(c / p) if c else 0 for c, p in zip(chunks, parts)]
+        waves = math.ceil(sum(parts) * ctas_per_seg / n_sm)
+        return parts, per, waves * (max(per) + SEGMENT_OVERHEAD_CHUNKS)
+
+    _, _, best_cost = layout(longest)
+    best_cost -= SEGMENT_OVERHEAD_CHUNKS  # the unsplit schedule has no hand-off
+    best = None
+    for p in range(2, longest // min_chunks + 1):
+        limit = math.ceil(longest / p)
+        if limit < min_chunks:
+            break
+        parts, per, cost = layout(limit)
+        if cost < best_cost:
+            best_cost, best = cost, (parts, per)
+    if best is None:
         return None
+    parts, per = best
     seg_bounds, seg_begin = [], []
-    for s, n, c in zip(bounds[:-1], lens, chunks):
+    for s, np_, pc in zip(bounds[:-1], parts, per):
         seg_begin.append(len(seg_bounds))
-        parts = math.ceil(c / seg_chunks) if c > 0 else 1
-        per = math.ceil(c / parts) if c > 0 else 0  # balanced, still chunk aligned
-        for i in range(parts):
-            seg_bounds.append(s + i * per * CHUNK_SIZE)
+        for i in range(np_):
+            seg_bounds.append(s + i * pc * CHUNK_SIZE)  # balanced, chunk aligned
     seg_begin.append(len(seg_bounds))
     seg_bounds.append(bounds[-1])
     return seg_bounds, seg_begin

@@ -2,25 +2,27 @@
 // TMA-fed tcgen05.mma with all accumulators in tensor memory, warp-specialised.
 //
 // One CTA (512 threads) walks the chunks of one (sequence or segment, value head), K = V = 128.
-// Everything is kept TRANSPOSED so that the 128-wide value dimension sits on the MMA M axis
-// (tensor-memory lane = value index v, one thread per lane):
-//     U^T  [v x tok]  = S^T K^T                    (A = bf16 copy of S^T, B = K tile, K-major)
-//     W^T             = beta_tok (V^T - gamma_tok U^T)                  (CUDA cores, V group)
-//     Vn^T [v x tok]  = W^T A^T                    (B = A tile, K-major)
-//     O^T  [v x tok]  = s gamma_tok (S^T Q^T)  +  Vn^T Pg^T             (two accumulators)
-//     S^T  [v x k]    = gamma_last S^T + (rho Vn)^T K                   (B = K tile, MN-major)
-//     P    [tok x tok'] = Q K^T  (M = 64),  Pg = s P exp(g_tok - g_tok') for tok >= tok'
+// The state path is kept TRANSPOSED so that the 128-wide value dimension sits on the MMA M axis
+// (tensor-memory lane = value index v, one thread per lane); the output path is not (M = 64 rows
+// = tokens, so that a thread owns one contiguous output row):
+//     VT   [v x tok]    = V^T            (A = V tile read MN-major, B = identity: a transpose)
+//     U^T  [v x tok]    = S^T K^T        (A = bf16 copy of S^T, B = K tile)
+//     W^T               = beta_tok VT - (beta gamma)_tok U^T                 (V group)
+//     Vn^T [v x tok]    = W^T A^T        (B = A tile)
+//     S^T  [v x k]      = gamma_last S^T + (rho Vn)^T K        (B = K tile read MN-major)
+//     P    [tok x tok'] = Q K^T,  Pg = s P exp(g_tok - g_tok') for tok >= tok'      (O group)
+//     O    [tok x v]    = s gamma_tok (Q S) + Pg Vn            (two M = 64 accumulators)
 // which is the algebra of the reference's blackwell/fused_fwd.py:349-596 with the gate folded
 // into A (see kkt_solve).
 //
 // Warp roles (thread ranges):
 //     0-127   S group : fp32 master state in tensor memory; per chunk writes the bf16 operand copy
 //                       of S^T to shared memory, decays S^T in place, emits h / the final state
-//     128-255 V group : U^T -> W^T, Vn^T -> Vn^T and rho-scaled copies (MMA operands), v_new out
-//     256-383 O group : P -> Pg (operand), output epilogue  o = s gamma O1 + O2
-//     warp 12 : issues every tcgen05.mma (one elected lane)
-//     warp 13 : producer: per-chunk gate vectors, TMA loads of the q, k, v, A tiles (2 stages),
-//               zero-fill of the rows past the end of a partial last chunk
+//     128-255 V group : U^T, VT -> W^T;  Vn^T -> Vn^T and rho-scaled copies (MMA operands)
+//     256-383 O group : P -> Pg (operand); output epilogue o = s gamma O1 + O2, 16-byte stores
+//     warp 12 : issues every tcgen05.mma (one elected lane), descriptors precomputed
+//     warp 13 : producer: per-chunk gate vectors (fetched one chunk ahead), TMA loads of the
+//               q, k, v, A tiles (2 stages), zero-fill of rows past the end of a partial chunk
 // Synchronisation is by mbarriers only; every wait is bounded and reports through a status word.
 #include <cuda.h>
 
@@ -34,10 +36,11 @@ namespace fqla {
 
 using namespace tc;
 
+// 0 = ok; 1 after some kernel abandoned a bounded wait (its outputs are then invalid)
 __device__ int g_device_status = 0;
-// Diagnostics (FQLA_PROFILE=1): cycles the first CTA's role leaders spent waiting per barrier,
-// [role 0..4][barrier 0..15], plus [5][0] = total cycles of the CTA.
-__device__ long long g_wait_profile[6 * 16];  // 0 ok; otherwise the code of the first bounded wait that gave up
+// Diagnostics (FQLA_PROFILE=1): cycles the first CTA's role leaders spent per barrier wait and
+// per section, [role 0..4][slot 0..15], plus [5][0] = total cycles of the CTA.
+__device__ long long g_wait_profile[6 * 16];
 
 struct FwdTcParams {
   const float* g;
@@ -65,19 +68,22 @@ constexpr int OFF_WT = OFF_ST + 32768;           // W^T   [128 x 128B]
 constexpr int OFF_VNT = OFF_WT + 16384;          // Vn^T
 constexpr int OFF_VRT = OFF_VNT + 16384;         // rho * Vn^T
 constexpr int OFF_P = OFF_VRT + 16384;           // Pg    [64 x 128B]
-constexpr int OFF_VEC = OFF_P + 8192;            // 4 slots x 5 vectors x 64 floats
-constexpr int VEC_SLOT_FLOATS = 5 * CHUNK;
+constexpr int OFF_I = OFF_P + 8192;              // identity [64 x 128B]
+constexpr int OFF_VEC = OFF_I + 8192;            // 4 slots x 6 vectors x 64 floats
+constexpr int VEC_SLOT_FLOATS = 6 * CHUNK;
 constexpr int OFF_BAR = OFF_VEC + 4 * VEC_SLOT_FLOATS * 4;
 constexpr int N_BARS = 20;
 constexpr int OFF_MISC = OFF_BAR + N_BARS * 8;
 constexpr int SMEM_BYTES = OFF_MISC + 16 + 1024;  // + slack for 1024-byte alignment of the base
-// tensor-memory columns
-constexpr uint32_t TM_S = 0, TM_UV = 128, TM_O1 = 192, TM_O2 = 256, TM_P = 320;
+// tensor-memory columns.  P shares the columns of O1 in the upper half-lanes: an M = 64
+// accumulator only occupies lanes 0-15 of each 32-lane quarter, a second one fits at lane +16.
+constexpr uint32_t TM_S = 0, TM_UV = 128, TM_VT = 192, TM_O1 = 256, TM_O2 = 384;
+constexpr uint32_t TM_P = TM_O1 + (16u << 16);
 // barrier indices
 enum { FULL0 = 0, FULL1, EMPTY0, EMPTY1, S_COPY, S_DEC, U_DONE, VN_DONE, S_DONE, P_DONE, O_DONE,
        W_READY, VR_READY, P_READY, O_FREE, PRIV };
-// vector indices inside a slot
-enum { V_G = 0, V_GAM = 1, V_RHO = 2, V_BETA = 3, V_SGAM = 4 };
+// vectors inside a slot; V_GL holds gamma_last at [0]
+enum { V_G = 0, V_BETA = 1, V_BG = 2, V_RHO = 3, V_SGAM = 4, V_GL = 5 };
 }  // namespace fwdtc
 
 __global__ void __launch_bounds__(512, 1)
@@ -86,8 +92,8 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
               const __grid_constant__ CUtensorMap map_a) {
   using namespace fwdtc;
   extern __shared__ unsigned char smem_dyn[];
-  unsigned char* smem =
-      reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + OFF_MISC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + OFF_MISC + 4);
@@ -102,8 +108,8 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
   if (tid == 0) {
     mbar_init(&bars[FULL0], 1);
     mbar_init(&bars[FULL1], 1);
-    mbar_init(&bars[EMPTY0], 1 + 128);  // MMA commit + V group
-    mbar_init(&bars[EMPTY1], 1 + 128);
+    mbar_init(&bars[EMPTY0], 1);  // the MMA commit: tiles are read by tensor-core operations only
+    mbar_init(&bars[EMPTY1], 1);
     mbar_init(&bars[S_COPY], 128);
     mbar_init(&bars[S_DEC], 128);
     mbar_init(&bars[U_DONE], 1);
@@ -123,6 +129,17 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
     tma_prefetch_desc(&map_v);
     tma_prefetch_desc(&map_a);
   }
+  // identity tile (B operand of the V transpose), written once
+  for (int i = tid; i < CHUNK * 8; i += 512) {
+    int r = i >> 3, ch = i & 7;
+    uint4 z = make_uint4(0, 0, 0, 0);
+    if (ch == (r >> 3)) {
+      uint32_t one = (r & 1) ? 0x3F800000u : 0x00003F80u;  // bf16 1.0 in the high / low half
+      (&z.x)[(r & 7) >> 1] = one;
+    }
+    *reinterpret_cast<uint4*>(smem + OFF_I + r * 128 + ((ch ^ (r & 7)) << 4)) = z;
+  }
+  fence_proxy_async();
   if (warp == 12) tmem_alloc(tmem_slot, 512);
   tc_fence_before();
   __syncthreads();
@@ -163,36 +180,46 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
       ok = WAIT(FULL0 + s, (it >> 1) & 1);
       if (!ok) break;
       tc_fence_after();
-      const float gl = vec[(it & 3) * VEC_SLOT_FLOATS + V_GAM * CHUNK + CHUNK - 1];
+      if (p.profile) t_sec = clock64();
+      const float gl = vec[(it & 3) * VEC_SLOT_FLOATS + V_GL * CHUNK];
       bf16* hdst = p.h ? p.h + ((sp.chunk_base + it) * p.Hv + hv) * (long long)D * D : nullptr;
-      for (int k0 = 0; k0 < D; k0 += 32) {
-        float x[32];
-        tmem_ld32(tmem + lane_sel + TM_S + k0, x);
-        tmem_ld_wait();
-        unsigned char* row = smem + OFF_ST + (k0 >> 6) * 16384 + v * 128;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {  // 4 chunks of 8 k values
-          uint4 pk;
-          pk.x = pack_bf16(x[8 * c + 0], x[8 * c + 1]);
-          pk.y = pack_bf16(x[8 * c + 2], x[8 * c + 3]);
-          pk.z = pack_bf16(x[8 * c + 4], x[8 * c + 5]);
-          pk.w = pack_bf16(x[8 * c + 6], x[8 * c + 7]);
-          int ch = ((k0 & 63) >> 3) + c;
-          *reinterpret_cast<uint4*>(row + ((ch ^ (v & 7)) << 4)) = pk;
+      for (int kb = 0; kb < 2; ++kb) {  // 64 columns (one operand block) per round
+        float x[32], y[32];
+        tmem_ld32(tmem + lane_sel + TM_S + kb * 64, x);
+        tmem_ld32(tmem + lane_sel + TM_S + kb * 64 + 32, y);
+        tmem_ld_wait();
+        unsigned char* row = smem + OFF_ST + kb * 16384 + v * 128;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          *reinterpret_cast<uint4*>(row + ((c ^ (v & 7)) << 4)) =
+              make_uint4(pack_bf16(x[8 * c + 0], x[8 * c + 1]), pack_bf16(x[8 * c + 2], x[8 * c + 3]),
+                         pack_bf16(x[8 * c + 4], x[8 * c + 5]), pack_bf16(x[8 * c + 6], x[8 * c + 7]));
+          *reinterpret_cast<uint4*>(row + (((c + 4) ^ (v & 7)) << 4)) =
+              make_uint4(pack_bf16(y[8 * c + 0], y[8 * c + 1]), pack_bf16(y[8 * c + 2], y[8 * c + 3]),
+                         pack_bf16(y[8 * c + 4], y[8 * c + 5]), pack_bf16(y[8 * c + 6], y[8 * c + 7]));
         }
         if (hdst) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) hdst[(long long)(k0 + j) * D + v] = __float2bfloat16(x[j]);
+          for (int j = 0; j < 32; ++j) {
+            hdst[(long long)(kb * 64 + j) * D + v] = __float2bfloat16(x[j]);
+            hdst[(long long)(kb * 64 + 32 + j) * D + v] = __float2bfloat16(y[j]);
+          }
         }
 #pragma unroll
-        for (int j = 0; j < 32; ++j) x[j] *= gl;
-        tmem_st32(tmem + lane_sel + TM_S + k0, x);
+        for (int j = 0; j < 32; ++j) {
+          x[j] *= gl;
+          y[j] *= gl;
+        }
+        tmem_st32(tmem + lane_sel + TM_S + kb * 64, x);
+        tmem_st32(tmem + lane_sel + TM_S + kb * 64 + 32, y);
       }
       fence_proxy_async();
       mbar_arrive(&bars[S_COPY]);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&bars[S_DEC]);
+      if (p.profile) waited[S_COPY] += clock64() - t_sec;
     }
     if (ok && n_it > 0) ok = WAIT(S_DONE, (n_it - 1) & 1);
     if (ok && p.ht) {
@@ -208,7 +235,6 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
   } else if (warp < 8) {
     // =============================== V group ===============================
     const int v = tid - 128;
-    const int vblk = v >> 6, vch = (v & 63) >> 3, vsub = (v & 7) * 2;
     for (int it = 0; it < n_it && ok; ++it) {
       const int s = it & 1;
       const float* vs = vec + (it & 3) * VEC_SLOT_FLOATS;
@@ -219,30 +245,29 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
       ok = WAIT(U_DONE, it & 1);
       if (!ok) break;
       tc_fence_after();
-      t_sec = clock64();
-      const unsigned char* vt = smem + OFF_STAGE + s * STAGE_BYTES + 2 * TILE_QK + vblk * 8192;
+      if (p.profile) t_sec = clock64();
+#pragma unroll
       for (int t0 = 0; t0 < CHUNK; t0 += 32) {
-        float u[32];
+        float u[32], vt[32];
+        long long t_l = p.profile ? clock64() : 0;
         tmem_ld32(tmem + lane_sel + TM_UV + t0, u);
+        tmem_ld32(tmem + lane_sel + TM_VT + t0, vt);
         tmem_ld_wait();
+        if (p.profile) waited[P_DONE] += clock64() - t_l;
         unsigned char* row = smem + OFF_WT + v * 128;
+        const float4* b4 = reinterpret_cast<const float4*>(vs + V_BETA * CHUNK + t0);
+        const float4* g4 = reinterpret_cast<const float4*>(vs + V_BG * CHUNK + t0);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          uint32_t w[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            float wv[2];
-#pragma unroll
-            for (int z = 0; z < 2; ++z) {
-              int j = 8 * c + 2 * e + z, tok = t0 + j;
-              float vv = __bfloat162float(*reinterpret_cast<const bf16*>(
-                  vt + tok * 128 + ((vch ^ (tok & 7)) << 4) + vsub));
-              wv[z] = vs[V_BETA * CHUNK + tok] * (vv - vs[V_GAM * CHUNK + tok] * u[j]);
-            }
-            w[e] = pack_bf16(wv[0], wv[1]);
-          }
-          int ch = (t0 >> 3) + c;
-          *reinterpret_cast<uint4*>(row + ((ch ^ (v & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+          float4 b0 = b4[2 * c], b1 = b4[2 * c + 1], g0 = g4[2 * c], g1 = g4[2 * c + 1];
+          const float* uu = u + 8 * c;
+          const float* vv = vt + 8 * c;
+          uint4 w;
+          w.x = pack_bf16(b0.x * vv[0] - g0.x * uu[0], b0.y * vv[1] - g0.y * uu[1]);
+          w.y = pack_bf16(b0.z * vv[2] - g0.z * uu[2], b0.w * vv[3] - g0.w * uu[3]);
+          w.z = pack_bf16(b1.x * vv[4] - g1.x * uu[4], b1.y * vv[5] - g1.y * uu[5]);
+          w.w = pack_bf16(b1.z * vv[6] - g1.z * uu[6], b1.w * vv[7] - g1.w * uu[7]);
+          *reinterpret_cast<uint4*>(row + ((((t0 >> 3) + c) ^ (v & 7)) << 4)) = w;
         }
       }
       fence_proxy_async();
@@ -250,27 +275,30 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
       mbar_arrive(&bars[W_READY]);
       if (p.profile) waited[S_COPY] += clock64() - t_sec;
       ok = WAIT(VN_DONE, it & 1);
-      t_sec = clock64();
       if (!ok) break;
       tc_fence_after();
+      if (p.profile) t_sec = clock64();
+#pragma unroll
       for (int t0 = 0; t0 < CHUNK; t0 += 32) {
         float x[32];
+        long long t_l = p.profile ? clock64() : 0;
         tmem_ld32(tmem + lane_sel + TM_UV + t0, x);
         tmem_ld_wait();
+        if (p.profile) waited[O_DONE] += clock64() - t_l;
         unsigned char* rown = smem + OFF_VNT + v * 128;
         unsigned char* rowr = smem + OFF_VRT + v * 128;
+        const float4* r4 = reinterpret_cast<const float4*>(vs + V_RHO * CHUNK + t0);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          uint32_t a[4], b[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            int j = 8 * c + 2 * e, tok = t0 + j;
-            a[e] = pack_bf16(x[j], x[j + 1]);
-            b[e] = pack_bf16(vs[V_RHO * CHUNK + tok] * x[j], vs[V_RHO * CHUNK + tok + 1] * x[j + 1]);
-          }
+          float4 r0 = r4[2 * c], r1 = r4[2 * c + 1];
+          const float* xx = x + 8 * c;
           int sw = (((t0 >> 3) + c) ^ (v & 7)) << 4;
-          *reinterpret_cast<uint4*>(rown + sw) = make_uint4(a[0], a[1], a[2], a[3]);
-          *reinterpret_cast<uint4*>(rowr + sw) = make_uint4(b[0], b[1], b[2], b[3]);
+          *reinterpret_cast<uint4*>(rown + sw) =
+              make_uint4(pack_bf16(xx[0], xx[1]), pack_bf16(xx[2], xx[3]), pack_bf16(xx[4], xx[5]),
+                         pack_bf16(xx[6], xx[7]));
+          *reinterpret_cast<uint4*>(rowr + sw) =
+              make_uint4(pack_bf16(r0.x * xx[0], r0.y * xx[1]), pack_bf16(r0.z * xx[2], r0.w * xx[3]),
+                         pack_bf16(r1.x * xx[4], r1.y * xx[5]), pack_bf16(r1.z * xx[6], r1.w * xx[7]));
         }
         if (p.vnew) {
 #pragma unroll
@@ -279,38 +307,49 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
               p.vnew[((row0 + t0 + j) * p.Hv + hv) * D + v] = __float2bfloat16(x[j]);
         }
       }
+      long long t_f = p.profile ? clock64() : 0;
       fence_proxy_async();
       tc_fence_before();
       mbar_arrive(&bars[VR_READY]);
       if (p.profile) waited[S_DEC] += clock64() - t_sec;
-      mbar_arrive(&bars[EMPTY0 + s]);
+      if (p.profile) waited[P_READY] += clock64() - t_f;
     }
   } else if (warp < 12) {
     // =============================== O group ===============================
-    const int v = tid - 256;
     const int wq = warp & 3;
+    const int tok_o = 16 * wq + (lane & 15);  // lanes 0-15: a row of O;  lanes 16-31: a row of P
     auto epilogue = [&](int it) {
       const float* vs = vec + (it & 3) * VEC_SLOT_FLOATS;
       const long long row0 = sp.bos + (long long)it * CHUNK;
       const int valid = min(CHUNK, sp.len - it * CHUNK);
-      for (int t0 = 0; t0 < CHUNK; t0 += 32) {
+      const float sg = vs[V_SGAM * CHUNK + tok_o];
+      bf16* orow = p.o ? p.o + ((row0 + tok_o) * p.Hv + hv) * D : nullptr;
+      const bool write = lane < 16 && tok_o < valid && orow != nullptr;
+#pragma unroll
+      for (int c0 = 0; c0 < D; c0 += 32) {
         float a[32], b[32];
-        tmem_ld32(tmem + lane_sel + TM_O1 + t0, a);
-        tmem_ld32(tmem + lane_sel + TM_O2 + t0, b);
+        tmem_ld32(tmem + lane_sel + TM_O1 + c0, a);
+        tmem_ld32(tmem + lane_sel + TM_O2 + c0, b);
         tmem_ld_wait();
-        if (t0 + 32 >= CHUNK) {  // all tensor-memory reads of this chunk's output are done
+        if (c0 + 32 >= D) {  // all tensor-memory reads of this chunk's output are done
           tc_fence_before();
           mbar_arrive(&bars[O_FREE]);
         }
-        if (p.o) {
+        if (write) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (t0 + j < valid)
-              p.o[((row0 + t0 + j) * p.Hv + hv) * D + v] =
-                  __float2bfloat16(vs[V_SGAM * CHUNK + t0 + j] * a[j] + b[j]);
+          for (int c = 0; c < 4; ++c) {
+            const float* aa = a + 8 * c;
+            const float* bb = b + 8 * c;
+            *reinterpret_cast<uint4*>(orow + c0 + 8 * c) = make_uint4(
+                pack_bf16(sg * aa[0] + bb[0], sg * aa[1] + bb[1]),
+                pack_bf16(sg * aa[2] + bb[2], sg * aa[3] + bb[3]),
+                pack_bf16(sg * aa[4] + bb[4], sg * aa[5] + bb[5]),
+                pack_bf16(sg * aa[6] + bb[6], sg * aa[7] + bb[7]));
+          }
         }
       }
     };
+    const float log2_scale = log2f(p.scale);
     for (int it = 0; it < n_it && ok; ++it) {
       const int s = it & 1;
       const float* vs = vec + (it & 3) * VEC_SLOT_FLOATS;
@@ -320,39 +359,38 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
         ok = WAIT(O_DONE, (it - 1) & 1);
         if (!ok) break;
         tc_fence_after();
-        { long long t_e = clock64(); epilogue(it - 1); if (p.profile) waited[S_COPY] += clock64() - t_e; }
+        if (p.profile) t_sec = clock64();
+        epilogue(it - 1);
+        if (p.profile) waited[S_COPY] += clock64() - t_sec;
       }
       ok = WAIT(P_DONE, it & 1);
       if (!ok) break;
       tc_fence_after();
-      t_sec = clock64();
-      // P is an M = 64 accumulator: row tok lives in lane (tok % 16) + 32 * (tok / 16)
-      const int tok = 16 * wq + (lane & 15);
-      const float gt = vs[V_G * CHUNK + tok];
+      if (p.profile) t_sec = clock64();
+      // Pg = s P exp(g_tok - g_col) = P exp2((g_tok - g_col) log2e + log2 s), col <= tok
+      const float gt2 = vs[V_G * CHUNK + tok_o] * 1.4426950408889634f + log2_scale;
+#pragma unroll
       for (int c0 = 0; c0 < CHUNK; c0 += 32) {
         float x[32];
-        tmem_ld32(tmem + lane_sel + TM_P + c0, x);
+        tmem_ld32(tmem + lane_sel + TM_O1 + c0, x);  // lanes 16-31 of the quarter hold P
         tmem_ld_wait();
-        if (lane < 16) {
-          unsigned char* row = smem + OFF_P + tok * 128;
+        if (lane >= 16) {
+          unsigned char* row = smem + OFF_P + tok_o * 128;
+          const float4* g4 = reinterpret_cast<const float4*>(vs + V_G * CHUNK + c0);
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
-            uint32_t w[4];
+            float4 ga = g4[2 * c], gb = g4[2 * c + 1];
+            const float gc[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
+            float pv[8];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              float pv[2];
-#pragma unroll
-              for (int z = 0; z < 2; ++z) {
-                int col = c0 + 8 * c + 2 * e + z;
-                pv[z] = tok >= col ? p.scale * x[8 * c + 2 * e + z] *
-                                         fast_exp(gt - vs[V_G * CHUNK + col])
-                                   : 0.f;
-              }
-              w[e] = pack_bf16(pv[0], pv[1]);
+            for (int e = 0; e < 8; ++e) {
+              int col = c0 + 8 * c + e;
+              float ex = exp2f(fmaf(gc[e], -1.4426950408889634f, gt2));
+              pv[e] = col <= tok_o ? x[8 * c + e] * ex : 0.f;
             }
-            int ch = (c0 >> 3) + c;
-            *reinterpret_cast<uint4*>(row + ((ch ^ (tok & 7)) << 4)) =
-                make_uint4(w[0], w[1], w[2], w[3]);
+            *reinterpret_cast<uint4*>(row + ((((c0 >> 3) + c) ^ (tok_o & 7)) << 4)) =
+                make_uint4(pack_bf16(pv[0], pv[1]), pack_bf16(pv[2], pv[3]), pack_bf16(pv[4], pv[5]),
+                           pack_bf16(pv[6], pv[7]));
           }
         }
       }
@@ -370,93 +408,129 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
     }
     // rows of o past the end of the last packed sequence come out zero
     if (p.o && p.lay.cu.ptr && n == p.N - 1) {
-      for (long long r = sp.bos + sp.len; r < p.T_rows; ++r)
-        p.o[(r * p.Hv + hv) * D + v] = __float2bfloat16(0.f);
+      const long long end = sp.bos + sp.len;
+      for (long long i = tid - 256; i < (p.T_rows - end) * 16; i += 128)
+        *reinterpret_cast<uint4*>(p.o + ((end + (i >> 4)) * p.Hv + hv) * D + (i & 15) * 8) =
+            make_uint4(0, 0, 0, 0);
     }
   } else if (warp == 12) {
     // =============================== MMA issuer ===============================
     if (lane == 0) {
       constexpr uint32_t ID_P = idesc_bf16(64, 64, 0, 0);
-      constexpr uint32_t ID_N64 = idesc_bf16(128, 64, 0, 0);
+      constexpr uint32_t ID_O = idesc_bf16(64, 128, 0, 0);
+      constexpr uint32_t ID_U = idesc_bf16(128, 64, 0, 0);
+      constexpr uint32_t ID_VT = idesc_bf16(128, 64, 1, 0);
       constexpr uint32_t ID_S = idesc_bf16(128, 128, 0, 1);
-      auto stage = [&](int s) { return smem + OFF_STAGE + s * STAGE_BYTES; };
-      auto issue_p = [&](int s) {
-        const unsigned char* q = stage(s);
-        const unsigned char* k = stage(s) + TILE_QK;
+      // descriptors of every operand tile, built once; a byte offset is added as (off >> 4)
+      uint64_t dQ[2], dK[2], dKmn[2], dVmn[2], dA[2];
+#pragma unroll
+      for (int s = 0; s < 2; ++s) {
+        const unsigned char* st = smem + OFF_STAGE + s * STAGE_BYTES;
+        dQ[s] = desc_kmajor(st);
+        dK[s] = desc_kmajor(st + TILE_QK);
+        dKmn[s] = desc_mnmajor(st + TILE_QK, 8192);
+        dVmn[s] = desc_mnmajor(st + 2 * TILE_QK, 8192);
+        dA[s] = desc_kmajor(st + 2 * TILE_QK + TILE_V);
+      }
+      const uint64_t dST = desc_kmajor(smem + OFF_ST), dWT = desc_kmajor(smem + OFF_WT);
+      const uint64_t dVNT = desc_kmajor(smem + OFF_VNT), dVRT = desc_kmajor(smem + OFF_VRT);
+      const uint64_t dP = desc_kmajor(smem + OFF_P), dI = desc_kmajor(smem + OFF_I);
+      // K-step j of a 128-wide K-major operand stored as two 64-column blocks of `blk` bytes
+      auto kstep = [](int j, int blk) { return (uint64_t)(((j >> 2) * blk + (j & 3) * 32) >> 4); };
+      auto issue_p_vt = [&](int s) {
 #pragma unroll
         for (int j = 0; j < 8; ++j)
-          umma(tmem + TM_P, desc_kmajor(q + (j >> 2) * 8192 + (j & 3) * 32),
-               desc_kmajor(k + (j >> 2) * 8192 + (j & 3) * 32), ID_P, j > 0);
+          umma(tmem + TM_P, dQ[s] + kstep(j, 8192), dK[s] + kstep(j, 8192), ID_P, j > 0);
         umma_commit(&bars[P_DONE]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)  // VT = V^T: A = V tile MN-major (16 rows per step), B = I
+          umma(tmem + TM_VT, dVmn[s] + (uint64_t)(j * 128), dI + (uint64_t)(j * 2), ID_VT, j > 0);
       };
       for (int it = 0; it < n_it && ok; ++it) {
         const int s = it & 1;
-        const unsigned char* q = stage(s);
-        const unsigned char* k = stage(s) + TILE_QK;
-        const unsigned char* a = stage(s) + 2 * TILE_QK + TILE_V;
         ok = WAIT(FULL0 + s, (it >> 1) & 1);
         if (!ok) break;
         tc_fence_after();
-        if (it == 0) issue_p(0);
+        if (it == 0) issue_p_vt(0);
         ok = WAIT(S_COPY, it & 1);
         if (!ok) break;
         tc_fence_after();
+        if (p.profile) t_sec = clock64();
         // U^T = S^T K^T
 #pragma unroll
         for (int j = 0; j < 8; ++j)
-          umma(tmem + TM_UV, desc_kmajor(smem + OFF_ST + (j >> 2) * 16384 + (j & 3) * 32),
-               desc_kmajor(k + (j >> 2) * 8192 + (j & 3) * 32), ID_N64, j > 0);
+          umma(tmem + TM_UV, dST + kstep(j, 16384), dK[s] + kstep(j, 8192), ID_U, j > 0);
         umma_commit(&bars[U_DONE]);
+        if (p.profile) waited[U_DONE] += clock64() - t_sec;
         if (it > 0) {
           ok = WAIT(O_FREE, (it - 1) & 1);
           if (!ok) break;
           tc_fence_after();
         }
-        // O1^T = S^T Q^T
+        if (p.profile) t_sec = clock64();
+        // O1 = Q S      (B = S^T copy: N = v rows, K = k)
 #pragma unroll
         for (int j = 0; j < 8; ++j)
-          umma(tmem + TM_O1, desc_kmajor(smem + OFF_ST + (j >> 2) * 16384 + (j & 3) * 32),
-               desc_kmajor(q + (j >> 2) * 8192 + (j & 3) * 32), ID_N64, j > 0);
+          umma(tmem + TM_O1, dQ[s] + kstep(j, 8192), dST + kstep(j, 16384), ID_O, j > 0);
+        if (p.profile) waited[O_DONE] += clock64() - t_sec;
         ok = WAIT(W_READY, it & 1);
         if (!ok) break;
         tc_fence_after();
+        if (p.profile) t_sec = clock64();
         // Vn^T = W^T A^T
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-          umma(tmem + TM_UV, desc_kmajor(smem + OFF_WT + j * 32), desc_kmajor(a + j * 32), ID_N64,
-               j > 0);
+          umma(tmem + TM_UV, dWT + (uint64_t)(j * 2), dA[s] + (uint64_t)(j * 2), ID_U, j > 0);
         umma_commit(&bars[VN_DONE]);
+        if (p.profile) waited[VN_DONE] += clock64() - t_sec;
         ok = WAIT(VR_READY, it & 1);
         if (!ok) break;
         ok = WAIT(S_DEC, it & 1);
         if (!ok) break;
         tc_fence_after();
+        if (p.profile) t_sec = clock64();
         // S^T += (rho Vn)^T K      (B = K tile read MN-major: contraction over its 64 rows)
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-          umma(tmem + TM_S, desc_kmajor(smem + OFF_VRT + j * 32), desc_mnmajor(k + j * 2048, 8192),
-               ID_S, true);
+          umma(tmem + TM_S, dVRT + (uint64_t)(j * 2), dKmn[s] + (uint64_t)(j * 128), ID_S, true);
         umma_commit(&bars[S_DONE]);
+        if (p.profile) waited[S_DONE] += clock64() - t_sec;
         ok = WAIT(P_READY, it & 1);
         if (!ok) break;
         tc_fence_after();
-        // O2^T = Vn^T Pg^T
+        if (p.profile) t_sec = clock64();
+        // O2 = Pg Vn     (B = Vn^T copy: N = v rows, K = tok')
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-          umma(tmem + TM_O2, desc_kmajor(smem + OFF_VNT + j * 32),
-               desc_kmajor(smem + OFF_P + j * 32), ID_N64, j > 0);
+          umma(tmem + TM_O2, dP + (uint64_t)(j * 2), dVNT + (uint64_t)(j * 2), ID_O, j > 0);
         umma_commit(&bars[O_DONE]);
         umma_commit(&bars[EMPTY0 + s]);
+        if (p.profile) waited[EMPTY0] += clock64() - t_sec;
         if (it + 1 < n_it) {
           ok = WAIT(FULL0 + (s ^ 1), ((it + 1) >> 1) & 1);
           if (!ok) break;
           tc_fence_after();
-          issue_p(s ^ 1);
+          if (p.profile) t_sec = clock64();
+          issue_p_vt(s ^ 1);
+          if (p.profile) waited[P_DONE] += clock64() - t_sec;
         }
       }
     }
   } else if (warp == 13) {
     // =============================== producer ===============================
+    float g_r[2] = {0.f, 0.f}, b_r[2] = {0.f, 0.f}, gl_r = 0.f;
+    auto fetch = [&](int it) {
+      const long long row0 = sp.bos + (long long)it * CHUNK;
+      const int valid = min(CHUNK, sp.len - it * CHUNK);
+      gl_r = p.g[(row0 + valid - 1) * p.Hv + hv];
+#pragma unroll
+      for (int z = 0; z < 2; ++z) {
+        int r = 2 * lane + z, rc = min(r, valid - 1);
+        g_r[z] = p.g[(row0 + rc) * p.Hv + hv];
+        b_r[z] = r < valid ? load_beta(p.beta, p.beta_is_f32, (row0 + r) * p.Hv + hv) : 0.f;
+      }
+    };
+    if (n_it > 0) fetch(0);
     for (int it = 0; it < n_it && ok; ++it) {
       const int s = it & 1;
       const long long row0 = sp.bos + (long long)it * CHUNK;
@@ -466,19 +540,17 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
         if (!ok) break;
       }
       float* vs = vec + (it & 3) * VEC_SLOT_FLOATS;
-      const float g_last = p.g[(row0 + valid - 1) * p.Hv + hv];
 #pragma unroll
       for (int z = 0; z < 2; ++z) {
-        int r = 2 * lane + z, rc = min(r, valid - 1);
-        float gv = p.g[(row0 + rc) * p.Hv + hv];
-        float bv = r < valid ? load_beta(p.beta, p.beta_is_f32, (row0 + r) * p.Hv + hv) : 0.f;
-        float gam = fast_exp(gv);
-        vs[V_G * CHUNK + r] = gv;
-        vs[V_GAM * CHUNK + r] = gam;
-        vs[V_RHO * CHUNK + r] = fast_exp(g_last - gv);
-        vs[V_BETA * CHUNK + r] = bv;
+        int r = 2 * lane + z;
+        float gam = fast_exp(g_r[z]);
+        vs[V_G * CHUNK + r] = g_r[z];
+        vs[V_BETA * CHUNK + r] = b_r[z];
+        vs[V_BG * CHUNK + r] = b_r[z] * gam;
+        vs[V_RHO * CHUNK + r] = fast_exp(gl_r - g_r[z]);
         vs[V_SGAM * CHUNK + r] = p.scale * gam;
       }
+      if (lane == 0) vs[V_GL * CHUNK] = fast_exp(gl_r);
       __syncwarp();
       unsigned char* st = smem + OFF_STAGE + s * STAGE_BYTES;
       const bool partial = valid < CHUNK;
@@ -488,15 +560,16 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
         const int y = (int)row0;
         tma_load_2d(st + TILE_QK, &map_k, hq * D, y, bar);
         tma_load_2d(st + TILE_QK + 8192, &map_k, hq * D + 64, y, bar);
-        tma_load_2d(st, &map_q, hq * D, y, bar);
-        tma_load_2d(st + 8192, &map_q, hq * D + 64, y, bar);
         tma_load_2d(st + 2 * TILE_QK, &map_v, hv * D, y, bar);
         tma_load_2d(st + 2 * TILE_QK + 8192, &map_v, hv * D + 64, y, bar);
+        tma_load_2d(st, &map_q, hq * D, y, bar);
+        tma_load_2d(st + 8192, &map_q, hq * D + 64, y, bar);
         tma_load_2d(st + 2 * TILE_QK + TILE_V, &map_a, hv * CHUNK, y, bar);
       }
+      if (it + 1 < n_it) fetch(it + 1);  // in flight while this warp waits for the next free stage
       if (partial) {
         // rows past the sequence end belong to the next sequence: wait for the copy, zero them
-        ok = WAIT(PRIV, 0);  // used at most once per CTA (last chunk)
+        ok = WAIT(PRIV, 0);  // only the last chunk of a sequence can be partial: used once
         if (!ok) break;
         for (int blk = 0; blk < 7; ++blk) {
           unsigned char* base = st + blk * 8192;
@@ -511,7 +584,8 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
     }
   }
 
-  if (p.profile && blockIdx.x == 0 && (tid == 0 || tid == 128 || tid == 256 || tid == 384 || tid == 416)) {
+  if (p.profile && blockIdx.x == 0 &&
+      (tid == 0 || tid == 128 || tid == 256 || tid == 384 || tid == 416)) {
     int role = tid == 0 ? 0 : tid == 128 ? 1 : tid == 256 ? 2 : tid == 384 ? 3 : 4;
     for (int i = 0; i < 16; ++i) g_wait_profile[role * 16 + i] = waited[i];
     if (tid == 0) g_wait_profile[5 * 16] = clock64() - t_start;

@@ -65,6 +65,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
   for (uint32_t i = 0; i < budget; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 255u) == 255u && *abort_flag) return false;
+#ifdef FQLA_WAIT_SLEEP_NS
+    __nanosleep(FQLA_WAIT_SLEEP_NS);  // keep waiting warps out of the issue slots of working ones
+#endif
   }
   *abort_flag = 1;
   return false;

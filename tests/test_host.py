@@ -70,8 +70,11 @@ def test_segment_planner_properties():
     assert split_sequences(list(range(0, 65 * 2048, 2048)), 8, 148) is None
     # nothing longer than a segment
     assert split_sequences([0, 256], 1, 148) is None
-    # 4 sequences x 16 heads x 2 value slices = 128 streams: already a full wave on 148 SMs
-    assert split_sequences([0, 8192, 16384, 24576, 32768], 16, 148) is None
+    # 4 sequences x 16 heads = 64 streams on 148 SMs: halving each sequence gives one full wave
+    seg, begin = split_sequences([0, 8192, 16384, 24576, 32768], 16, 148)
+    assert len(seg) - 1 == 8 and begin == [0, 2, 4, 6, 8]
+    # 10 sequences x 16 heads already fill the SMs
+    assert split_sequences(list(range(0, 11 * 4096, 4096)), 16, 148) is None
     for bounds, heads in (([0, 262144], 8), ([0, 8192, 16384, 24576, 32768], 2),
                           ([0, 100, 5000, 5064, 30000], 2), ([0, 4096 + 77], 2)):
         res = split_sequences(bounds, heads, 148)
