@@ -163,17 +163,35 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     w = WORKLOADS[args.workload]
+    tshard = False
     if args.scaling == "strong" and world > 1:
-        # shard the fixed workload by value head (and the matching q/k heads): no communication
-        hv = max(w["Hv"] // world, 1)
-        hq = max(w["Hq"] // world, 1)
-        x = make_batch(w, dev, 1234 + rank, heads_q=hq, heads_v=hv)
+        if w["B"] == 1 and not w["varlen"]:
+            # one long sequence: shard along T, boundary states handed over by one all-gather
+            tshard = True
+            w_loc = dict(w, T=w["T"] // world)
+            x = make_batch(w_loc, dev, 1234 + rank)
+            x["h0"] = None
+        else:
+            # shard by value head (and the matching q/k heads): no communication
+            hv = max(w["Hv"] // world, 1)
+            hq = max(w["Hq"] // world, 1)
+            x = make_batch(w, dev, 1234 + rank, heads_q=hq, heads_v=hv)
     else:
         x = make_batch(w, dev, 1234 + rank)
     tokens = x["tokens"]
     bwd = w["mode"] == "fwdbwd"
 
     def step(inp):
+        if tshard:
+            from flashqla_b200 import distributed as fd
+
+            g_cum, A, o, ht, saved = fd.fwd_tsharded(inp["q"], inp["k"], inp["v"], inp["g"],
+                                                     inp["beta"], None, None)
+            if not bwd:
+                return o, ht
+            grads = fd.bwd_tsharded(inp["q"], inp["k"], inp["v"], g_cum, inp["beta"], A,
+                                    inp["do"], inp["dht"], None, saved)
+            return (o, ht) + tuple(grads)
         g_cum, A, o, _, ht, cache = fq.chunk_gated_delta_rule_fwd(
             inp["q"], inp["k"], inp["v"], inp["g"], inp["beta"], None, inp["h0"], inp["cu"],
             output_final_state=True, enable_fwd_cp_cache=bwd)
@@ -291,6 +309,8 @@ def run_ours(args):
         "ms_per_step": round(ms_per_step, 4), "higher_is_better": True,
         "scaling": args.scaling, "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": args.workload, **{k: v for k, v in w.items()},
+                   "sharding": ("T" if tshard else "head") if args.scaling == "strong" and world > 1
+                   else "replicated workload per GPU (independent sequences)",
                    "tokens_per_gpu": tokens, "Hq_per_gpu": x["Hq"], "Hv_per_gpu": x["Hv"],
                    "K": 128, "V": 128, "chunk": 64,
                    "l2": "inputs larger than L2 (no flush needed)"},

@@ -45,6 +45,28 @@ def _beta_in(beta):
     return beta if beta.dtype in (torch.float32, torch.bfloat16) else beta.float()
 
 
+def run_forward(q, k, v, A, g_cum, beta, scale, h0, tables, output_final_state=True,
+                output_h=False, auto_cp=True, enable_fwd_cp_cache=False):
+    """The part of the forward after cumsum and kkt+solve: optional split into segments with
+    state hand-off, then the sequential recurrence.  Returns ``(outputs dict, cp_cache)``."""
+    plan = cp.plan_segments(tables, v.shape[2], is_bwd=False, device=k.device) if auto_cp else None
+    cp_cache = None
+    if plan is not None:
+        seg_h0 = cp.forward_segment_states(plan, k, v, A, g_cum, beta, scale, h0)
+        res = ops.fwd_seq(q, k, v, A, g_cum, beta, scale, seg_h0,
+                          output_final_state=output_final_state, output_h=output_h,
+                          tables=plan.seg_tables)
+        if output_final_state:
+            res["ht"] = res["ht"][plan.last_seg_of_raw]
+        if enable_fwd_cp_cache:
+            cp_cache = (seg_h0,)
+    else:
+        res = ops.fwd_seq(q, k, v, A, g_cum, beta, scale, h0,
+                          output_final_state=output_final_state, output_h=output_h,
+                          tables=tables)
+    return res, cp_cache
+
+
 def chunk_gated_delta_rule_fwd(
     q: torch.Tensor,
     k: torch.Tensor,
@@ -74,21 +96,8 @@ def chunk_gated_delta_rule_fwd(
     A = ops.kkt_solve(k, beta, g_cum, cu_seqlens)
     h0 = _state_in(initial_state, state_v_first)
 
-    plan = cp.plan_segments(tables, v.shape[2], is_bwd=False, device=k.device) if auto_cp else None
-    cp_cache = None
-    if plan is not None:
-        seg_h0 = cp.forward_segment_states(plan, k, v, A, g_cum, beta, scale, h0)
-        res = ops.fwd_seq(q, k, v, A, g_cum, beta, scale, seg_h0,
-                          output_final_state=output_final_state, output_h=output_h,
-                          tables=plan.seg_tables)
-        if output_final_state:
-            res["ht"] = res["ht"][plan.last_seg_of_raw]
-        if enable_fwd_cp_cache:
-            cp_cache = (seg_h0,)
-    else:
-        res = ops.fwd_seq(q, k, v, A, g_cum, beta, scale, h0,
-                          output_final_state=output_final_state, output_h=output_h,
-                          tables=tables)
+    res, cp_cache = run_forward(q, k, v, A, g_cum, beta, scale, h0, tables, output_final_state,
+                                output_h, auto_cp, enable_fwd_cp_cache)
     o = res["o"]
     h = res.get("h")
     if h is not None:

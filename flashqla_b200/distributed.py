@@ -1,0 +1,166 @@
+"""Multi-GPU use of the gated-delta-rule path: one process per GPU, ``torch.distributed``.
+
+Two ways to spread the work over the GPUs of a node (the reference has neither; its "TP4/TP8"
+benchmark rows only emulate the head count one tensor-parallel shard would see):
+
+* **(batch, head) sharding** - streams are independent per (sequence, value head), so each rank
+  simply runs the operator on its own slice.  No communication.  ``shard_heads`` cuts a full
+  problem into the slice of one rank.
+* **T sharding of one long sequence** - rank ``r`` owns the tokens ``[r*T/R, (r+1)*T/R)``.  Each
+  rank first computes, from a zero state, the end state of its own tokens and (only where the
+  gates do not let the past die out inside the shard) the exact transition matrix ``M`` of its
+  shard; one all-gather hands every rank all boundary summaries (``[Hv,K,V]`` + ``[Hv,K,K]`` fp32
+  per rank, about 1 MiB at Hv = 8), every rank chains them locally
+  (``start[r+1] = local[r] + M[r] start[r]``) and then runs the ordinary forward on its tokens
+  with its start state.  The backward pass mirrors this for the state gradient with ``M^T`` in
+  the other direction.  The payload always lands in the receiving GPU's own memory (the
+  all-gather output) before any kernel reads it.
+
+The collective is issued through ``torch.distributed`` (NCCL over NVLink on GPUs, gloo in the
+CPU tests of the host logic); a rank that never joins surfaces as the process group's timeout
+error on the host, no kernel ever waits on another GPU.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from . import cp, ops
+from .api import chunk_gated_delta_rule_bwd, run_forward
+from .ops import CHUNK_SIZE
+
+
+def shard_heads(q, k, v, g, beta, rank: int, world: int, initial_state=None):
+    """Slice of a full problem owned by ``rank`` under value-head sharding (the matching q/k
+    heads follow their value heads; with fewer q/k heads than ranks the group's q/k head is
+    replicated).  Returns contiguous tensors ``(q, k, v, g, beta, initial_state)``."""
+    Hq, Hv = q.shape[2], v.shape[2]
+    if Hv % world:
+        raise ValueError(f"{Hv} value heads do not divide over {world} ranks")
+    hv = Hv // world
+    v0 = rank * hv
+    G = Hv // Hq
+    if hv % G == 0:
+        q0, hq = v0 // G, hv // G
+    elif G % hv == 0:
+        q0, hq = v0 // G, 1  # the shard lies inside one q/k group
+    else:
+        raise ValueError("value-head shard straddles q/k groups unevenly")
+    sl = lambda x, a, n: x[:, :, a:a + n].contiguous()  # noqa: E731
+    h0 = None if initial_state is None else initial_state[:, v0:v0 + hv].contiguous()
+    return sl(q, q0, hq), sl(k, q0, hq), sl(v, v0, hv), sl(g, v0, hv), sl(beta, v0, hv), h0
+
+
+# ---- T sharding -----------------------------------------------------------------------------
+
+def chain_boundary_states(local, M, use_m, first, rank: int, reverse: bool = False,
+                          merge_fn=None):
+    """Start state (or, reversed, end gradient) of ``rank`` from the gathered per-rank
+    summaries.  ``local``, ``M``: ``[R, Hv, D, D]`` fp32; ``use_m``: ``[R, Hv]`` int32;
+    ``first``: ``[1, Hv, D, D]`` state entering rank 0 (leaving rank R-1 when reversed) or None.
+    ``merge_fn`` defaults to the CUDA merge kernel; the CPU tests pass a torch stand-in."""
+    merge_fn = merge_fn or ops.merge_states
+    R = local.shape[0]
+    seg_begin = torch.tensor([0, R], dtype=torch.int32, device=local.device)
+    chained = merge_fn(local, M, use_m, first, seg_begin, reverse)
+    return chained[rank:rank + 1].contiguous()
+
+
+def _gather(x, group):
+    world = dist.get_world_size(group)
+    parts = [torch.empty_like(x) for _ in range(world)]
+    dist.all_gather(parts, x.contiguous(), group=group)
+    return torch.stack(parts)
+
+
+def exchange_forward(local, M, use_m, initial_state, group=None, merge_fn=None):
+    """All-gather the forward summaries of every rank and return this rank's start state
+    ``[1, Hv, D, D]``.  ``local``/``M``: ``[1, Hv, D, D]``; ``use_m``: ``[1, Hv]`` int32;
+    ``initial_state`` is the sequence's initial state (used from rank 0 only) or None."""
+    rank = dist.get_rank(group)
+    first = None
+    if initial_state is not None:
+        first = initial_state.clone()
+        dist.broadcast(first, src=dist.get_global_rank(group, 0) if group else 0, group=group)
+    all_local, all_m, all_use = _gather(local[0], group), _gather(M[0], group), _gather(use_m[0], group)
+    return chain_boundary_states(all_local, all_m, all_use, first, rank, False, merge_fn)
+
+
+def exchange_backward(local, M, use_m, dht, group=None, merge_fn=None):
+    """Mirror of ``exchange_forward`` for the state gradient: returns the gradient of the state
+    leaving this rank's tokens.  ``dht`` is the gradient of the sequence's final state (used from
+    the last rank only) or None."""
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    last = None
+    if dht is not None:
+        last = dht.clone()
+        src = world - 1
+        dist.broadcast(last, src=dist.get_global_rank(group, src) if group else src, group=group)
+    all_local, all_m, all_use = _gather(local[0], group), _gather(M[0], group), _gather(use_m[0], group)
+    return chain_boundary_states(all_local, all_m, all_use, last, rank, True, merge_fn)
+
+
+def _local_summary_fwd(k, v, A, g_cum, beta, scale):
+    """(end state from zero, M, fallback flag) of this rank's whole shard, shapes [1,Hv,D,D]."""
+    T = k.shape[1]
+    seg_cu = torch.tensor([0, T], dtype=torch.int32, device=k.device)
+    warm, fallback = ops.warmup_scan(g_cum, seg_cu, cp.THRESHOLD, from_start=False)
+    tables = ops.SeqTables(1, T, seg_cu)
+    res = ops.fwd_seq(None, k, v, A, g_cum, beta, scale, None, output_o=False,
+                      output_final_state=True, output_m=True, warm_chunks=warm, m_mask=fallback,
+                      tables=tables)
+    return res["ht"], res["M"], fallback
+
+
+def fwd_tsharded(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=True,
+                 group=None):
+    """Forward of ONE sequence whose tokens are split evenly over the ranks of ``group``
+    (this rank passes its own ``[1, T/R, ...]`` slice, a multiple of 64 tokens).  Returns
+    ``(g_cum, A, o, final_state, saved)``; ``final_state`` is the sequence's final state on every
+    rank, ``saved`` carries what ``bwd_tsharded`` needs."""
+    assert q.shape[0] == 1 and q.shape[1] % CHUNK_SIZE == 0, "T shard must be a chunk multiple"
+    if scale is None:
+        scale = k.shape[-1] ** -0.5
+    world = dist.get_world_size(group)
+    g32 = g if g.dtype == torch.float32 else g.float()
+    g_cum = ops.chunk_local_cumsum(g32.contiguous(), CHUNK_SIZE, None)
+    A = ops.kkt_solve(k, beta, g_cum, None)
+    local, M, fallback = _local_summary_fwd(k, v, A, g_cum, beta, scale)
+    h0 = None if initial_state is None else initial_state.float().contiguous()
+    start = exchange_forward(local, M, fallback, h0, group)
+    res, _ = run_forward(q, k, v, A, g_cum, beta, scale, start, ops.SeqTables(1, q.shape[1], None),
+                         output_final_state=True)
+    o, ht = res["o"], res["ht"]
+    final_state = None
+    if output_final_state:
+        final_state = ht.clone()
+        src = world - 1
+        dist.broadcast(final_state, src=dist.get_global_rank(group, src) if group else src,
+                       group=group)
+    return g_cum, A, o, final_state, (start, M)
+
+
+def bwd_tsharded(q, k, v, g_cum, beta, A, do, dht=None, scale=None, saved=None, group=None):
+    """Backward of a T-sharded sequence.  ``saved`` is the tuple returned by ``fwd_tsharded``.
+    Returns ``(dq, dk, dv, db, dg, dh0)`` for this rank's tokens; ``dh0`` (gradient of the
+    sequence's initial state) is valid on every rank."""
+    if scale is None:
+        scale = k.shape[-1] ** -0.5
+    start, M_fwd = saved
+    T = k.shape[1]
+    seg_cu = torch.tensor([0, T], dtype=torch.int32, device=k.device)
+    tables = ops.SeqTables(1, T, seg_cu)
+    warm, fallback = ops.warmup_scan(g_cum, seg_cu, cp.THRESHOLD, from_start=True)
+    local = ops.bwd_dh(q, k, A, g_cum, beta, do, scale, None, output_dh=False, output_du=False,
+                       output_dh0=True, warm_chunks=warm, tables=tables)["dh0"]
+    # the exact transition matrix of this shard is needed wherever the gradient survives it
+    M = ops.fwd_seq(None, k, v, A, g_cum, beta, scale, None, output_o=False, output_m=True,
+                    m_mask=fallback, tables=tables)["M"]
+    dht32 = None if dht is None else dht.float().contiguous()
+    end = exchange_backward(local, M, fallback, dht32, group)
+    dq, dk, dv, db, dg, dh0 = chunk_gated_delta_rule_bwd(q, k, v, g_cum, beta, A, do, end, scale,
+                                                         start, None)
+    dh0 = dh0.clone()
+    dist.broadcast(dh0, src=dist.get_global_rank(group, 0) if group else 0, group=group)
+    return dq, dk, dv, db, dg, dh0

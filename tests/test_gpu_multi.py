@@ -1,0 +1,92 @@
+"""T sharding and head sharding on two real GPUs (NCCL), against the single-GPU result of the
+same operator.  Skipped when fewer than two GPUs are visible."""
+
+import datetime
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rel(a, b):
+    a, b = a.double().cpu(), b.double().cpu()
+    return float((a - b).norm() / b.norm().clamp_min(1e-30))
+
+
+def _worker(rank, world, port, gate, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=120),
+                            device_id=torch.device("cuda", rank))
+    import flashqla_b200 as fq
+    from flashqla_b200 import distributed as fd
+    from oracle import gdr_oracle as orc
+
+    T, Hq, Hv, D = 2048, 2, 4, 128
+    x = orc.make_inputs(1, T, Hq, Hv, D, D, seed=31, gate=gate)
+    d = {n: t.cuda() for n, t in x.items()}
+    bf = {n: d[n].bfloat16() for n in ("q", "k", "v", "beta", "do")}
+    # single-GPU truth (same kernels, unsplit)
+    g_cum, A, o, _, ht, _ = fq.chunk_gated_delta_rule_fwd(
+        bf["q"], bf["k"], bf["v"], d["g"], bf["beta"], None, d["h0"], auto_cp=False)
+    ref = fq.chunk_gated_delta_rule_bwd(bf["q"], bf["k"], bf["v"], g_cum, bf["beta"], A, bf["do"],
+                                        d["dht"], None, d["h0"], auto_cp=False)
+    # T-sharded
+    per = T // world
+    sl = slice(rank * per, (rank + 1) * per)
+    loc = {n: bf[n][:, sl].contiguous() for n in bf}
+    g_loc = d["g"][:, sl].contiguous()
+    g_cum_l, A_l, o_l, ht_l, saved = fd.fwd_tsharded(loc["q"], loc["k"], loc["v"], g_loc,
+                                                     loc["beta"], None, d["h0"])
+    grads = fd.bwd_tsharded(loc["q"], loc["k"], loc["v"], g_cum_l, loc["beta"], A_l, loc["do"],
+                            d["dht"], None, saved)
+    errs = {"o": _rel(o_l, o[:, sl]), "ht": _rel(ht_l, ht)}
+    for name, got, want in zip(("dq", "dk", "dv", "db", "dg"), grads[:5], ref[:5]):
+        errs[name] = _rel(got.float(), want[:, sl].float())
+    errs["dh0"] = _rel(grads[5], ref[5])
+    # head sharding: this rank's heads of the full problem equal the slice of the full result
+    qs, ks, vs, gs, bs, hs = fd.shard_heads(bf["q"], bf["k"], bf["v"], d["g"], bf["beta"], rank,
+                                            world, d["h0"])
+    _, _, o_h, _, ht_h, _ = fq.chunk_gated_delta_rule_fwd(qs, ks, vs, gs, bs, None, hs,
+                                                          auto_cp=False)
+    hv = Hv // world
+    errs["o_heads"] = _rel(o_h, o[:, :, rank * hv:(rank + 1) * hv])
+    errs["ht_heads"] = _rel(ht_h, ht[:, rank * hv:(rank + 1) * hv])
+    out[rank] = errs
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("gate", ["logsigmoid", "weak"])
+def test_two_gpu_sharding_matches_single_gpu(gate):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world, port = 2, _free_port()
+    with mp.Manager() as mgr:
+        out = mgr.dict()
+        mp.spawn(_worker, args=(world, port, gate, out), nprocs=world, join=True)
+        for rank in range(world):
+            errs = dict(out[rank])
+            print(gate, rank, {k: f"{v:.2e}" for k, v in errs.items()})
+            # two runs that round differently: forward within 5e-3 + 5e-3, gradients 1e-2 + 1e-2
+            assert max(errs[n] for n in ("o", "ht")) < 8e-3, errs
+            assert max(errs[n] for n in ("dq", "dk", "dv", "db", "dg", "dh0")) < 1.5e-2, errs
+            assert errs["o_heads"] < 1e-6 and errs["ht_heads"] < 1e-6, errs
