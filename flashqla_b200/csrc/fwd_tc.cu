@@ -421,33 +421,25 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
       constexpr uint32_t ID_U = idesc_bf16(128, 64, 0, 0);
       constexpr uint32_t ID_VT = idesc_bf16(128, 64, 1, 0);
       constexpr uint32_t ID_S = idesc_bf16(128, 128, 0, 1);
-      // descriptors of every operand tile, built once; a byte offset is added as (off >> 4)
-      uint64_t dQ[2], dK[2], dKmn[2], dVmn[2], dA[2];
-#pragma unroll
-      for (int s = 0; s < 2; ++s) {
-        const unsigned char* st = smem + OFF_STAGE + s * STAGE_BYTES;
-        dQ[s] = desc_kmajor(st);
-        dK[s] = desc_kmajor(st + TILE_QK);
-        dKmn[s] = desc_mnmajor(st + TILE_QK, 8192);
-        dVmn[s] = desc_mnmajor(st + 2 * TILE_QK, 8192);
-        dA[s] = desc_kmajor(st + 2 * TILE_QK + TILE_V);
-      }
-      const uint64_t dST = desc_kmajor(smem + OFF_ST), dWT = desc_kmajor(smem + OFF_WT);
-      const uint64_t dVNT = desc_kmajor(smem + OFF_VNT), dVRT = desc_kmajor(smem + OFF_VRT);
-      const uint64_t dP = desc_kmajor(smem + OFF_P), dI = desc_kmajor(smem + OFF_I);
-      // K-step j of a 128-wide K-major operand stored as two 64-column blocks of `blk` bytes
-      auto kstep = [](int j, int blk) { return (uint64_t)(((j >> 2) * blk + (j & 3) * 32) >> 4); };
-      auto issue_p_vt = [&](int s) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          umma(tmem + TM_P, dQ[s] + kstep(j, 8192), dK[s] + kstep(j, 8192), ID_P, j > 0);
+      // low descriptor words of every operand tile (see umma_lo); steps are 32-bit adds
+      const uint32_t st_lo = desc_lo_kmajor(smem + OFF_ST), wt_lo = desc_lo_kmajor(smem + OFF_WT);
+      const uint32_t vnt_lo = desc_lo_kmajor(smem + OFF_VNT), vrt_lo = desc_lo_kmajor(smem + OFF_VRT);
+      const uint32_t p_lo = desc_lo_kmajor(smem + OFF_P), i_lo = desc_lo_kmajor(smem + OFF_I);
+      const uint32_t q0_lo = desc_lo_kmajor(smem + OFF_STAGE);
+      const uint32_t k0_lo = desc_lo_kmajor(smem + OFF_STAGE + TILE_QK);
+      const uint32_t a0_lo = desc_lo_kmajor(smem + OFF_STAGE + 2 * TILE_QK + TILE_V);
+      const uint32_t kmn0_lo = desc_lo_mnmajor(smem + OFF_STAGE + TILE_QK, 8192);
+      const uint32_t vmn0_lo = desc_lo_mnmajor(smem + OFF_STAGE + 2 * TILE_QK, 8192);
+      constexpr uint32_t STAGE_LO = STAGE_BYTES >> 4;
+      auto issue_p_vt = [&](uint32_t so) {  // so = stage offset in descriptor units
+        umma_group<8, 2, 512, 2, 512, false>(tmem + TM_P, q0_lo + so, k0_lo + so, ID_P);
         umma_commit(&bars[P_DONE]);
-#pragma unroll
-        for (int j = 0; j < 4; ++j)  // VT = V^T: A = V tile MN-major (16 rows per step), B = I
-          umma(tmem + TM_VT, dVmn[s] + (uint64_t)(j * 128), dI + (uint64_t)(j * 2), ID_VT, j > 0);
+        // VT = V^T: A = V tile read MN-major (16 rows per step), B = identity
+        umma_group<4, 128, 0, 2, 0, false>(tmem + TM_VT, vmn0_lo + so, i_lo, ID_VT);
       };
       for (int it = 0; it < n_it && ok; ++it) {
         const int s = it & 1;
+        const uint32_t so = s ? STAGE_LO : 0u, so_next = s ? 0u : STAGE_LO;
         ok = WAIT(FULL0 + s, (it >> 1) & 1);
         if (!ok) break;
         tc_fence_after();
@@ -457,9 +449,7 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
         tc_fence_after();
         if (p.profile) t_sec = clock64();
         // U^T = S^T K^T
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          umma(tmem + TM_UV, dST + kstep(j, 16384), dK[s] + kstep(j, 8192), ID_U, j > 0);
+        umma_group<8, 2, 1024, 2, 512, false>(tmem + TM_UV, st_lo, k0_lo + so, ID_U);
         umma_commit(&bars[U_DONE]);
         if (p.profile) waited[U_DONE] += clock64() - t_sec;
         if (it > 0) {
@@ -469,18 +459,14 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
         }
         if (p.profile) t_sec = clock64();
         // O1 = Q S      (B = S^T copy: N = v rows, K = k)
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-          umma(tmem + TM_O1, dQ[s] + kstep(j, 8192), dST + kstep(j, 16384), ID_O, j > 0);
+        umma_group<8, 2, 512, 2, 1024, false>(tmem + TM_O1, q0_lo + so, st_lo, ID_O);
         if (p.profile) waited[O_DONE] += clock64() - t_sec;
         ok = WAIT(W_READY, it & 1);
         if (!ok) break;
         tc_fence_after();
         if (p.profile) t_sec = clock64();
         // Vn^T = W^T A^T
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          umma(tmem + TM_UV, dWT + (uint64_t)(j * 2), dA[s] + (uint64_t)(j * 2), ID_U, j > 0);
+        umma_group<4, 2, 0, 2, 0, false>(tmem + TM_UV, wt_lo, a0_lo + so, ID_U);
         umma_commit(&bars[VN_DONE]);
         if (p.profile) waited[VN_DONE] += clock64() - t_sec;
         ok = WAIT(VR_READY, it & 1);
@@ -490,9 +476,7 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
         tc_fence_after();
         if (p.profile) t_sec = clock64();
         // S^T += (rho Vn)^T K      (B = K tile read MN-major: contraction over its 64 rows)
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          umma(tmem + TM_S, dVRT + (uint64_t)(j * 2), dKmn[s] + (uint64_t)(j * 128), ID_S, true);
+        umma_group<4, 2, 0, 128, 0, true>(tmem + TM_S, vrt_lo, kmn0_lo + so, ID_S);
         umma_commit(&bars[S_DONE]);
         if (p.profile) waited[S_DONE] += clock64() - t_sec;
         ok = WAIT(P_READY, it & 1);
@@ -500,9 +484,7 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
         tc_fence_after();
         if (p.profile) t_sec = clock64();
         // O2 = Pg Vn     (B = Vn^T copy: N = v rows, K = tok')
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          umma(tmem + TM_O2, dP + (uint64_t)(j * 2), dVNT + (uint64_t)(j * 2), ID_O, j > 0);
+        umma_group<4, 2, 0, 2, 0, false>(tmem + TM_O2, p_lo, vnt_lo, ID_O);
         umma_commit(&bars[O_DONE]);
         umma_commit(&bars[EMPTY0 + s]);
         if (p.profile) waited[EMPTY0] += clock64() - t_sec;
@@ -511,7 +493,7 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
           if (!ok) break;
           tc_fence_after();
           if (p.profile) t_sec = clock64();
-          issue_p_vt(s ^ 1);
+          issue_p_vt(so_next);
           if (p.profile) waited[P_DONE] += clock64() - t_sec;
         }
       }

@@ -59,7 +59,7 @@ __global__ void __launch_bounds__(128) cumsum_kernel(const float* __restrict__ g
 // ------------------------------------------------------------------------------------------
 // kkt + solve.  One CTA (128 threads) per (chunk, value head).
 //   1. K K^T (64x64xD) on tensor cores, 2. L = strict_lower(beta_s * KK^T * exp(g_s-g_t)) in fp32,
-//   3. X = (I+L)^-1 by forward substitution, thread c owning column c, 4. bf16 rows out.
+//   3. X = (I+L)^-1 by blocked forward substitution in fp32, 4. bf16 rows out.
 // ------------------------------------------------------------------------------------------
 template <int D>
 __global__ void __launch_bounds__(128) kkt_solve_kernel(
@@ -73,6 +73,8 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(
   float* sL = reinterpret_cast<float*>(smem_raw + CHUNK * LDK * sizeof(bf16));
   float* sG = sL + CHUNK * LDL;
   float* sB = sG + CHUNK;
+  float* sX = sB + CHUNK;         // [64][LDL] the inverse
+  float* sY = sX + CHUNK * LDL;   // up to 3 blocks of 16 x 16 partial products
 
   int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   int hv = blockIdx.y, hq = hv / (Hv / Hq);
@@ -115,34 +117,56 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(
     }
   __syncthreads();
 
-  // Forward substitution: x_i = e_i - sum_{j<i} L[i][j] x_j, column c in thread c's registers.
+  // Blocked inverse of the unit lower-triangular (I + L), 4 x 4 blocks of 16 x 16, fp32:
+  //   diagonal blocks by forward substitution (thread = one column of one block), then the
+  //   blocks at distance d = 1, 2, 3 below the diagonal:
+  //   X_ij = -X_ii * sum_{k=j}^{i-1} L_ik X_kj.
   if (tid < CHUNK) {
-    float x[CHUNK];
+    const int b0 = (tid >> 4) * 16, c = tid & 15;
+    float x[16];
 #pragma unroll
-    for (int i = 0; i < CHUNK; ++i) {
-      float s = (i == tid) ? 1.f : 0.f;
+    for (int i = 0; i < 16; ++i) {
+      float s = (i == c) ? 1.f : 0.f;
 #pragma unroll
-      for (int j4 = 0; j4 < (i + 3) / 4; ++j4) {
-        float4 l = *reinterpret_cast<const float4*>(&sL[i * LDL + j4 * 4]);
-        if (j4 * 4 + 0 < i) s -= l.x * x[j4 * 4 + 0];
-        if (j4 * 4 + 1 < i) s -= l.y * x[j4 * 4 + 1];
-        if (j4 * 4 + 2 < i) s -= l.z * x[j4 * 4 + 2];
-        if (j4 * 4 + 3 < i) s -= l.w * x[j4 * 4 + 3];
-      }
+      for (int jj = 0; jj < i; ++jj) s -= sL[(b0 + i) * LDL + b0 + jj] * x[jj];
       x[i] = s;
+      sX[(b0 + i) * LDL + b0 + c] = s;
     }
-    __syncwarp();
-    // stage as bf16 rows in the (now dead) K tile: sK[i][c]
-#pragma unroll
-    for (int i = 0; i < CHUNK; ++i) sK[i * LDK + tid] = __float2bfloat16(x[i]);
   }
   __syncthreads();
-  // coalesced row stores: 64 rows x 128 bytes
+  for (int d = 1; d < 4; ++d) {
+    const int n_out = (4 - d) * 256;
+    for (int o = tid; o < n_out; o += 128) {
+      const int b = o >> 8, r = (o >> 4) & 15, c = o & 15, bi = (b + d) * 16, bj = b * 16;
+      float acc = 0.f;
+      for (int kk = bj; kk < bi; kk += 16) {
+#pragma unroll
+        for (int t = 0; t < 16; ++t) acc += sL[(bi + r) * LDL + kk + t] * sX[(kk + t) * LDL + bj + c];
+      }
+      sY[o] = acc;
+    }
+    __syncthreads();
+    for (int o = tid; o < n_out; o += 128) {
+      const int b = o >> 8, r = (o >> 4) & 15, c = o & 15, bi = (b + d) * 16, bj = b * 16;
+      float acc = 0.f;
+#pragma unroll
+      for (int t = 0; t < 16; ++t) acc += sX[(bi + r) * LDL + bi + t] * sY[(b << 8) + t * 16 + c];
+      sX[(bi + r) * LDL + bj + c] = -acc;
+    }
+    __syncthreads();
+  }
+  // bf16 rows out, 16 bytes per store; blocks above the diagonal are zero
   for (int i = tid; i < CHUNK * 8; i += 128) {
-    int r = i >> 3, c = (i & 7) * 8;
-    if (r < valid)
-      *reinterpret_cast<uint4*>(A + ((row0 + r) * Hv + hv) * CHUNK + c) =
-          *reinterpret_cast<const uint4*>(sK + r * LDK + c);
+    const int r = i >> 3, c0 = (i & 7) * 8;
+    if (r < valid) {
+      uint4 pk = make_uint4(0, 0, 0, 0);
+      if ((c0 >> 4) <= (r >> 4)) {
+        const float* xr = sX + r * LDL + c0;
+        pk = make_uint4(pack_bf16(xr[0], xr[1]), pack_bf16(xr[2], xr[3]), pack_bf16(xr[4], xr[5]),
+                        pack_bf16(xr[6], xr[7]));
+      }
+      *reinterpret_cast<uint4*>(A + ((row0 + r) * Hv + hv) * CHUNK + c0) = pk;
+    }
   }
 }
 
@@ -197,7 +221,7 @@ template <int D>
 static int launch_kkt(const void* k, const void* beta, int beta_is_f32, const float* g, void* A,
                       int Hq, int Hv, SeqLayout lay, IndexTable ci, long long n,
                       cudaStream_t st) {
-  constexpr int smem = CHUNK * (D + 8) * 2 + CHUNK * (CHUNK + 4) * 4 + 2 * CHUNK * 4;
+  constexpr int smem = CHUNK * (D + 8) * 2 + 2 * CHUNK * (CHUNK + 4) * 4 + 2 * CHUNK * 4 + 768 * 4;
   int rc = configure_smem((const void*)kkt_solve_kernel<D>, smem);
   if (rc != 0) return rc;
   kkt_solve_kernel<D><<<dim3((unsigned)n, Hv), 128, smem, st>>>(

@@ -186,6 +186,53 @@ __device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a_desc, uint64_t 
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(acc)
       : "memory");
 }
+// Lean issue form.  Every descriptor of an SW128 tile has the same high word (SBO = 1024,
+// version 1, 128-byte swizzle); the low word is (address >> 4) | (LBO >> 4) << 16, so a K step
+// is one 32-bit add on a per-tile base kept in a register.  Few, mutually independent
+// instructions per MMA matter: the issuing thread shares its scheduler with three busy warps
+// and pays a scheduling delay for every dependent instruction.
+constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t desc_lo_kmajor(const void* tile) {
+  return ((s32(tile) >> 4) & 0x3FFF) | (1u << 16);
+}
+__device__ __forceinline__ uint32_t desc_lo_mnmajor(const void* tile, uint32_t block_stride_bytes) {
+  return ((s32(tile) >> 4) & 0x3FFF) | ((block_stride_bytes >> 4) << 16);
+}
+template <bool ACCUMULATE>
+__device__ __forceinline__ void umma_lo(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo,
+                                        uint32_t idesc) {
+  if (ACCUMULATE) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, 1, 0;\n\t"
+        "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_lo), "r"(b_lo), "r"(DESC_HI), "r"(idesc)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, 0, 0;\n\t"
+        "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_lo), "r"(b_lo), "r"(DESC_HI), "r"(idesc)
+        : "memory");
+  }
+}
+// One product: NK K-steps; operand low words advance by A_STEP / B_STEP (units of 16 bytes) per
+// step, plus A_BLK / B_BLK after every fourth step (next 64-column block of a K-major operand).
+template <int NK, int A_STEP, int A_BLK, int B_STEP, int B_BLK, bool ACC_FIRST>
+__device__ __forceinline__ void umma_group(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo,
+                                           uint32_t idesc) {
+#pragma unroll
+  for (int j = 0; j < NK; ++j) {
+    const uint32_t a = a_lo + (uint32_t)((j & 3) * A_STEP + (j >> 2) * A_BLK);
+    const uint32_t b = b_lo + (uint32_t)((j & 3) * B_STEP + (j >> 2) * B_BLK);
+    if (j == 0 && !ACC_FIRST) umma_lo<false>(d_tmem, a, b, idesc);
+    else umma_lo<true>(d_tmem, a, b, idesc);
+  }
+}
+
 // mbarrier arrives (count 1) once every tcgen05.mma issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
