@@ -2,27 +2,34 @@
 // TMA-fed tcgen05.mma with all accumulators in tensor memory, warp-specialised.
 //
 // One CTA (512 threads) walks the chunks of one (sequence or segment, value head), K = V = 128.
+// Per chunk, with S [K x V] the fp32 state entering the chunk, A the gated inverse from
+// kkt_solve, g the chunk-local cumulative log gate (gamma = exp g, rho = exp(g_last - g)):
+//
+//   off the serial chain, prepared one chunk ahead (WY form, FLA's w and u):
+//     A'  = A diag(beta),  A'' = A diag(beta gamma)                               (prep warps)
+//     u^T [v x tok] = V^T A'^T          (A operand = V tile read MN-major)        -> TM_UV
+//     w   [tok x k] = A'' K             (B operand = K tile read MN-major)        -> TM_W -> smem
+//     P   [tok x tok'] = Q K^T,  Pg = s P exp(g_tok - g_tok') for tok >= tok'     (O group)
+//   on the chain (two products):
+//     Vn^T [v x tok] = u^T - S^T w^T    (A = bf16 copy of S^T, negated; accumulates onto u^T)
+//     S^T  [v x k]   = gamma_last S^T + (rho Vn)^T K     (B = K tile read MN-major)
+//   output:
+//     O [tok x v] = s gamma_tok (Q S) + Pg Vn      (two M = 64 accumulators, one thread per row)
+//
 // The state path is kept TRANSPOSED so that the 128-wide value dimension sits on the MMA M axis
-// (tensor-memory lane = value index v, one thread per lane); the output path is not (M = 64 rows
-// = tokens, so that a thread owns one contiguous output row):
-//     VT   [v x tok]    = V^T            (A = V tile read MN-major, B = identity: a transpose)
-//     U^T  [v x tok]    = S^T K^T        (A = bf16 copy of S^T, B = K tile)
-//     W^T               = beta_tok VT - (beta gamma)_tok U^T                 (V group)
-//     Vn^T [v x tok]    = W^T A^T        (B = A tile)
-//     S^T  [v x k]      = gamma_last S^T + (rho Vn)^T K        (B = K tile read MN-major)
-//     P    [tok x tok'] = Q K^T,  Pg = s P exp(g_tok - g_tok') for tok >= tok'      (O group)
-//     O    [tok x v]    = s gamma_tok (Q S) + Pg Vn            (two M = 64 accumulators)
-// which is the algebra of the reference's blackwell/fused_fwd.py:349-596 with the gate folded
-// into A (see kkt_solve).
+// (tensor-memory lane = value index, one thread per lane).  This is the algebra of the
+// reference's blackwell/fused_fwd.py:349-596 (and the X/Y form of prepare_h.py:312-318) with the
+// gate folded into A.
 //
 // Warp roles (thread ranges):
-//     0-127   S group : fp32 master state in tensor memory; per chunk writes the bf16 operand copy
-//                       of S^T to shared memory, decays S^T in place, emits h / the final state
-//     128-255 V group : U^T, VT -> W^T;  Vn^T -> Vn^T and rho-scaled copies (MMA operands)
-//     256-383 O group : P -> Pg (operand); output epilogue o = s gamma O1 + O2, 16-byte stores
-//     warp 12 : issues every tcgen05.mma (one elected lane), descriptors precomputed
-//     warp 13 : producer: per-chunk gate vectors (fetched one chunk ahead), TMA loads of the
+//     128-255 S group : fp32 master state in tensor memory; per chunk writes the bf16 operand copy
+//                       of S^T to shared memory (on the chain), then decays S^T in place
+//     256-383 V group : Vn^T -> rho-scaled and plain bf16 operand copies; w -> bf16 operand tile
+//     384-511 O group : P -> Pg (operand); output epilogue o = s gamma O1 + O2
+//     warp 0  : issues every tcgen05.mma (one elected lane)
+//     warp 1  : producer: per-chunk gate vectors (fetched one chunk ahead), TMA loads of the
 //               q, k, v, A tiles (2 stages), zero-fill of rows past the end of a partial chunk
+//     64-127  prep    : one thread per chunk row: A' and A'' tiles
 // Synchronisation is by mbarriers only; every wait is bounded and reports through a status word.
 #include <cuda.h>
 
@@ -39,8 +46,8 @@ using namespace tc;
 // 0 = ok; 1 after some kernel abandoned a bounded wait (its outputs are then invalid)
 __device__ int g_device_status = 0;
 // Diagnostics (FQLA_PROFILE=1): cycles the first CTA's role leaders spent per barrier wait and
-// per section, [role 0..4][slot 0..15], plus [5][0] = total cycles of the CTA.
-__device__ long long g_wait_profile[6 * 16];
+// per section, [role 0..5][slot 0..23], plus [6][0] = total cycles of the CTA.
+__device__ long long g_wait_profile[7 * 24];
 
 struct FwdTcParams {
   const float* g;
@@ -64,28 +71,39 @@ constexpr int TILE_QK = 16384, TILE_V = 16384, TILE_A = 8192;
 constexpr int STAGE_BYTES = 2 * TILE_QK + TILE_V + TILE_A;  // 57344
 constexpr int OFF_STAGE = 0;
 constexpr int OFF_ST = 2 * STAGE_BYTES;          // S^T copy, 2 blocks of [128 x 128B]
-constexpr int OFF_WT = OFF_ST + 32768;           // W^T   [128 x 128B]
-constexpr int OFF_VNT = OFF_WT + 16384;          // Vn^T
-constexpr int OFF_VRT = OFF_VNT + 16384;         // rho * Vn^T
-constexpr int OFF_P = OFF_VRT + 16384;           // Pg    [64 x 128B]
-constexpr int OFF_I = OFF_P + 8192;              // identity [64 x 128B]
-constexpr int OFF_VEC = OFF_I + 8192;            // 4 slots x 6 vectors x 64 floats
+constexpr int OFF_VNT = OFF_ST + 32768;          // Vn^T  [128 x 128B]
+constexpr int OFF_W = OFF_VNT + 16384;           // w     2 blocks of [64 x 128B]
+constexpr int OFF_VRT = OFF_W + 16384;           // rho-scaled Vn^T [128 x 128B]
+constexpr int OFF_P = OFF_VRT + 16384;            // Pg    [64 x 128B]
+constexpr int OFF_AP = OFF_P + 8192;             // A diag(beta)
+constexpr int OFF_APP = OFF_AP + 8192;           // A diag(beta gamma)
+constexpr int OFF_VEC = OFF_APP + 8192;          // 4 slots x 6 vectors x 64 floats
 constexpr int VEC_SLOT_FLOATS = 6 * CHUNK;
 constexpr int OFF_BAR = OFF_VEC + 4 * VEC_SLOT_FLOATS * 4;
-constexpr int N_BARS = 20;
+constexpr int N_BARS = 24;
 constexpr int OFF_MISC = OFF_BAR + N_BARS * 8;
 constexpr int SMEM_BYTES = OFF_MISC + 16 + 1024;  // + slack for 1024-byte alignment of the base
-// tensor-memory columns.  P shares the columns of O1 in the upper half-lanes: an M = 64
-// accumulator only occupies lanes 0-15 of each 32-lane quarter, a second one fits at lane +16.
-constexpr uint32_t TM_S = 0, TM_UV = 128, TM_VT = 192, TM_O1 = 256, TM_O2 = 384;
-constexpr uint32_t TM_P = TM_O1 + (16u << 16);
+// tensor-memory columns.  An M = 64 accumulator only occupies lanes 0-15 of each 32-lane
+// quarter, so a second one fits at lane +16 of the same columns: P under O1, w under O2.
+constexpr uint32_t TM_S = 0, TM_UV = 128, TM_O1 = 256, TM_O2 = 384;
+constexpr uint32_t TM_P = TM_O1 + (16u << 16), TM_W = TM_O2 + (16u << 16);
 // barrier indices
-enum { FULL0 = 0, FULL1, EMPTY0, EMPTY1, S_COPY, S_DEC, U_DONE, VN_DONE, S_DONE, P_DONE, O_DONE,
-       W_READY, VR_READY, P_READY, O_FREE, PRIV };
+enum { FULL0 = 0, FULL1, EMPTY0, EMPTY1, S_COPY, S_DEC, VN_DONE, S_DONE, P_DONE, O_DONE, W_DONE,
+       VN_READY, W_READY, P_READY, O_FREE, AP_READY, VR_READY, PRIV,
+       SEC_A = 18, SEC_B, SEC_C, SEC_D, SEC_E, SEC_F };  // SEC_*: profiling slots only
 // vectors inside a slot; V_GL holds gamma_last at [0]
 enum { V_G = 0, V_BETA = 1, V_BG = 2, V_RHO = 3, V_SGAM = 4, V_GL = 5 };
 }  // namespace fwdtc
 
+__device__ __forceinline__ uint32_t scale_bf16x2(uint32_t packed, float lo, float hi) {
+  float2 f = __bfloat1622float2(*reinterpret_cast<const bf162*>(&packed));
+  return pack_bf16(f.x * lo, f.y * hi);
+}
+
+// PROFILE: wait/section cycle counters (diagnostics).  EXTRA: per-chunk state and v_new outputs.
+// Both are compiled out of the common instantiation: the six roles run six different code
+// regions at once, and the kernel is sensitive to its instruction-cache footprint.
+template <bool PROFILE, bool EXTRA>
 __global__ void __launch_bounds__(512, 1)
 fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
               const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
@@ -108,19 +126,21 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
   if (tid == 0) {
     mbar_init(&bars[FULL0], 1);
     mbar_init(&bars[FULL1], 1);
-    mbar_init(&bars[EMPTY0], 1);  // the MMA commit: tiles are read by tensor-core operations only
-    mbar_init(&bars[EMPTY1], 1);
+    mbar_init(&bars[EMPTY0], 1 + 2);  // MMA commit + the two prep warps (they read the A tile)
+    mbar_init(&bars[EMPTY1], 1 + 2);
     mbar_init(&bars[S_COPY], 128);
     mbar_init(&bars[S_DEC], 128);
-    mbar_init(&bars[U_DONE], 1);
     mbar_init(&bars[VN_DONE], 1);
     mbar_init(&bars[S_DONE], 1);
     mbar_init(&bars[P_DONE], 1);
     mbar_init(&bars[O_DONE], 1);
+    mbar_init(&bars[W_DONE], 1);
+    mbar_init(&bars[VN_READY], 128);
     mbar_init(&bars[W_READY], 128);
-    mbar_init(&bars[VR_READY], 128);
     mbar_init(&bars[P_READY], 128);
     mbar_init(&bars[O_FREE], 128);
+    mbar_init(&bars[AP_READY], 2);
+    mbar_init(&bars[VR_READY], 128);
     mbar_init(&bars[PRIV], 1);
     *abort_flag = 0;
     fence_mbar_init();
@@ -129,18 +149,7 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
     tma_prefetch_desc(&map_v);
     tma_prefetch_desc(&map_a);
   }
-  // identity tile (B operand of the V transpose), written once
-  for (int i = tid; i < CHUNK * 8; i += 512) {
-    int r = i >> 3, ch = i & 7;
-    uint4 z = make_uint4(0, 0, 0, 0);
-    if (ch == (r >> 3)) {
-      uint32_t one = (r & 1) ? 0x3F800000u : 0x00003F80u;  // bf16 1.0 in the high / low half
-      (&z.x)[(r & 7) >> 1] = one;
-    }
-    *reinterpret_cast<uint4*>(smem + OFF_I + r * 128 + ((ch ^ (r & 7)) << 4)) = z;
-  }
-  fence_proxy_async();
-  if (warp == 12) tmem_alloc(tmem_slot, 512);
+  if (warp == 0) tmem_alloc(tmem_slot, 512);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -148,23 +157,32 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
   const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;  // this warp's lane quarter
   const long long state_off = ((long long)n * p.Hv + hv) * D * D;
   bool ok = true;
-  long long waited[16];
+  long long waited[24];
 #pragma unroll
-  for (int i = 0; i < 16; ++i) waited[i] = 0;
+  for (int i = 0; i < 24; ++i) waited[i] = 0;
   const long long t_start = clock64();
   long long t_sec = 0;
   auto WAIT = [&](int idx, uint32_t parity) {
-    if (!p.profile) return mbar_wait(&bars[idx], parity, abort_flag);
-    long long t0 = clock64();
-    bool r = mbar_wait(&bars[idx], parity, abort_flag);
-    waited[idx] += clock64() - t0;
-    return r;
+    if constexpr (!PROFILE) {
+      return mbar_wait(&bars[idx], parity, abort_flag);
+    } else {
+      long long t0 = clock64();
+      bool r = mbar_wait(&bars[idx], parity, abort_flag);
+      waited[idx] += clock64() - t0;
+      return r;
+    }
   };
+#define SEC_BEGIN() do { if constexpr (PROFILE) t_sec = clock64(); } while (0)
+#define SEC_END(slot) do { if constexpr (PROFILE) waited[slot] += clock64() - t_sec; } while (0)
 
-  if (warp < 4) {
+  // Role of each warp.  The MMA issuer is warp 0 and the producer warp 1 on purpose: among the
+  // warps of one scheduler the oldest (lowest id) wins when several are ready, and these two
+  // single-thread roles must never queue behind the arithmetic of the compute groups.
+  if (warp >= 4 && warp < 8) {
     // =============================== S group ===============================
-    const int v = tid;  // lane of tensor memory = value index
+    const int v = tid - 128;  // lane of tensor memory = value index
     // initial state -> tensor memory (S^T[v][k] = h0[k][v])
+#pragma unroll 1
     for (int k0 = 0; k0 < D; k0 += 32) {
       float x[32];
 #pragma unroll
@@ -177,13 +195,11 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
       const int s = it & 1;
       if (it > 0) ok = WAIT(S_DONE, (it - 1) & 1);
       if (!ok) break;
-      ok = WAIT(FULL0 + s, (it >> 1) & 1);
-      if (!ok) break;
       tc_fence_after();
-      if (p.profile) t_sec = clock64();
-      const float gl = vec[(it & 3) * VEC_SLOT_FLOATS + V_GL * CHUNK];
-      bf16* hdst = p.h ? p.h + ((sp.chunk_base + it) * p.Hv + hv) * (long long)D * D : nullptr;
-#pragma unroll
+      SEC_BEGIN();
+      bf16* hdst = (EXTRA && p.h) ? p.h + ((sp.chunk_base + it) * p.Hv + hv) * (long long)D * D : nullptr;
+      // on the chain: the bf16 operand copy of S^T
+#pragma unroll 1
       for (int kb = 0; kb < 2; ++kb) {  // 64 columns (one operand block) per round
         float x[32], y[32];
         tmem_ld32(tmem + lane_sel + TM_S + kb * 64, x);
@@ -199,13 +215,29 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
               make_uint4(pack_bf16(y[8 * c + 0], y[8 * c + 1]), pack_bf16(y[8 * c + 2], y[8 * c + 3]),
                          pack_bf16(y[8 * c + 4], y[8 * c + 5]), pack_bf16(y[8 * c + 6], y[8 * c + 7]));
         }
-        if (hdst) {
+        if (EXTRA && hdst) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             hdst[(long long)(kb * 64 + j) * D + v] = __float2bfloat16(x[j]);
             hdst[(long long)(kb * 64 + 32 + j) * D + v] = __float2bfloat16(y[j]);
           }
         }
+      }
+      fence_proxy_async();
+      tc_fence_before();
+      mbar_arrive(&bars[S_COPY]);
+      SEC_END(SEC_A);
+      // off the chain: decay in place, needed only by the state update at the end of the chunk
+      ok = WAIT(FULL0 + s, (it >> 1) & 1);
+      if (!ok) break;
+      SEC_BEGIN();
+      const float gl = vec[(it & 3) * VEC_SLOT_FLOATS + V_GL * CHUNK];
+#pragma unroll 1
+      for (int kb = 0; kb < 2; ++kb) {
+        float x[32], y[32];
+        tmem_ld32(tmem + lane_sel + TM_S + kb * 64, x);
+        tmem_ld32(tmem + lane_sel + TM_S + kb * 64 + 32, y);
+        tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < 32; ++j) {
           x[j] *= gl;
@@ -214,16 +246,15 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
         tmem_st32(tmem + lane_sel + TM_S + kb * 64, x);
         tmem_st32(tmem + lane_sel + TM_S + kb * 64 + 32, y);
       }
-      fence_proxy_async();
-      mbar_arrive(&bars[S_COPY]);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&bars[S_DEC]);
-      if (p.profile) waited[S_COPY] += clock64() - t_sec;
+      SEC_END(SEC_B);
     }
     if (ok && n_it > 0) ok = WAIT(S_DONE, (n_it - 1) & 1);
     if (ok && p.ht) {
       tc_fence_after();
+#pragma unroll 1
       for (int k0 = 0; k0 < D; k0 += 32) {
         float x[32];
         tmem_ld32(tmem + lane_sel + TM_S + k0, x);
@@ -232,120 +263,131 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
         for (int j = 0; j < 32; ++j) p.ht[state_off + (long long)(k0 + j) * D + v] = x[j];
       }
     }
-  } else if (warp < 8) {
+  } else if (warp >= 8 && warp < 12) {
     // =============================== V group ===============================
-    const int v = tid - 128;
-    for (int it = 0; it < n_it && ok; ++it) {
-      const int s = it & 1;
-      const float* vs = vec + (it & 3) * VEC_SLOT_FLOATS;
-      const long long row0 = sp.bos + (long long)it * CHUNK;
-      const int valid = min(CHUNK, sp.len - it * CHUNK);
-      ok = WAIT(FULL0 + s, (it >> 1) & 1);
-      if (!ok) break;
-      ok = WAIT(U_DONE, it & 1);
-      if (!ok) break;
+    const int v = tid - 256;
+    const int wq = warp & 3;
+    const int tok_w = 16 * wq + (lane & 15);  // lanes 16-31 of each quarter hold a row of w
+    // w of chunk `it` (tensor memory, M = 64 layout at lane +16) -> bf16 operand tile
+    auto convert_w = [&](int it) {
+      if (!WAIT(W_DONE, it & 1)) return false;
       tc_fence_after();
-      if (p.profile) t_sec = clock64();
-#pragma unroll
-      for (int t0 = 0; t0 < CHUNK; t0 += 32) {
-        float u[32], vt[32];
-        long long t_l = p.profile ? clock64() : 0;
-        tmem_ld32(tmem + lane_sel + TM_UV + t0, u);
-        tmem_ld32(tmem + lane_sel + TM_VT + t0, vt);
+      SEC_BEGIN();
+#pragma unroll 1
+      for (int c0 = 0; c0 < D; c0 += 32) {
+        float x[32];
+        tmem_ld32(tmem + lane_sel + TM_O2 + c0, x);
         tmem_ld_wait();
-        if (p.profile) waited[P_DONE] += clock64() - t_l;
-        unsigned char* row = smem + OFF_WT + v * 128;
-        const float4* b4 = reinterpret_cast<const float4*>(vs + V_BETA * CHUNK + t0);
-        const float4* g4 = reinterpret_cast<const float4*>(vs + V_BG * CHUNK + t0);
+        if (lane >= 16) {
+          unsigned char* row = smem + OFF_W + (c0 >> 6) * 8192 + tok_w * 128;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          float4 b0 = b4[2 * c], b1 = b4[2 * c + 1], g0 = g4[2 * c], g1 = g4[2 * c + 1];
-          const float* uu = u + 8 * c;
-          const float* vv = vt + 8 * c;
-          uint4 w;
-          w.x = pack_bf16(b0.x * vv[0] - g0.x * uu[0], b0.y * vv[1] - g0.y * uu[1]);
-          w.y = pack_bf16(b0.z * vv[2] - g0.z * uu[2], b0.w * vv[3] - g0.w * uu[3]);
-          w.z = pack_bf16(b1.x * vv[4] - g1.x * uu[4], b1.y * vv[5] - g1.y * uu[5]);
-          w.w = pack_bf16(b1.z * vv[6] - g1.z * uu[6], b1.w * vv[7] - g1.w * uu[7]);
-          *reinterpret_cast<uint4*>(row + ((((t0 >> 3) + c) ^ (v & 7)) << 4)) = w;
+          for (int c = 0; c < 4; ++c)
+            *reinterpret_cast<uint4*>(row + (((((c0 & 63) >> 3) + c) ^ (tok_w & 7)) << 4)) =
+                make_uint4(pack_bf16(x[8 * c + 0], x[8 * c + 1]), pack_bf16(x[8 * c + 2], x[8 * c + 3]),
+                           pack_bf16(x[8 * c + 4], x[8 * c + 5]), pack_bf16(x[8 * c + 6], x[8 * c + 7]));
         }
       }
       fence_proxy_async();
       tc_fence_before();
       mbar_arrive(&bars[W_READY]);
-      if (p.profile) waited[S_COPY] += clock64() - t_sec;
-      ok = WAIT(VN_DONE, it & 1);
+      SEC_END(SEC_B);
+      return true;
+    };
+    if (n_it > 0) ok = convert_w(0);
+    for (int it = 0; it < n_it && ok; ++it) {
+      const long long row0 = sp.bos + (long long)it * CHUNK;
+      const int valid = min(CHUNK, sp.len - it * CHUNK);
+      ok = WAIT(FULL0 + (it & 1), (it >> 1) & 1) && WAIT(VN_DONE, it & 1);
       if (!ok) break;
       tc_fence_after();
-      if (p.profile) t_sec = clock64();
-#pragma unroll
-      for (int t0 = 0; t0 < CHUNK; t0 += 32) {
-        float x[32];
-        long long t_l = p.profile ? clock64() : 0;
-        tmem_ld32(tmem + lane_sel + TM_UV + t0, x);
+      SEC_BEGIN();
+      {
+        float x[32], y[32];
+        tmem_ld32(tmem + lane_sel + TM_UV, x);
+        tmem_ld32(tmem + lane_sel + TM_UV + 32, y);
         tmem_ld_wait();
-        if (p.profile) waited[O_DONE] += clock64() - t_l;
-        unsigned char* rown = smem + OFF_VNT + v * 128;
+        // first the rho-scaled copy (operand of the state update, on the chain) ...
+        const float* rho = vec + (it & 3) * VEC_SLOT_FLOATS + V_RHO * CHUNK;
         unsigned char* rowr = smem + OFF_VRT + v * 128;
-        const float4* r4 = reinterpret_cast<const float4*>(vs + V_RHO * CHUNK + t0);
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-          float4 r0 = r4[2 * c], r1 = r4[2 * c + 1];
-          const float* xx = x + 8 * c;
-          int sw = (((t0 >> 3) + c) ^ (v & 7)) << 4;
-          *reinterpret_cast<uint4*>(rown + sw) =
-              make_uint4(pack_bf16(xx[0], xx[1]), pack_bf16(xx[2], xx[3]), pack_bf16(xx[4], xx[5]),
-                         pack_bf16(xx[6], xx[7]));
-          *reinterpret_cast<uint4*>(rowr + sw) =
-              make_uint4(pack_bf16(r0.x * xx[0], r0.y * xx[1]), pack_bf16(r0.z * xx[2], r0.w * xx[3]),
-                         pack_bf16(r1.x * xx[4], r1.y * xx[5]), pack_bf16(r1.z * xx[6], r1.w * xx[7]));
+          const float4 r0 = *reinterpret_cast<const float4*>(rho + 8 * c);
+          const float4 r1 = *reinterpret_cast<const float4*>(rho + 8 * c + 4);
+          const float4 r2 = *reinterpret_cast<const float4*>(rho + 32 + 8 * c);
+          const float4 r3 = *reinterpret_cast<const float4*>(rho + 32 + 8 * c + 4);
+          *reinterpret_cast<uint4*>(rowr + ((c ^ (v & 7)) << 4)) = make_uint4(
+              pack_bf16(r0.x * x[8 * c + 0], r0.y * x[8 * c + 1]),
+              pack_bf16(r0.z * x[8 * c + 2], r0.w * x[8 * c + 3]),
+              pack_bf16(r1.x * x[8 * c + 4], r1.y * x[8 * c + 5]),
+              pack_bf16(r1.z * x[8 * c + 6], r1.w * x[8 * c + 7]));
+          *reinterpret_cast<uint4*>(rowr + (((c + 4) ^ (v & 7)) << 4)) = make_uint4(
+              pack_bf16(r2.x * y[8 * c + 0], r2.y * y[8 * c + 1]),
+              pack_bf16(r2.z * y[8 * c + 2], r2.w * y[8 * c + 3]),
+              pack_bf16(r3.x * y[8 * c + 4], r3.y * y[8 * c + 5]),
+              pack_bf16(r3.z * y[8 * c + 6], r3.w * y[8 * c + 7]));
         }
-        if (p.vnew) {
+        fence_proxy_async();
+        tc_fence_before();
+        mbar_arrive(&bars[VR_READY]);
+        SEC_END(SEC_A);
+        // ... then the plain copy (operand of the output product)
+        unsigned char* row = smem + OFF_VNT + v * 128;
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (t0 + j < valid)
-              p.vnew[((row0 + t0 + j) * p.Hv + hv) * D + v] = __float2bfloat16(x[j]);
+        for (int c = 0; c < 4; ++c) {
+          *reinterpret_cast<uint4*>(row + ((c ^ (v & 7)) << 4)) =
+              make_uint4(pack_bf16(x[8 * c + 0], x[8 * c + 1]), pack_bf16(x[8 * c + 2], x[8 * c + 3]),
+                         pack_bf16(x[8 * c + 4], x[8 * c + 5]), pack_bf16(x[8 * c + 6], x[8 * c + 7]));
+          *reinterpret_cast<uint4*>(row + (((c + 4) ^ (v & 7)) << 4)) =
+              make_uint4(pack_bf16(y[8 * c + 0], y[8 * c + 1]), pack_bf16(y[8 * c + 2], y[8 * c + 3]),
+                         pack_bf16(y[8 * c + 4], y[8 * c + 5]), pack_bf16(y[8 * c + 6], y[8 * c + 7]));
+        }
+        fence_proxy_async();
+        mbar_arrive(&bars[VN_READY]);
+        if (EXTRA && p.vnew) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (j < valid) p.vnew[((row0 + j) * p.Hv + hv) * D + v] = __float2bfloat16(x[j]);
+            if (32 + j < valid)
+              p.vnew[((row0 + 32 + j) * p.Hv + hv) * D + v] = __float2bfloat16(y[j]);
+          }
         }
       }
-      long long t_f = p.profile ? clock64() : 0;
-      fence_proxy_async();
-      tc_fence_before();
-      mbar_arrive(&bars[VR_READY]);
-      if (p.profile) waited[S_DEC] += clock64() - t_sec;
-      if (p.profile) waited[P_READY] += clock64() - t_f;
+      if (it + 1 < n_it) ok = convert_w(it + 1);
     }
-  } else if (warp < 12) {
+  } else if (warp >= 12) {
     // =============================== O group ===============================
+    // M = 64 accumulators are read with the 16-lane shape: lane l of warp q owns rows
+    // 16q + l/4 and 16q + l/4 + 8, and in every group of 8 columns the pair 2*(l%4), +1.
     const int wq = warp & 3;
-    const int tok_o = 16 * wq + (lane & 15);  // lanes 0-15: a row of O;  lanes 16-31: a row of P
+    const int row_a = 16 * wq + (lane >> 2), row_b = row_a + 8, cp = 2 * (lane & 3);
+    const uint32_t lanes_o = (uint32_t)(wq * 32) << 16;        // O1 / O2: lanes 0-15 of the quarter
+    const uint32_t lanes_p = (uint32_t)(wq * 32 + 16) << 16;   // P: lanes 16-31
     auto epilogue = [&](int it) {
       const float* vs = vec + (it & 3) * VEC_SLOT_FLOATS;
       const long long row0 = sp.bos + (long long)it * CHUNK;
       const int valid = min(CHUNK, sp.len - it * CHUNK);
-      const float sg = vs[V_SGAM * CHUNK + tok_o];
-      bf16* orow = p.o ? p.o + ((row0 + tok_o) * p.Hv + hv) * D : nullptr;
-      const bool write = lane < 16 && tok_o < valid && orow != nullptr;
-#pragma unroll
-      for (int c0 = 0; c0 < D; c0 += 32) {
+      const float sg_a = vs[V_SGAM * CHUNK + row_a], sg_b = vs[V_SGAM * CHUNK + row_b];
+      bf16* o_a = p.o + ((row0 + row_a) * p.Hv + hv) * D + cp;
+      bf16* o_b = p.o + ((row0 + row_b) * p.Hv + hv) * D + cp;
+      const bool wr_a = p.o != nullptr && row_a < valid, wr_b = p.o != nullptr && row_b < valid;
+#pragma unroll 1
+      for (int c0 = 0; c0 < D; c0 += 64) {
         float a[32], b[32];
-        tmem_ld32(tmem + lane_sel + TM_O1 + c0, a);
-        tmem_ld32(tmem + lane_sel + TM_O2 + c0, b);
+        tmem_ld_16x64(tmem + lanes_o + TM_O1 + c0, a);
+        tmem_ld_16x64(tmem + lanes_o + TM_O2 + c0, b);
         tmem_ld_wait();
-        if (c0 + 32 >= D) {  // all tensor-memory reads of this chunk's output are done
+        if (c0 + 64 >= D) {  // all tensor-memory reads of this chunk's output are done
           tc_fence_before();
           mbar_arrive(&bars[O_FREE]);
         }
-        if (write) {
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            const float* aa = a + 8 * c;
-            const float* bb = b + 8 * c;
-            *reinterpret_cast<uint4*>(orow + c0 + 8 * c) = make_uint4(
-                pack_bf16(sg * aa[0] + bb[0], sg * aa[1] + bb[1]),
-                pack_bf16(sg * aa[2] + bb[2], sg * aa[3] + bb[3]),
-                pack_bf16(sg * aa[4] + bb[4], sg * aa[5] + bb[5]),
-                pack_bf16(sg * aa[6] + bb[6], sg * aa[7] + bb[7]));
-          }
+        for (int i = 0; i < 8; ++i) {
+          if (wr_a)
+            *reinterpret_cast<uint32_t*>(o_a + c0 + 8 * i) =
+                pack_bf16(sg_a * a[4 * i] + b[4 * i], sg_a * a[4 * i + 1] + b[4 * i + 1]);
+          if (wr_b)
+            *reinterpret_cast<uint32_t*>(o_b + c0 + 8 * i) =
+                pack_bf16(sg_b * a[4 * i + 2] + b[4 * i + 2], sg_b * a[4 * i + 3] + b[4 * i + 3]);
         }
       }
     };
@@ -359,45 +401,40 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
         ok = WAIT(O_DONE, (it - 1) & 1);
         if (!ok) break;
         tc_fence_after();
-        if (p.profile) t_sec = clock64();
+        SEC_BEGIN();
         epilogue(it - 1);
-        if (p.profile) waited[S_COPY] += clock64() - t_sec;
+        SEC_END(SEC_A);
       }
       ok = WAIT(P_DONE, it & 1);
       if (!ok) break;
       tc_fence_after();
-      if (p.profile) t_sec = clock64();
-      // Pg = s P exp(g_tok - g_col) = P exp2((g_tok - g_col) log2e + log2 s), col <= tok
-      const float gt2 = vs[V_G * CHUNK + tok_o] * 1.4426950408889634f + log2_scale;
-#pragma unroll
-      for (int c0 = 0; c0 < CHUNK; c0 += 32) {
+      SEC_BEGIN();
+      // Pg = s P exp(g_row - g_col) = P exp2((g_row - g_col) log2e + log2 s), col <= row
+      {
+        const float ga2 = vs[V_G * CHUNK + row_a] * 1.4426950408889634f + log2_scale;
+        const float gb2 = vs[V_G * CHUNK + row_b] * 1.4426950408889634f + log2_scale;
         float x[32];
-        tmem_ld32(tmem + lane_sel + TM_O1 + c0, x);  // lanes 16-31 of the quarter hold P
+        tmem_ld_16x64(tmem + lanes_p + TM_O1, x);
         tmem_ld_wait();
-        if (lane >= 16) {
-          unsigned char* row = smem + OFF_P + tok_o * 128;
-          const float4* g4 = reinterpret_cast<const float4*>(vs + V_G * CHUNK + c0);
+        unsigned char* pa = smem + OFF_P + row_a * 128 + cp * 2;
+        unsigned char* pb = smem + OFF_P + row_b * 128 + cp * 2;
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            float4 ga = g4[2 * c], gb = g4[2 * c + 1];
-            const float gc[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
-            float pv[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              int col = c0 + 8 * c + e;
-              float ex = exp2f(fmaf(gc[e], -1.4426950408889634f, gt2));
-              pv[e] = col <= tok_o ? x[8 * c + e] * ex : 0.f;
-            }
-            *reinterpret_cast<uint4*>(row + ((((c0 >> 3) + c) ^ (tok_o & 7)) << 4)) =
-                make_uint4(pack_bf16(pv[0], pv[1]), pack_bf16(pv[2], pv[3]), pack_bf16(pv[4], pv[5]),
-                           pack_bf16(pv[6], pv[7]));
-          }
+        for (int i = 0; i < 8; ++i) {
+          const float2 gc = *reinterpret_cast<const float2*>(vs + V_G * CHUNK + 8 * i + cp);
+          const int col = 8 * i + cp;
+          const float e0 = -1.4426950408889634f * gc.x, e1 = -1.4426950408889634f * gc.y;
+          const float a0 = col <= row_a ? x[4 * i] * exp2f(e0 + ga2) : 0.f;
+          const float a1 = col + 1 <= row_a ? x[4 * i + 1] * exp2f(e1 + ga2) : 0.f;
+          const float b0 = col <= row_b ? x[4 * i + 2] * exp2f(e0 + gb2) : 0.f;
+          const float b1 = col + 1 <= row_b ? x[4 * i + 3] * exp2f(e1 + gb2) : 0.f;
+          *reinterpret_cast<uint32_t*>(pa + ((i ^ (row_a & 7)) << 4)) = pack_bf16(a0, a1);
+          *reinterpret_cast<uint32_t*>(pb + ((i ^ (row_b & 7)) << 4)) = pack_bf16(b0, b1);
         }
       }
       fence_proxy_async();
       tc_fence_before();
       mbar_arrive(&bars[P_READY]);
-      if (p.profile) waited[S_DEC] += clock64() - t_sec;
+      SEC_END(SEC_B);
     }
     if (ok && n_it > 0) {
       ok = WAIT(O_DONE, (n_it - 1) & 1);
@@ -409,96 +446,95 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
     // rows of o past the end of the last packed sequence come out zero
     if (p.o && p.lay.cu.ptr && n == p.N - 1) {
       const long long end = sp.bos + sp.len;
-      for (long long i = tid - 256; i < (p.T_rows - end) * 16; i += 128)
+      for (long long i = tid - 384; i < (p.T_rows - end) * 16; i += 128)
         *reinterpret_cast<uint4*>(p.o + ((end + (i >> 4)) * p.Hv + hv) * D + (i & 15) * 8) =
             make_uint4(0, 0, 0, 0);
     }
-  } else if (warp == 12) {
+  } else if (warp == 0) {
     // =============================== MMA issuer ===============================
     if (lane == 0) {
       constexpr uint32_t ID_P = idesc_bf16(64, 64, 0, 0);
       constexpr uint32_t ID_O = idesc_bf16(64, 128, 0, 0);
-      constexpr uint32_t ID_U = idesc_bf16(128, 64, 0, 0);
-      constexpr uint32_t ID_VT = idesc_bf16(128, 64, 1, 0);
+      constexpr uint32_t ID_UT = idesc_bf16(128, 64, 1, 0);            // A = V tile, MN-major
+      constexpr uint32_t ID_W = idesc_bf16(64, 128, 0, 1);             // B = K tile, MN-major
+      constexpr uint32_t ID_VN = idesc_bf16(128, 64, 0, 0) | (1u << 13);  // A negated
       constexpr uint32_t ID_S = idesc_bf16(128, 128, 0, 1);
       // low descriptor words of every operand tile (see umma_lo); steps are 32-bit adds
-      const uint32_t st_lo = desc_lo_kmajor(smem + OFF_ST), wt_lo = desc_lo_kmajor(smem + OFF_WT);
-      const uint32_t vnt_lo = desc_lo_kmajor(smem + OFF_VNT), vrt_lo = desc_lo_kmajor(smem + OFF_VRT);
-      const uint32_t p_lo = desc_lo_kmajor(smem + OFF_P), i_lo = desc_lo_kmajor(smem + OFF_I);
+      const uint32_t st_lo = desc_lo_kmajor(smem + OFF_ST), vnt_lo = desc_lo_kmajor(smem + OFF_VNT);
+      const uint32_t w_lo = desc_lo_kmajor(smem + OFF_W), p_lo = desc_lo_kmajor(smem + OFF_P);
+      const uint32_t ap_lo = desc_lo_kmajor(smem + OFF_AP), app_lo = desc_lo_kmajor(smem + OFF_APP);
+      const uint32_t vrt_lo = desc_lo_kmajor(smem + OFF_VRT);
       const uint32_t q0_lo = desc_lo_kmajor(smem + OFF_STAGE);
       const uint32_t k0_lo = desc_lo_kmajor(smem + OFF_STAGE + TILE_QK);
-      const uint32_t a0_lo = desc_lo_kmajor(smem + OFF_STAGE + 2 * TILE_QK + TILE_V);
       const uint32_t kmn0_lo = desc_lo_mnmajor(smem + OFF_STAGE + TILE_QK, 8192);
       const uint32_t vmn0_lo = desc_lo_mnmajor(smem + OFF_STAGE + 2 * TILE_QK, 8192);
       constexpr uint32_t STAGE_LO = STAGE_BYTES >> 4;
-      auto issue_p_vt = [&](uint32_t so) {  // so = stage offset in descriptor units
+      auto issue_u_w = [&](uint32_t so) {  // so = stage offset in descriptor units
+        umma_group<4, 128, 0, 2, 0, false>(tmem + TM_UV, vmn0_lo + so, ap_lo, ID_UT);
+        umma_group<4, 2, 0, 128, 0, false>(tmem + TM_W, app_lo, kmn0_lo + so, ID_W);
+        umma_commit(&bars[W_DONE]);
+      };
+      auto issue_p = [&](uint32_t so) {
         umma_group<8, 2, 512, 2, 512, false>(tmem + TM_P, q0_lo + so, k0_lo + so, ID_P);
         umma_commit(&bars[P_DONE]);
-        // VT = V^T: A = V tile read MN-major (16 rows per step), B = identity
-        umma_group<4, 128, 0, 2, 0, false>(tmem + TM_VT, vmn0_lo + so, i_lo, ID_VT);
       };
       for (int it = 0; it < n_it && ok; ++it) {
         const int s = it & 1;
         const uint32_t so = s ? STAGE_LO : 0u, so_next = s ? 0u : STAGE_LO;
-        ok = WAIT(FULL0 + s, (it >> 1) & 1);
+        if (it == 0) {
+          ok = WAIT(FULL0, 0) && WAIT(AP_READY, 0);
+          if (!ok) break;
+          tc_fence_after();
+          issue_u_w(0);
+          issue_p(0);
+        }
+        ok = WAIT(S_COPY, it & 1) && WAIT(W_READY, it & 1);
         if (!ok) break;
         tc_fence_after();
-        if (it == 0) issue_p_vt(0);
-        ok = WAIT(S_COPY, it & 1);
-        if (!ok) break;
-        tc_fence_after();
-        if (p.profile) t_sec = clock64();
-        // U^T = S^T K^T
-        umma_group<8, 2, 1024, 2, 512, false>(tmem + TM_UV, st_lo, k0_lo + so, ID_U);
-        umma_commit(&bars[U_DONE]);
-        if (p.profile) waited[U_DONE] += clock64() - t_sec;
+        SEC_BEGIN();
+        // Vn^T = u^T - S^T w^T   (accumulates onto u^T)
+        umma_group<8, 2, 1024, 2, 512, true>(tmem + TM_UV, st_lo, w_lo, ID_VN);
+        umma_commit(&bars[VN_DONE]);
+        SEC_END(SEC_A);
         if (it > 0) {
           ok = WAIT(O_FREE, (it - 1) & 1);
           if (!ok) break;
           tc_fence_after();
         }
-        if (p.profile) t_sec = clock64();
+        SEC_BEGIN();
         // O1 = Q S      (B = S^T copy: N = v rows, K = k)
         umma_group<8, 2, 512, 2, 1024, false>(tmem + TM_O1, q0_lo + so, st_lo, ID_O);
-        if (p.profile) waited[O_DONE] += clock64() - t_sec;
-        ok = WAIT(W_READY, it & 1);
+        SEC_END(SEC_B);
+        ok = WAIT(VR_READY, it & 1) && WAIT(S_DEC, it & 1);
         if (!ok) break;
         tc_fence_after();
-        if (p.profile) t_sec = clock64();
-        // Vn^T = W^T A^T
-        umma_group<4, 2, 0, 2, 0, false>(tmem + TM_UV, wt_lo, a0_lo + so, ID_U);
-        umma_commit(&bars[VN_DONE]);
-        if (p.profile) waited[VN_DONE] += clock64() - t_sec;
-        ok = WAIT(VR_READY, it & 1);
-        if (!ok) break;
-        ok = WAIT(S_DEC, it & 1);
-        if (!ok) break;
-        tc_fence_after();
-        if (p.profile) t_sec = clock64();
+        SEC_BEGIN();
         // S^T += (rho Vn)^T K      (B = K tile read MN-major: contraction over its 64 rows)
         umma_group<4, 2, 0, 128, 0, true>(tmem + TM_S, vrt_lo, kmn0_lo + so, ID_S);
         umma_commit(&bars[S_DONE]);
-        if (p.profile) waited[S_DONE] += clock64() - t_sec;
-        ok = WAIT(P_READY, it & 1);
+        SEC_END(SEC_C);
+        if (it + 1 < n_it) {
+          ok = WAIT(FULL0 + (s ^ 1), ((it + 1) >> 1) & 1) && WAIT(AP_READY, (it + 1) & 1) &&
+               WAIT(VN_READY, it & 1);  // the V group has read Vn^T out of TM_UV
+          if (!ok) break;
+          tc_fence_after();
+          SEC_BEGIN();
+          issue_u_w(so_next);
+          SEC_END(SEC_D);
+        }
+        ok = WAIT(P_READY, it & 1) && (it + 1 < n_it || WAIT(VN_READY, it & 1));
         if (!ok) break;
         tc_fence_after();
-        if (p.profile) t_sec = clock64();
+        SEC_BEGIN();
         // O2 = Pg Vn     (B = Vn^T copy: N = v rows, K = tok')
         umma_group<4, 2, 0, 2, 0, false>(tmem + TM_O2, p_lo, vnt_lo, ID_O);
         umma_commit(&bars[O_DONE]);
         umma_commit(&bars[EMPTY0 + s]);
-        if (p.profile) waited[EMPTY0] += clock64() - t_sec;
-        if (it + 1 < n_it) {
-          ok = WAIT(FULL0 + (s ^ 1), ((it + 1) >> 1) & 1);
-          if (!ok) break;
-          tc_fence_after();
-          if (p.profile) t_sec = clock64();
-          issue_p_vt(so_next);
-          if (p.profile) waited[P_DONE] += clock64() - t_sec;
-        }
+        if (it + 1 < n_it) issue_p(so_next);
+        SEC_END(SEC_E);
       }
     }
-  } else if (warp == 13) {
+  } else if (warp == 1) {
     // =============================== producer ===============================
     float g_r[2] = {0.f, 0.f}, b_r[2] = {0.f, 0.f}, gl_r = 0.f;
     auto fetch = [&](int it) {
@@ -540,13 +576,13 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
       if (lane == 0) {
         mbar_arrive_expect_tx(bar, STAGE_BYTES);
         const int y = (int)row0;
+        tma_load_2d(st + 2 * TILE_QK + TILE_V, &map_a, hv * CHUNK, y, bar);
         tma_load_2d(st + TILE_QK, &map_k, hq * D, y, bar);
         tma_load_2d(st + TILE_QK + 8192, &map_k, hq * D + 64, y, bar);
         tma_load_2d(st + 2 * TILE_QK, &map_v, hv * D, y, bar);
         tma_load_2d(st + 2 * TILE_QK + 8192, &map_v, hv * D + 64, y, bar);
         tma_load_2d(st, &map_q, hq * D, y, bar);
         tma_load_2d(st + 8192, &map_q, hq * D + 64, y, bar);
-        tma_load_2d(st + 2 * TILE_QK + TILE_V, &map_a, hv * CHUNK, y, bar);
       }
       if (it + 1 < n_it) fetch(it + 1);  // in flight while this warp waits for the next free stage
       if (partial) {
@@ -564,19 +600,57 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
         if (lane == 0) mbar_arrive(&bars[FULL0 + s]);
       }
     }
+  } else {
+    // =============================== prep (warps 2, 3) ===============================
+    // A' = A diag(beta), A'' = A diag(beta gamma), one thread per chunk row.  Eight consecutive
+    // rows visit the eight 16-byte chunks of their rows in rotated order: conflict-free.
+    const int r = tid - 64;
+    for (int it = 0; it < n_it && ok; ++it) {
+      const int s = it & 1;
+      ok = WAIT(FULL0 + s, (it >> 1) & 1);
+      if (ok && it > 0) ok = WAIT(W_DONE, (it - 1) & 1);  // u, w of the chunk before are done
+      if (!ok) break;
+      SEC_BEGIN();
+      const float* vs = vec + (it & 3) * VEC_SLOT_FLOATS;
+      const unsigned char* src = smem + OFF_STAGE + s * STAGE_BYTES + 2 * TILE_QK + TILE_V + r * 128;
+#pragma unroll 1
+      for (int q8 = 0; q8 < 8; ++q8) {
+        const int pc = (q8 + r) & 7;            // physical chunk; holds columns 8*(pc ^ (r&7)) ..
+        const int col = (pc ^ (r & 7)) * 8;
+        const uint4 a = *reinterpret_cast<const uint4*>(src + pc * 16);
+        const float4 b0 = *reinterpret_cast<const float4*>(vs + V_BETA * CHUNK + col);
+        const float4 b1 = *reinterpret_cast<const float4*>(vs + V_BETA * CHUNK + col + 4);
+        const float4 g0 = *reinterpret_cast<const float4*>(vs + V_BG * CHUNK + col);
+        const float4 g1 = *reinterpret_cast<const float4*>(vs + V_BG * CHUNK + col + 4);
+        *reinterpret_cast<uint4*>(smem + OFF_AP + r * 128 + pc * 16) =
+            make_uint4(scale_bf16x2(a.x, b0.x, b0.y), scale_bf16x2(a.y, b0.z, b0.w),
+                       scale_bf16x2(a.z, b1.x, b1.y), scale_bf16x2(a.w, b1.z, b1.w));
+        *reinterpret_cast<uint4*>(smem + OFF_APP + r * 128 + pc * 16) =
+            make_uint4(scale_bf16x2(a.x, g0.x, g0.y), scale_bf16x2(a.y, g0.z, g0.w),
+                       scale_bf16x2(a.z, g1.x, g1.y), scale_bf16x2(a.w, g1.z, g1.w));
+      }
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&bars[AP_READY]);
+        mbar_arrive(&bars[EMPTY0 + s]);  // the A tile of this stage is no longer read here
+      }
+      SEC_END(SEC_A);
+    }
   }
 
-  if (p.profile && blockIdx.x == 0 &&
-      (tid == 0 || tid == 128 || tid == 256 || tid == 384 || tid == 416)) {
-    int role = tid == 0 ? 0 : tid == 128 ? 1 : tid == 256 ? 2 : tid == 384 ? 3 : 4;
-    for (int i = 0; i < 16; ++i) g_wait_profile[role * 16 + i] = waited[i];
-    if (tid == 0) g_wait_profile[5 * 16] = clock64() - t_start;
+  if (PROFILE && blockIdx.x == 0 && (tid % 128 == 0 || tid == 32 || tid == 64)) {
+    int role = tid == 128 ? 0 : tid == 256 ? 1 : tid == 384 ? 2 : tid == 0 ? 3 : tid == 32 ? 4 : 5;
+    for (int i = 0; i < 24; ++i) g_wait_profile[role * 24 + i] = waited[i];
+    if (tid == 128) g_wait_profile[6 * 24] = clock64() - t_start;
   }
+#undef SEC_BEGIN
+#undef SEC_END
   // ---- teardown: everybody meets, then the allocating warp frees tensor memory
   if (!ok) *abort_flag = 1;
   tc_fence_before();
   __syncthreads();
-  if (warp == 12) tmem_dealloc(tmem, 512);
+  if (warp == 0) tmem_dealloc(tmem, 512);
   if (tid == 0 && *abort_flag) atomicCAS(&g_device_status, 0, 1);
 }
 
@@ -628,16 +702,22 @@ int launch_fwd_tc(const void* q, const void* k, const void* v, const void* A, co
   p.N = N; p.Hq = Hq; p.Hv = Hv; p.T_rows = T_rows; p.scale = scale; p.lay = lay;
   static const bool profile = getenv("FQLA_PROFILE") != nullptr;
   p.profile = profile ? 1 : 0;
-  rc = configure_smem((const void*)fwd_tc_kernel, SMEM_BYTES);
-  if (rc != 0) return rc;
-  fwd_tc_kernel<<<(unsigned)(N * Hv), 512, SMEM_BYTES, st>>>(p, mq, mk, mv, ma);
-  return (int)cudaGetLastError();
+  const bool extra = h != nullptr || vnew != nullptr;
+  auto launch = [&](auto kernel) {
+    int err = configure_smem((const void*)kernel, SMEM_BYTES);
+    if (err != 0) return err;
+    kernel<<<(unsigned)(N * Hv), 512, SMEM_BYTES, st>>>(p, mq, mk, mv, ma);
+    return (int)cudaGetLastError();
+  };
+  if (p.profile) return launch(fwd_tc_kernel<true, true>);
+  if (extra) return launch(fwd_tc_kernel<false, true>);
+  return launch(fwd_tc_kernel<false, false>);
 }
 
 }  // namespace fqla
 
-extern "C" int fqla_debug_wait_profile(long long* out96) {
-  return (int)cudaMemcpyFromSymbol(out96, fqla::g_wait_profile, sizeof(long long) * 96);
+extern "C" int fqla_debug_wait_profile(long long* out168) {
+  return (int)cudaMemcpyFromSymbol(out168, fqla::g_wait_profile, sizeof(long long) * 7 * 24);
 }
 
 extern "C" int fqla_device_status(int* out, int reset) {

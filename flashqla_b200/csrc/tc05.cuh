@@ -45,29 +45,29 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
                "r"(bytes)
                : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+// One try: the thread is suspended by the hardware until the phase completes or the time hint
+// (nanoseconds) runs out; no instructions are issued meanwhile, so waiting warps do not take
+// issue slots from the warps they share a scheduler with.
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(s32(bar)), "r"(parity)
+      : "r"(s32(bar)), "r"(parity), "r"(hint_ns)
       : "memory");
   return ok != 0;
 }
 
-// Bounded wait.  Gives up after `budget` polls or as soon as *abort_flag (shared memory) is set;
-// on its own timeout it sets *abort_flag so that every other role of the CTA leaves too.
-// Returns false when the wait was abandoned.
+// Bounded wait: at most `budget` tries of up to 1 ms each.  Gives up as soon as *abort_flag
+// (shared memory) is set; on its own timeout it sets *abort_flag so that every other role of the
+// CTA leaves too.  Returns false when the wait was abandoned.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
-                                          volatile int* abort_flag, uint32_t budget = 1u << 26) {
+                                          volatile int* abort_flag, uint32_t budget = 2000) {
   for (uint32_t i = 0; i < budget; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 255u) == 255u && *abort_flag) return false;
-#ifdef FQLA_WAIT_SLEEP_NS
-    __nanosleep(FQLA_WAIT_SLEEP_NS);  // keep waiting warps out of the issue slots of working ones
-#endif
+    if (mbar_try_wait(bar, parity, 1000000u)) return true;
+    if (*abort_flag) return false;
   }
   *abort_flag = 1;
   return false;
@@ -116,6 +116,23 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
   uint32_t* r = reinterpret_cast<uint32_t*>(v);
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+// 16 lanes x 64 consecutive columns spread over the 32 threads of a warp (the natural read of an
+// M = 64 accumulator quarter): register 4i+e of lane l holds row l/4 + 8*(e>>1), column
+// 8*i + 2*(l%4) + (e&1).  `taddr` names the first of the 16 lanes.
+__device__ __forceinline__ void tmem_ld_16x64(uint32_t taddr, float (&v)[32]) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x256b.x8.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
       "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
