@@ -475,8 +475,13 @@ static int launch_bwd_main(const BwdMainParams& p, long long n_chunks, cudaStrea
   return (int)cudaGetLastError();
 }
 
+// tcgen05 version for K = V = 128 (bwd_main_tc.cu)
+int launch_bwd_main_tc(const void* q, const void* k, const void* v, const void* vnew, const void* A,
+                       const float* g, const void* beta, int beta_is_f32, const void* dO,
+                       const void* du, const void* h, const void* dh, void* dq, void* dk, void* dv,
+                       float* db, float* dg, int Hq, int Hv, long long T_rows, long long n_chunks,
+                       float scale, SeqLayout lay, IndexTable chunk_indices, cudaStream_t st);
 }  // namespace fqla
-
 using namespace fqla;
 
 extern "C" int fqla_bwd_main(const void* q, const void* k, const void* v, const void* vnew,
@@ -502,6 +507,10 @@ extern "C" int fqla_bwd_main(const void* q, const void* k, const void* v, const 
   long long n = cu_seqlens ? num_chunks : (long long)B * ((T + CHUNK - 1) / CHUNK);
   if (n <= 0) return FQLA_OK;
   cudaStream_t st = (cudaStream_t)stream;
+  static const bool force_legacy = getenv("FQLA_FORCE_MMA_SYNC") != nullptr;
+  if (D == 128 && !force_legacy)
+    return launch_bwd_main_tc(q, k, v, vnew, A, g_cum, beta, beta_is_f32, dO, du, h, dh, dq, dk, dv,
+                              db, dg, Hq, Hv, (long long)B * T, n, scale, p.lay, p.chunk_indices, st);
   if (D == 128) return launch_bwd_main<128>(p, n, st);
   if (D == 64) return launch_bwd_main<64>(p, n, st);
   return FQLA_ERR_UNSUPPORTED_DIM;

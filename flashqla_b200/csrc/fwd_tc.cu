@@ -149,6 +149,11 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
     tma_prefetch_desc(&map_v);
     tma_prefetch_desc(&map_a);
   }
+  // Pg is lower triangular: its tile is zeroed once, the O group only ever rewrites the column
+  // groups that can be non-zero for its rows
+  for (int i = tid; i < 8192 / 16; i += 512)
+    *reinterpret_cast<uint4*>(smem + OFF_P + i * 16) = make_uint4(0, 0, 0, 0);
+  fence_proxy_async();
   if (warp == 0) tmem_alloc(tmem_slot, 512);
   tc_fence_before();
   __syncthreads();
@@ -418,8 +423,10 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
         tmem_ld_wait();
         unsigned char* pa = smem + OFF_P + row_a * 128 + cp * 2;
         unsigned char* pb = smem + OFF_P + row_b * 128 + cp * 2;
+        // column groups entirely above this warp's rows stay zero (written once at start)
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
+          if (i > 2 * wq + 1) continue;
           const float2 gc = *reinterpret_cast<const float2*>(vs + V_G * CHUNK + 8 * i + cp);
           const int col = 8 * i + cp;
           const float e0 = -1.4426950408889634f * gc.x, e1 = -1.4426950408889634f * gc.y;
@@ -720,11 +727,17 @@ extern "C" int fqla_debug_wait_profile(long long* out168) {
   return (int)cudaMemcpyFromSymbol(out168, fqla::g_wait_profile, sizeof(long long) * 7 * 24);
 }
 
+namespace fqla {
+int bwd_main_tc_status(int* out, int reset);
+}
+
 extern "C" int fqla_device_status(int* out, int reset) {
-  int v = 0;
+  int v = 0, w = 0;
   cudaError_t e = cudaMemcpyFromSymbol(&v, fqla::g_device_status, sizeof(int));
   if (e != cudaSuccess) return (int)e;
-  if (out) *out = v;
+  int rc = fqla::bwd_main_tc_status(&w, reset);
+  if (rc != 0) return rc;
+  if (out) *out = v | w;
   if (reset && v != 0) {
     int z = 0;
     e = cudaMemcpyToSymbol(fqla::g_device_status, &z, sizeof(int));

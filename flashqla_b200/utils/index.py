@@ -21,6 +21,14 @@ def _is_capturing() -> bool:
     return torch.cuda.is_available() and torch.cuda.is_current_stream_capturing()
 
 
+def _same_arg(a, b) -> bool:
+    """Tensors (and other objects) are compared by identity, plain numbers by value: two equal
+    ints are not guaranteed to be the same object."""
+    if isinstance(a, (int, float, bool, str)) and type(a) is type(b):
+        return a == b
+    return a is b
+
+
 def tensor_cache(fn: Callable[..., Any]) -> Callable[..., Any]:
     """Memoise ``fn`` on the *identity* of its arguments (reference: ``utils/index.py:11-76``).
 
@@ -35,9 +43,9 @@ def tensor_cache(fn: Callable[..., Any]) -> Callable[..., Any]:
     def _same(args, kwargs, e_args, e_kwargs) -> bool:
         if len(args) != len(e_args) or len(kwargs) != len(e_kwargs):
             return False
-        if any(a is not b for a, b in zip(args, e_args)):
+        if any(not _same_arg(a, b) for a, b in zip(args, e_args)):
             return False
-        return all(k in e_kwargs and v is e_kwargs[k] for k, v in kwargs.items())
+        return all(k in e_kwargs and _same_arg(v, e_kwargs[k]) for k, v in kwargs.items())
 
     @functools.wraps(fn)
     def wrapper(*args: Any, **kwargs: Any) -> Any:
