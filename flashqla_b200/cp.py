@@ -46,6 +46,8 @@ class SegmentPlan:
     seg_begin: torch.Tensor        # int32 [n_raw+1]: first segment of every raw sequence
     first_seg_of_raw: torch.Tensor  # int64 [n_raw]
     last_seg_of_raw: torch.Tensor   # int64 [n_raw]
+    keep_fwd: torch.Tensor         # int32 [n_seg]: 0 for the last segment of a raw sequence
+    keep_bwd: torch.Tensor         # int32 [n_seg]: 0 for the first segment of a raw sequence
     n_seg: int
 
 
@@ -117,9 +119,16 @@ def _build_plan(bounds, Hv, device, idx_dtype, T_rows) -> SegmentPlan | None:
     seg_cu = torch.tensor(seg_bounds, dtype=idx_dtype, device=device)
     begin = torch.tensor(seg_begin, dtype=torch.int32, device=device)
     tables = SeqTables(1, T_rows, seg_cu)
-    first = begin[:-1].long()
-    last = begin[1:].long() - 1
-    return SegmentPlan(tables, begin, first, last, len(seg_bounds) - 1)
+    n_seg = len(seg_bounds) - 1
+    keep_fwd = [1] * n_seg
+    keep_bwd = [1] * n_seg
+    for first, nxt in zip(seg_begin[:-1], seg_begin[1:]):
+        if nxt > first:
+            keep_bwd[first] = 0
+            keep_fwd[nxt - 1] = 0
+    return SegmentPlan(tables, begin, begin[:-1].long(), begin[1:].long() - 1,
+                       torch.tensor(keep_fwd, dtype=torch.int32, device=device),
+                       torch.tensor(keep_bwd, dtype=torch.int32, device=device), n_seg)
 
 
 @tensor_cache
@@ -146,10 +155,9 @@ def plan_segments(tables: SeqTables, Hv: int, is_bwd: bool = False,
 def forward_segment_states(plan: SegmentPlan, k, v, A, g_cum, beta, scale, h0):
     """Start state of every segment, fp32 ``[n_seg, Hv, D, D]``."""
     seg = plan.seg_tables
-    warm, fallback = ops.warmup_scan(g_cum, seg.cu, THRESHOLD, from_start=False)
     # the last segment of a sequence hands nothing on
-    warm[plan.last_seg_of_raw] = 0
-    fallback[plan.last_seg_of_raw] = 0
+    warm, fallback = ops.warmup_scan(g_cum, seg.cu, THRESHOLD, from_start=False,
+                                     keep=plan.keep_fwd)
     res = ops.fwd_seq(None, k, v, A, g_cum, beta, scale, None, output_o=False,
                       output_final_state=True, output_m=True, warm_chunks=warm,
                       m_mask=fallback, tables=seg)
@@ -159,10 +167,9 @@ def forward_segment_states(plan: SegmentPlan, k, v, A, g_cum, beta, scale, h0):
 def backward_segment_states(plan: SegmentPlan, q, k, v, A, g_cum, beta, do, scale, dht):
     """Gradient of the state leaving every segment, fp32 ``[n_seg, Hv, D, D]``."""
     seg = plan.seg_tables
-    warm, fallback = ops.warmup_scan(g_cum, seg.cu, THRESHOLD, from_start=True)
     # the first segment of a sequence receives nothing from before it
-    warm[plan.first_seg_of_raw] = 0
-    fallback[plan.first_seg_of_raw] = 0
+    warm, fallback = ops.warmup_scan(g_cum, seg.cu, THRESHOLD, from_start=True,
+                                     keep=plan.keep_bwd)
     local = ops.bwd_dh(q, k, A, g_cum, beta, do, scale, None, output_dh=False, output_du=False,
                        output_dh0=True, warm_chunks=warm, tables=seg)["dh0"]
     # exact transition matrices where the gradient does not die out inside the segment

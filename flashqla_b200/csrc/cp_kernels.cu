@@ -13,26 +13,51 @@
 
 namespace fqla {
 
-// One thread per (segment, head).  Walks the chunk totals (the cumsum value on each chunk's last
-// row) from the segment end backwards (forward pass) or from its start forwards (backward pass).
-__global__ void warmup_scan_kernel(const float* __restrict__ g_cum, int Hv, SeqLayout lay,
-                                   int n_seg, float threshold, int from_start,
-                                   int* __restrict__ warm, int* __restrict__ fallback) {
-  int seg = blockIdx.x, hv = threadIdx.x;
-  if (seg >= n_seg || hv >= Hv) return;
-  SeqSpan sp = lay.span(seg);
-  float acc = 0.f;
-  int n = 0;
-  bool reached = false;
-  for (int i = 0; i < sp.n_chunks; ++i) {
-    int c = from_start ? i : sp.n_chunks - 1 - i;
-    int last_row = min(sp.len, (c + 1) * CHUNK) - 1;
-    acc += g_cum[(sp.bos + last_row) * Hv + hv];
-    ++n;
-    if (acc < threshold) { reached = true; break; }
+// One warp per (segment, head).  Walks the chunk totals (the cumsum value on each chunk's last
+// row) from the segment end backwards (forward pass) or from its start forwards (backward pass),
+// 32 chunks per step: the lanes load in parallel, a warp prefix sum finds the first crossing.
+// keep (optional, [n_seg]): segments with keep == 0 hand nothing on; they get warm = fallback = 0.
+__global__ void __launch_bounds__(128)
+warmup_scan_kernel(const float* __restrict__ g_cum, int Hv, SeqLayout lay, int n_seg,
+                   float threshold, int from_start, const int* __restrict__ keep,
+                   int* __restrict__ warm, int* __restrict__ fallback) {
+  const int lane = threadIdx.x & 31;
+  const int item = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (item >= n_seg * Hv) return;
+  const int seg = item / Hv, hv = item % Hv;
+  if (keep && keep[seg] == 0) {
+    if (lane == 0) warm[item] = fallback[item] = 0;
+    return;
   }
-  warm[seg * Hv + hv] = n;
-  fallback[seg * Hv + hv] = reached ? 0 : 1;
+  const SeqSpan sp = lay.span(seg);
+  float carry = 0.f;
+  int n = sp.n_chunks;
+  bool reached = false;
+  for (int base = 0; base < sp.n_chunks && !reached; base += 32) {
+    const int i = base + lane;
+    const bool in = i < sp.n_chunks;
+    float x = 0.f;
+    if (in) {
+      const int c = from_start ? i : sp.n_chunks - 1 - i;
+      const int last_row = min(sp.len, (c + 1) * CHUNK) - 1;
+      x = g_cum[(sp.bos + last_row) * Hv + hv];
+    }
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const float y = __shfl_up_sync(0xffffffffu, x, d);
+      if (lane >= d) x += y;
+    }
+    const unsigned hit = __ballot_sync(0xffffffffu, in && carry + x < threshold);
+    if (hit) {
+      n = base + __ffs(hit);
+      reached = true;
+    }
+    carry += __shfl_sync(0xffffffffu, x, 31);
+  }
+  if (lane == 0) {
+    warm[item] = n;
+    fallback[item] = reached ? 0 : 1;
+  }
 }
 
 // Chain the segments of one raw sequence for one head and one 32-wide value slice.
@@ -108,13 +133,13 @@ using namespace fqla;
 
 extern "C" int fqla_warmup_scan(const float* g_cum, int T, int Hv, const void* seg_cu_seqlens,
                                 int idx_is64, int n_seg, float threshold, int from_start,
-                                int* warm, int* fallback, void* stream) {
-  if (!g_cum || !seg_cu_seqlens || !warm || !fallback || Hv <= 0 || Hv > 1024)
-    return FQLA_ERR_INVALID_ARG;
+                                const int* keep, int* warm, int* fallback, void* stream) {
+  if (!g_cum || !seg_cu_seqlens || !warm || !fallback || Hv <= 0) return FQLA_ERR_INVALID_ARG;
   if (n_seg <= 0) return FQLA_OK;
   SeqLayout lay{{seg_cu_seqlens, idx_is64}, {seg_cu_seqlens, idx_is64}, T};
-  warmup_scan_kernel<<<n_seg, ((Hv + 31) / 32) * 32, 0, (cudaStream_t)stream>>>(
-      g_cum, Hv, lay, n_seg, threshold, from_start, warm, fallback);
+  const long long items = (long long)n_seg * Hv;
+  warmup_scan_kernel<<<(unsigned)((items + 3) / 4), 128, 0, (cudaStream_t)stream>>>(
+      g_cum, Hv, lay, n_seg, threshold, from_start, keep, warm, fallback);
   return (int)cudaGetLastError();
 }
 

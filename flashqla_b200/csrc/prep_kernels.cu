@@ -56,6 +56,47 @@ __global__ void __launch_bounds__(128) cumsum_kernel(const float* __restrict__ g
   }
 }
 
+// C[16 x 8*NT] = A[16 x 8*KT] * B[8*KT x 8*NT], both row-major fp32 in shared memory, as
+// mma.m16n8k8 with tf32 inputs.  Fragment element (g = lane/4, t = lane%4): c[nt][0..3] =
+// C[g][8nt+2t], C[g][8nt+2t+1], C[g+8][8nt+2t], C[g+8][8nt+2t+1].
+__device__ __forceinline__ uint32_t to_tf32(float x) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+  return r;
+}
+template <int NT, int KT>
+__device__ __forceinline__ void tf32_gemm(float (&c)[NT][4], const float* A, int lda, const float* B,
+                                          int ldb, int lane) {
+  const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) c[nt][0] = c[nt][1] = c[nt][2] = c[nt][3] = 0.f;
+#pragma unroll
+  for (int kt = 0; kt < KT; ++kt) {
+    const uint32_t a0 = to_tf32(A[g * lda + 8 * kt + t]), a1 = to_tf32(A[(g + 8) * lda + 8 * kt + t]);
+    const uint32_t a2 = to_tf32(A[g * lda + 8 * kt + t + 4]), a3 = to_tf32(A[(g + 8) * lda + 8 * kt + t + 4]);
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const uint32_t b0 = to_tf32(B[(8 * kt + t) * ldb + 8 * nt + g]);
+      const uint32_t b1 = to_tf32(B[(8 * kt + t + 4) * ldb + 8 * nt + g]);
+      asm volatile(
+          "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+          "{%0,%1,%2,%3};"
+          : "+f"(c[nt][0]), "+f"(c[nt][1]), "+f"(c[nt][2]), "+f"(c[nt][3])
+          : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+    }
+  }
+}
+template <int NT>
+__device__ __forceinline__ void store_frag(float* C, int ldc, const float (&c)[NT][4], float sign,
+                                           int lane) {
+  const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    *reinterpret_cast<float2*>(C + g * ldc + 8 * nt + 2 * t) = make_float2(sign * c[nt][0], sign * c[nt][1]);
+    *reinterpret_cast<float2*>(C + (g + 8) * ldc + 8 * nt + 2 * t) = make_float2(sign * c[nt][2], sign * c[nt][3]);
+  }
+}
+
 // ------------------------------------------------------------------------------------------
 // kkt + solve.  One CTA (128 threads) per (chunk, value head).
 //   1. K K^T (64x64xD) on tensor cores, 2. L = strict_lower(beta_s * KK^T * exp(g_s-g_t)) in fp32,
@@ -74,7 +115,8 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(
   float* sG = sL + CHUNK * LDL;
   float* sB = sG + CHUNK;
   float* sX = sB + CHUNK;         // [64][LDL] the inverse
-  float* sY = sX + CHUNK * LDL;   // up to 3 blocks of 16 x 16 partial products
+  constexpr int LDY = 40;         // partial products [32][LDY]; reuse the K tile, dead by then
+  float* sY = reinterpret_cast<float*>(smem_raw);
 
   int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   int hv = blockIdx.y, hq = hv / (Hv / Hq);
@@ -117,10 +159,11 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(
     }
   __syncthreads();
 
-  // Blocked inverse of the unit lower-triangular (I + L), 4 x 4 blocks of 16 x 16, fp32:
-  //   diagonal blocks by forward substitution (thread = one column of one block), then the
-  //   blocks at distance d = 1, 2, 3 below the diagonal:
-  //   X_ij = -X_ii * sum_{k=j}^{i-1} L_ik X_kj.
+  // Inverse of the unit lower-triangular (I + L) by recursive halving:
+  //   [[P, 0], [C, Q]]^-1 = [[P^-1, 0], [-Q^-1 C P^-1, Q^-1]].
+  // The four 16 x 16 diagonal blocks come from forward substitution in fp32 (thread = one column
+  // of one block); the two 16 x 16 and then the one 32 x 32 off-diagonal blocks are two small
+  // products each, on tensor cores with tf32 inputs (round to nearest) and fp32 accumulation.
   if (tid < CHUNK) {
     const int b0 = (tid >> 4) * 16, c = tid & 15;
     float x[16];
@@ -132,27 +175,36 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(
       x[i] = s;
       sX[(b0 + i) * LDL + b0 + c] = s;
     }
+  } else {
+    // the 16 x 16 blocks above the diagonal inside each 32 x 32 diagonal block are operands of
+    // the last two products: they must read as zero
+    const int t = tid - CHUNK, blk = t >> 5, r = (t >> 1) & 15, c0 = (t & 1) * 8;
+    float* z = sX + (32 * blk + r) * LDL + 32 * blk + 16 + c0;
+    *reinterpret_cast<float4*>(z) = make_float4(0.f, 0.f, 0.f, 0.f);
+    *reinterpret_cast<float4*>(z + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
   }
   __syncthreads();
-  for (int d = 1; d < 4; ++d) {
-    const int n_out = (4 - d) * 256;
-    for (int o = tid; o < n_out; o += 128) {
-      const int b = o >> 8, r = (o >> 4) & 15, c = o & 15, bi = (b + d) * 16, bj = b * 16;
-      float acc = 0.f;
-      for (int kk = bj; kk < bi; kk += 16) {
-#pragma unroll
-        for (int t = 0; t < 16; ++t) acc += sL[(bi + r) * LDL + kk + t] * sX[(kk + t) * LDL + bj + c];
-      }
-      sY[o] = acc;
-    }
+  {
+    // 32 x 32 diagonal blocks: pair p covers rows/cols [32p, 32p+32); warp = (pair, 8-column tile pair)
+    const int pr = warp >> 1, bi = 32 * pr + 16, bj = 32 * pr, n0 = 8 * (warp & 1);
+    float* y = sY + pr * 16 * LDY;
+    float c[1][4];
+    tf32_gemm<1, 2>(c, sL + bi * LDL + bj, LDL, sX + bj * LDL + bj + n0, LDL, lane);
+    store_frag<1>(y + n0, LDY, c, 1.f, lane);
     __syncthreads();
-    for (int o = tid; o < n_out; o += 128) {
-      const int b = o >> 8, r = (o >> 4) & 15, c = o & 15, bi = (b + d) * 16, bj = b * 16;
-      float acc = 0.f;
-#pragma unroll
-      for (int t = 0; t < 16; ++t) acc += sX[(bi + r) * LDL + bi + t] * sY[(b << 8) + t * 16 + c];
-      sX[(bi + r) * LDL + bj + c] = -acc;
-    }
+    tf32_gemm<1, 2>(c, sX + bi * LDL + bi, LDL, y + n0, LDY, lane);
+    store_frag<1>(sX + bi * LDL + bj + n0, LDL, c, -1.f, lane);
+    __syncthreads();
+  }
+  {
+    // the 32 x 32 block below the diagonal: warp = (16-row tile, 16-column half)
+    const int m0 = 16 * (warp >> 1), n0 = 16 * (warp & 1);
+    float c[2][4];
+    tf32_gemm<2, 4>(c, sL + (32 + m0) * LDL, LDL, sX + n0, LDL, lane);
+    store_frag<2>(sY + m0 * LDY + n0, LDY, c, 1.f, lane);
+    __syncthreads();
+    tf32_gemm<2, 4>(c, sX + (32 + m0) * LDL + 32, LDL, sY + n0, LDY, lane);
+    store_frag<2>(sX + (32 + m0) * LDL + n0, LDL, c, -1.f, lane);
     __syncthreads();
   }
   // bf16 rows out, 16 bytes per store; blocks above the diagonal are zero
@@ -221,7 +273,7 @@ template <int D>
 static int launch_kkt(const void* k, const void* beta, int beta_is_f32, const float* g, void* A,
                       int Hq, int Hv, SeqLayout lay, IndexTable ci, long long n,
                       cudaStream_t st) {
-  constexpr int smem = CHUNK * (D + 8) * 2 + 2 * CHUNK * (CHUNK + 4) * 4 + 2 * CHUNK * 4 + 768 * 4;
+  constexpr int smem = CHUNK * (D + 8) * 2 + 2 * CHUNK * (CHUNK + 4) * 4 + 2 * CHUNK * 4;
   int rc = configure_smem((const void*)kkt_solve_kernel<D>, smem);
   if (rc != 0) return rc;
   kkt_solve_kernel<D><<<dim3((unsigned)n, Hv), 128, smem, st>>>(

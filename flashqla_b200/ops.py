@@ -217,9 +217,11 @@ def group_reduce_vector(x, num_groups: int):
     return out
 
 
-def warmup_scan(g_cum, seg_cu_seqlens, threshold: float = -10.0, from_start: bool = False):
+def warmup_scan(g_cum, seg_cu_seqlens, threshold: float = -10.0, from_start: bool = False,
+                keep=None):
     """Per (segment, head) warm-up chunk count and fallback flag, both int32 ``[n_seg, Hv]``
-    (reference: ``blackwell/cp_fwd.py:81-115``, ``:224-264``)."""
+    (reference: ``blackwell/cp_fwd.py:81-115``, ``:224-264``).  ``keep`` (int32 ``[n_seg]``)
+    marks with 0 the segments that hand nothing on: they get 0 / 0."""
     _require_cuda(g_cum, seg_cu_seqlens)
     B, T, Hv = g_cum.shape
     n_seg = seg_cu_seqlens.numel() - 1
@@ -227,7 +229,8 @@ def warmup_scan(g_cum, seg_cu_seqlens, threshold: float = -10.0, from_start: boo
     fallback = torch.empty_like(warm)
     st = _lib.load().fqla_warmup_scan(
         _ptr(g_cum), T, Hv, _ptr(seg_cu_seqlens), int(seg_cu_seqlens.dtype == torch.int64), n_seg,
-        float(threshold), int(from_start), _ptr(warm), _ptr(fallback), _stream(g_cum))
+        float(threshold), int(from_start), _ptr(keep), _ptr(warm), _ptr(fallback),
+        _stream(g_cum))
     _lib.check(st, "warmup_scan")
     return warm, fallback
 

@@ -97,11 +97,13 @@ int fqla_group_reduce(const void* in, void* out, long long rows, int Hq, int G, 
 
 /* Per (segment, head): number of chunks, counted from the segment end (from_start == 0) or start
  * (from_start != 0), after which the accumulated log gate is below `threshold`; fallback = 1
- * where the whole segment does not get there.  seg_cu_seqlens [n_seg+1].
+ * where the whole segment does not get there.  seg_cu_seqlens [n_seg+1].  keep (int32 [n_seg]
+ * or NULL): segments with keep == 0 are skipped and get warm = fallback = 0 (the last segment of
+ * a sequence hands nothing forward, the first nothing backward).
  * Replaces get_warmup_chunks / get_warmup_chunks_bidi, blackwell/cp_fwd.py:81-115, :224-264. */
 int fqla_warmup_scan(const float* g_cum, int T, int Hv, const void* seg_cu_seqlens, int idx_is64,
-                     int n_seg, float threshold, int from_start, int* warm, int* fallback,
-                     void* stream);
+                     int n_seg, float threshold, int from_start, const int* keep, int* warm,
+                     int* fallback, void* stream);
 
 /* Chain segment states of each raw sequence (segments seg_begin[r] .. seg_begin[r+1]-1):
  * reverse == 0: out[first] = raw[r] (or 0); out[i+1] = local[i] + use_m[i,hv] * M[i]   out[i]
