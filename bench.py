@@ -153,7 +153,7 @@ def run_ours(args):
     import torch.distributed as dist
 
     import flashqla_b200 as fq
-    from flashqla_b200 import _lib, ops
+    from flashqla_b200 import _lib, cp, ops
 
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
@@ -300,20 +300,49 @@ def run_ours(args):
         e2e_ms = timed(e2e_step, e2e_steps) / e2e_steps
     e2e_value = tokens * world / (e2e_ms * 1e-3)
 
-    # ---- dominant kernel alone: the sequential forward recurrence, timed with CUDA events
+    # ---- dominant kernel alone, launched exactly as inside the step (same segment plan),
+    # timed with CUDA events on the launching stream
     g_cum = ops.chunk_local_cumsum(x["g"], 64, x["cu"])
     A = ops.kkt_solve(x["k"], x["beta"], g_cum, x["cu"])
     scale = 128 ** -0.5
+    B_, T_ = x["q"].shape[:2]
+    tables = ops.SeqTables(B_, T_, x["cu"])
+    plan = cp.plan_segments(tables, x["Hv"], device=x["q"].device)
+    run_tables, run_h0 = tables, x["h0"]
+    if plan is not None:
+        run_tables = plan.seg_tables
+        run_h0 = cp.forward_segment_states(plan, x["k"], x["v"], A, g_cum, x["beta"], scale, x["h0"])
+    G = x["Hv"] // x["Hq"]
+    if not bwd:
+        kernel_name = "fwd_tc_kernel"
 
-    def dominant():
-        ops.fwd_seq(x["q"], x["k"], x["v"], A, g_cum, x["beta"], scale, x["h0"],
-                    output_final_state=True, cu_seqlens=x["cu"])
+        def dominant():
+            ops.fwd_seq(x["q"], x["k"], x["v"], A, g_cum, x["beta"], scale, run_h0,
+                        output_final_state=True, tables=run_tables)
+
+        # per (token, value head): q,k / v / A / g / beta / o
+        bytes_per_th = 2 * 128 * 2 / G + 2 * 128 + 2 * 64 + 4 + 2 + 2 * 128
+        flop_per_th = 147_456
+    else:
+        kernel_name = "bwd_main_tc_kernel"
+        fw = ops.fwd_seq(None, x["k"], x["v"], A, g_cum, x["beta"], scale, run_h0, output_o=False,
+                         output_h=True, output_vnew=True, tables=run_tables)
+        bw = ops.bwd_dh(x["q"], x["k"], A, g_cum, x["beta"], x["do"], scale, None,
+                        tables=run_tables)
+
+        def dominant():
+            ops.bwd_main(x["q"], x["k"], x["v"], fw["vnew"], A, g_cum, x["beta"], x["do"],
+                         bw["du"], fw["h"], bw["dh"], scale, tables=run_tables)
+
+        # per (token, value head): q,k / v,vnew,do,du / A / h,dh (2 x 32 KiB per 64 tokens) /
+        # g,beta / dq,dk,dv / dg,db
+        bytes_per_th = 2 * 128 * 2 / G + 4 * 256 + 128 + 2 * 32768 / 64 + 6 + 3 * 256 + 8
+        # 16 tile products per chunk: 3 of 64x128x128, 5 of 64x64x128, 6 of 64x128x64, 2 of 64x64x64
+        flop_per_th = 2 * (3 * 128 * 128 + 5 * 64 * 128 + 6 * 128 * 64 + 2 * 64 * 64)
 
     for _ in range(3):
         dominant()
     k_ms = timed(dominant, args.steps) / args.steps
-    G = x["Hv"] // x["Hq"]
-    bytes_per_th = 2 * 128 * 2 / G + 2 * 128 + 2 * 64 + 4 + 2 + 2 * 128  # q,k / v / A / g / beta / o
     alg_bytes = tokens * x["Hv"] * bytes_per_th
     peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(peaks_path):
@@ -321,11 +350,11 @@ def run_ours(args):
     else:
         peak, peak_src = 6650.0, "fallback"
     achieved = alg_bytes / (k_ms * 1e-3) / 1e9
-    roofline = {"kernel": "fwd_seq_kernel", "bound": "hbm", "achieved": round(achieved, 1),
+    roofline = {"kernel": kernel_name, "bound": "hbm", "achieved": round(achieved, 1),
                 "peak": peak, "peak_source": peak_src, "unit": "GB/s",
                 "frac": round(achieved / peak, 4), "traffic": None,
                 "kernel_ms": round(k_ms, 4),
-                "tensor_tflops": round(tokens * x["Hv"] * 147_456 / (k_ms * 1e-3) / 1e12, 1)}
+                "tensor_tflops": round(tokens * x["Hv"] * flop_per_th / (k_ms * 1e-3) / 1e12, 1)}
 
     if rank != 0:
         if world > 1:

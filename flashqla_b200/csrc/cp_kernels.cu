@@ -71,9 +71,12 @@ __global__ void __launch_bounds__(D) merge_kernel(const float* __restrict__ loca
                                                   const float* __restrict__ raw,
                                                   const int* __restrict__ seg_begin,
                                                   float* __restrict__ out, int Hv, int reverse) {
-  constexpr int BV = 32, BK = 32;
-  __shared__ float cur[D][BV];
-  // one staging buffer for a D x BK panel of M: forward [a][j] (row stride BK+1), reverse [j][a]
+  constexpr int BV = 32, BK = 32, LDC = BV + 1;
+  // all global traffic is one 128-byte row segment per warp instruction; the padded row stride
+  // keeps both the row-wise (warp = row) and the thread-owns-a-row accesses free of bank conflicts
+  __shared__ float cur[D * LDC];
+  // one staging buffer: the local state of the step, then D x BK panels of M, forward [a][j]
+  // (row stride BK+1), reverse [j][a]
   __shared__ float panel[D * (BK + 1)];
   const int a = threadIdx.x, lane = a & 31, warp = a >> 5;
   const int v0 = blockIdx.x * BV, hv = blockIdx.y, r = blockIdx.z;
@@ -85,23 +88,27 @@ __global__ void __launch_bounds__(D) merge_kernel(const float* __restrict__ loca
   // initial value
   {
     const float* src = raw ? state(raw, r) : nullptr;
-    for (int j = 0; j < BV; ++j) cur[a][j] = src ? src[(long long)a * D + v0 + j] : 0.f;
+    for (int row = warp; row < D; row += D / 32)
+      cur[row * LDC + lane] = src ? src[(long long)row * D + v0 + lane] : 0.f;
   }
   __syncthreads();
   const int n = s1 - s0;
   for (int step = 0; step < n; ++step) {
     const int i = reverse ? s1 - 1 - step : s0 + step;
     float* dst = const_cast<float*>(state(out, i));
-    for (int j = 0; j < BV; ++j) dst[(long long)a * D + v0 + j] = cur[a][j];
+    for (int row = warp; row < D; row += D / 32) dst[(long long)row * D + v0 + lane] = cur[row * LDC + lane];
     if (step == n - 1) break;
-    float acc[BV];
     const float* loc = state(local, i);
-#pragma unroll
-    for (int j = 0; j < BV; ++j) acc[j] = loc[(long long)a * D + v0 + j];
+    for (int row = warp; row < D; row += D / 32) panel[row * LDC + lane] = loc[(long long)row * D + v0 + lane];
     const bool with_m = use_m == nullptr || use_m[i * Hv + hv] != 0;
+    __syncthreads();
+    float acc[BV];
+#pragma unroll
+    for (int j = 0; j < BV; ++j) acc[j] = panel[a * LDC + j];
     if (with_m) {
       const float* m = state(M, i);
       for (int b0 = 0; b0 < D; b0 += BK) {
+        __syncthreads();  // the previous contents of the panel have been consumed
         if (!reverse) {
           // panel[a'][j] = M[a'][b0+j], one warp per row, coalesced
           for (int row = warp; row < D; row += D / 32)
@@ -115,14 +122,13 @@ __global__ void __launch_bounds__(D) merge_kernel(const float* __restrict__ loca
         for (int j = 0; j < BK; ++j) {
           float w = reverse ? panel[j * D + a] : panel[a * (BK + 1) + j];
 #pragma unroll
-          for (int vv = 0; vv < BV; ++vv) acc[vv] += w * cur[b0 + j][vv];
+          for (int vv = 0; vv < BV; ++vv) acc[vv] += w * cur[(b0 + j) * LDC + vv];
         }
-        __syncthreads();
       }
     }
-    __syncthreads();
+    __syncthreads();  // every read of cur (and of the panel) is done
 #pragma unroll
-    for (int j = 0; j < BV; ++j) cur[a][j] = acc[j];
+    for (int j = 0; j < BV; ++j) cur[a * LDC + j] = acc[j];
     __syncthreads();
   }
 }

@@ -363,10 +363,12 @@ extern "C" int fqla_fwd_seq(const void* q, const void* k, const void* v, const v
   p.lay = SeqLayout{{cu_seqlens, idx_is64}, {chunk_offsets, idx_is64}, T};
   if (p.N <= 0) return FQLA_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  // The full forward (q and o present, K = V = 128) runs on the tcgen05 kernel; state-only
-  // passes, transition matrices and D = 64 run on the mma.sync kernel in this file.
+  // The full forward (q and o present, K = V = 128) and the recomputation of the per-chunk
+  // states and v_new for the backward pass (neither q nor o) run on the tcgen05 kernel;
+  // state-only passes, transition matrices and D = 64 run on the mma.sync kernel in this file.
   static const bool force_legacy = getenv("FQLA_FORCE_MMA_SYNC") != nullptr;
-  if (D == 128 && q && o && !M && !warm_chunks && !m_mask && !force_legacy)
+  const bool full = q && o, recompute = !q && !o && (h || vnew);
+  if (D == 128 && (full || recompute) && !M && !warm_chunks && !m_mask && !force_legacy)
     return launch_fwd_tc(q, k, v, A, g_cum, beta, beta_is_f32, h0, ht, o, h, vnew, p.N, Hq, Hv,
                          p.T_rows, scale, p.lay, st);
   if (D == 128) return launch_fwd_seq<128>(p, st);

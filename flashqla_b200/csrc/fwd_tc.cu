@@ -699,7 +699,9 @@ int launch_fwd_tc(const void* q, const void* k, const void* v, const void* A, co
   using namespace fwdtc;
   CUtensorMap mq, mk, mv, ma;
   int rc;
-  if ((rc = make_map(&mq, q, T_rows, (long long)Hq * D))) return rc;
+  // without q (recomputation of h and v_new for the backward pass) the output products run on
+  // k instead; their result is never stored
+  if ((rc = make_map(&mq, q ? q : k, T_rows, (long long)Hq * D))) return rc;
   if ((rc = make_map(&mk, k, T_rows, (long long)Hq * D))) return rc;
   if ((rc = make_map(&mv, v, T_rows, (long long)Hv * D))) return rc;
   if ((rc = make_map(&ma, A, T_rows, (long long)Hv * CHUNK))) return rc;

@@ -12,7 +12,7 @@ from __future__ import annotations
 import torch
 
 from . import _lib
-from .utils import prepare_chunk_indices, prepare_chunk_offsets
+from .utils import prepare_chunk_indices, prepare_chunk_offsets, tensor_cache
 
 CHUNK_SIZE = 64
 
@@ -54,8 +54,18 @@ class SeqTables:
             self.is64 = int(cu_seqlens.dtype == torch.int64)
 
     @property
+    def total(self) -> int:
+        """Rows covered by sequences (host int, cached per ``cu_seqlens`` tensor)."""
+        return self.B * self.T if self.cu is None else _total_rows(self.cu)
+
+    @property
     def args(self):
         return _ptr(self.cu), _ptr(self.chunk_offsets), self.is64, self.N
+
+
+@tensor_cache
+def _total_rows(cu_seqlens: torch.Tensor) -> int:
+    return int(cu_seqlens[-1].item())
 
 
 def _beta_flag(beta: torch.Tensor) -> int:
@@ -184,13 +194,14 @@ def bwd_main(q, k, v, vnew, a, g_cum, b, do, du, h, dh, scale, cu_seqlens=None,
     Hv = v.shape[2]
     tb = tables or SeqTables(B, T, cu_seqlens)
     dev = k.device
-    # rows past the last packed sequence are never written by the kernel: start from zero
-    alloc = torch.zeros if (tb.cu is not None) else torch.empty
-    dq = alloc(B, T, Hv, D, dtype=k.dtype, device=dev)
-    dk = alloc(B, T, Hv, D, dtype=k.dtype, device=dev)
-    dv = alloc(B, T, Hv, D, dtype=k.dtype, device=dev)
-    db = alloc(B, T, Hv, dtype=torch.float32, device=dev)
-    dg = alloc(B, T, Hv, dtype=torch.float32, device=dev)
+    dq = torch.empty(B, T, Hv, D, dtype=k.dtype, device=dev)
+    dk = torch.empty(B, T, Hv, D, dtype=k.dtype, device=dev)
+    dv = torch.empty(B, T, Hv, D, dtype=k.dtype, device=dev)
+    db = torch.empty(B, T, Hv, dtype=torch.float32, device=dev)
+    dg = torch.empty(B, T, Hv, dtype=torch.float32, device=dev)
+    if tb.total < B * T:  # rows past the last packed sequence are never written by the kernel
+        for t in (dq, dk, dv, db, dg):
+            t[:, tb.total:].zero_()
     cu, offs, is64, _ = tb.args
     st = _lib.load().fqla_bwd_main(
         _ptr(q), _ptr(k), _ptr(v), _ptr(vnew), _ptr(a), _ptr(g_cum), _ptr(b), _beta_flag(b),
