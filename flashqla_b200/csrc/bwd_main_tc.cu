@@ -39,28 +39,34 @@ struct BwdMainTcParams {
   float scale;
   SeqLayout lay;
   IndexTable chunk_indices;
+  long long n_chunks;
   int profile;
 };
 
 namespace bmtc {
 constexpr int D = 128;
+constexpr int NT = 512;          // threads: 16 warps = 4 lane quarters x 4 column quarters
 constexpr int ROW_TILE = 16384;  // [64 x 128] bf16 as two 64-column blocks
 constexpr int SQ_TILE = 32768;   // [128 x 128] bf16 as two 64-column blocks of 128 rows
 constexpr int OFF_Q = 0, OFF_K = OFF_Q + ROW_TILE, OFF_V = OFF_K + ROW_TILE;
 constexpr int OFF_VN = OFF_V + ROW_TILE, OFF_DO = OFF_VN + ROW_TILE, OFF_DU = OFF_DO + ROW_TILE;
-constexpr int OFF_H = OFF_DU + ROW_TILE;   // later: dw (first 16 KB)
+constexpr int OFF_H = OFF_DU + ROW_TILE;
 constexpr int OFF_DH = OFF_H + SQ_TILE;
 constexpr int OFF_A = OFF_DH + SQ_TILE;
 constexpr int OFF_DS = OFF_A + 8192;       // ds, later T = A^T dA
 constexpr int OFF_DA = OFF_DS + 8192;
 constexpr int OFF_D3 = OFF_DA + 8192;      // dA3
 constexpr int OFF_D3B = OFF_D3 + 8192;     // diag(beta) dA3
-constexpr int OFF_VEC = OFF_D3B + 8192;    // g, gamma, rho, beta, dg, db (64 floats each) + dg_last
+constexpr int OFF_DW = OFF_D3B + 8192;     // -du h^T
+constexpr int OFF_VEC = OFF_DW + ROW_TILE;  // g, gamma, rho, beta, dg, db (64 floats each) + dg_last
 constexpr int OFF_BAR = OFF_VEC + (6 * 64 + 4) * 4;
 constexpr int OFF_MISC = OFF_BAR + 8 * 8;
 constexpr int SMEM_BYTES = OFF_MISC + 16 + 1024;
-constexpr int OFF_DW = OFF_H;
-constexpr uint32_t TX_BYTES = 6 * ROW_TILE + 2 * SQ_TILE + 8192;
+// the operand tiles of one work item arrive in three groups, in the order their buffers of the
+// previous item become free
+constexpr uint32_t TX_A = 2 * SQ_TILE + 2 * ROW_TILE;  // h, dh, dO, v_new
+constexpr uint32_t TX_B = 3 * ROW_TILE;                // du, q, v
+constexpr uint32_t TX_C = ROW_TILE + 8192;             // k, A
 // tensor memory: (column, lane half) of every accumulator
 constexpr uint32_t HI = 16u << 16;
 constexpr uint32_t T_DQ1 = 0, T_DK1 = 128, T_DW = 256, T_T1 = 384;
@@ -69,10 +75,11 @@ constexpr uint32_t T_X1 = 256, T_X2 = 320;            // after dw has been read
 constexpr uint32_t T_T = 384 + HI, T_KK = 448 + HI;    // after ds, qk have been read
 constexpr uint32_t T_D3 = 256;                         // after x1 has been read
 constexpr uint32_t T_T3 = 0, T_DK5 = 0 + HI;           // after dq1, dq2 have been read
-enum { BAR_LOAD = 0, BAR_MMA = 1 };
+enum { BAR_LOAD_A = 0, BAR_LOAD_B, BAR_LOAD_C, BAR_MMA };
 }  // namespace bmtc
 
-// 16 lanes x 32 columns: register 4i+e of lane l holds row l/4 + 8*(e>>1), column 8i + 2(l%4) + (e&1)
+// 16 lanes x 32 (x4) or 16 (x2) columns: register 4i+e of lane l holds row l/4 + 8*(e>>1),
+// column 8i + 2(l%4) + (e&1)
 __device__ __forceinline__ void tmem_ld_16x32(uint32_t taddr, float (&v)[16]) {
   uint32_t* r = reinterpret_cast<uint32_t*>(v);
   asm volatile(
@@ -84,8 +91,19 @@ __device__ __forceinline__ void tmem_ld_16x32(uint32_t taddr, float (&v)[16]) {
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void tmem_ld_16x16(uint32_t taddr, float (&v)[8]) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.16x256b.x2.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7])
+      : "r"(taddr)
+      : "memory");
+}
 
-__global__ void __launch_bounds__(256, 1)
+// Persistent: CTA b handles work items b, b + gridDim.x, ...; item w = (chunk w / Hv, head w % Hv),
+// so neighbouring CTAs share q and k of a grouped-value-attention group through L2.
+__global__ void __launch_bounds__(bmtc::NT, 1)
 bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap map_q,
                    const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                    const __grid_constant__ CUtensorMap map_vn, const __grid_constant__ CUtensorMap map_do,
@@ -107,25 +125,87 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
   float* sDgLast = sDb + 64;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int hv = blockIdx.y, hq = hv / (p.Hv / p.Hq);
-  int seq, ci;
-  if (p.lay.cu.ptr) {
-    seq = (int)p.chunk_indices[2 * blockIdx.x];
-    ci = (int)p.chunk_indices[2 * blockIdx.x + 1];
-  } else {
-    int per = (p.lay.T + CHUNK - 1) / CHUNK;
-    seq = blockIdx.x / per;
-    ci = blockIdx.x % per;
-  }
-  const SeqSpan sp = p.lay.span(seq);
-  const long long row0 = sp.bos + (long long)ci * CHUNK;
-  const int valid = min(CHUNK, sp.len - ci * CHUNK);
-  const long long chunk_id = sp.chunk_base + ci;
+  const long long total = p.n_chunks * p.Hv;
+
+  struct Item {
+    long long row0, chunk_id;
+    int valid, hv, hq;
+  };
+  auto decode = [&](long long w) {
+    Item t;
+    const long long cidx = w / p.Hv;
+    t.hv = (int)(w % p.Hv);
+    t.hq = t.hv / (p.Hv / p.Hq);
+    int seq, ci;
+    if (p.lay.cu.ptr) {
+      seq = (int)p.chunk_indices[2 * cidx];
+      ci = (int)p.chunk_indices[2 * cidx + 1];
+    } else {
+      const int per = (p.lay.T + CHUNK - 1) / CHUNK;
+      seq = (int)(cidx / per);
+      ci = (int)(cidx % per);
+    }
+    const SeqSpan sp = p.lay.span(seq);
+    t.row0 = sp.bos + (long long)ci * CHUNK;
+    t.valid = min(CHUNK, sp.len - ci * CHUNK);
+    t.chunk_id = sp.chunk_base + ci;
+    return t;
+  };
+  auto load_a = [&](const Item& t) {
+    const int y = (int)t.row0, ys = (int)((t.chunk_id * p.Hv + t.hv) * D);
+    mbar_arrive_expect_tx(&bars[BAR_LOAD_A], TX_A);
+    tma_load_2d(smem + OFF_DO, &map_do, t.hv * D, y, &bars[BAR_LOAD_A]);
+    tma_load_2d(smem + OFF_DO + 8192, &map_do, t.hv * D + 64, y, &bars[BAR_LOAD_A]);
+    tma_load_2d(smem + OFF_H, &map_h, 0, ys, &bars[BAR_LOAD_A]);
+    tma_load_2d(smem + OFF_H + 16384, &map_h, 64, ys, &bars[BAR_LOAD_A]);
+    tma_load_2d(smem + OFF_VN, &map_vn, t.hv * D, y, &bars[BAR_LOAD_A]);
+    tma_load_2d(smem + OFF_VN + 8192, &map_vn, t.hv * D + 64, y, &bars[BAR_LOAD_A]);
+    tma_load_2d(smem + OFF_DH, &map_dh, 0, ys, &bars[BAR_LOAD_A]);
+    tma_load_2d(smem + OFF_DH + 16384, &map_dh, 64, ys, &bars[BAR_LOAD_A]);
+  };
+  auto load_b = [&](const Item& t) {
+    const int y = (int)t.row0;
+    mbar_arrive_expect_tx(&bars[BAR_LOAD_B], TX_B);
+    tma_load_2d(smem + OFF_DU, &map_du, t.hv * D, y, &bars[BAR_LOAD_B]);
+    tma_load_2d(smem + OFF_DU + 8192, &map_du, t.hv * D + 64, y, &bars[BAR_LOAD_B]);
+    tma_load_2d(smem + OFF_Q, &map_q, t.hq * D, y, &bars[BAR_LOAD_B]);
+    tma_load_2d(smem + OFF_Q + 8192, &map_q, t.hq * D + 64, y, &bars[BAR_LOAD_B]);
+    tma_load_2d(smem + OFF_V, &map_v, t.hv * D, y, &bars[BAR_LOAD_B]);
+    tma_load_2d(smem + OFF_V + 8192, &map_v, t.hv * D + 64, y, &bars[BAR_LOAD_B]);
+  };
+  auto load_c = [&](const Item& t) {
+    const int y = (int)t.row0;
+    mbar_arrive_expect_tx(&bars[BAR_LOAD_C], TX_C);
+    tma_load_2d(smem + OFF_K, &map_k, t.hq * D, y, &bars[BAR_LOAD_C]);
+    tma_load_2d(smem + OFF_K + 8192, &map_k, t.hq * D + 64, y, &bars[BAR_LOAD_C]);
+    tma_load_2d(smem + OFF_A, &map_a, t.hv * CHUNK, y, &bars[BAR_LOAD_C]);
+  };
+  // per-row scalars of an item, fetched one item ahead into registers by threads 0..63
+  float pre_g = 0.f, pre_gl = 0.f, pre_beta = 0.f;
+  auto fetch_vectors = [&](const Item& t) {
+    if (tid < CHUNK) {
+      const int r = min(tid, t.valid - 1);
+      pre_g = p.g[(t.row0 + r) * p.Hv + t.hv];
+      pre_gl = p.g[(t.row0 + t.valid - 1) * p.Hv + t.hv];
+      pre_beta = tid < t.valid ? load_beta(p.beta, p.beta_is_f32, (t.row0 + tid) * p.Hv + t.hv) : 0.f;
+    }
+  };
+  // rows past the end of the sequence belong to the next one: zero them in n_blocks 8 KB blocks
+  auto zero_rows = [&](int off, int n_blocks, int valid) {
+    for (int blk = 0; blk < n_blocks; ++blk) {
+      unsigned char* base = smem + off + blk * 8192;
+      for (int i = tid; i < (CHUNK - valid) * 8; i += NT)
+        *reinterpret_cast<uint4*>(base + (valid + (i >> 3)) * 128 + ((i & 7) << 4)) = make_uint4(0, 0, 0, 0);
+    }
+  };
 
   if (tid == 0) {
-    mbar_init(&bars[BAR_LOAD], 1);
+    mbar_init(&bars[BAR_LOAD_A], 1);
+    mbar_init(&bars[BAR_LOAD_B], 1);
+    mbar_init(&bars[BAR_LOAD_C], 1);
     mbar_init(&bars[BAR_MMA], 1);
     *abort_flag = 0;
+    *sDgLast = 0.f;
     fence_mbar_init();
   }
   if (warp == 0) tmem_alloc(tmem_slot, 512);
@@ -133,60 +213,20 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const bool prof = p.profile && tid == 0 && blockIdx.x == 0 && blockIdx.y == 0;
+  const bool prof = p.profile && tid == 0 && blockIdx.x == 0;
   int stamp_i = 0;
   auto stamp = [&]() {
-    if (prof) g_bwd_main_profile[stamp_i++] = clock64();
+    if (prof && stamp_i < 16) g_bwd_main_profile[stamp_i++] = clock64();
   };
   stamp();
 
+  Item cur = decode(blockIdx.x);  // the grid never exceeds the number of items
   if (tid == 0) {
-    const int y = (int)row0;
-    mbar_arrive_expect_tx(&bars[BAR_LOAD], TX_BYTES);
-    tma_load_2d(smem + OFF_DO, &map_do, hv * D, y, &bars[BAR_LOAD]);
-    tma_load_2d(smem + OFF_DO + 8192, &map_do, hv * D + 64, y, &bars[BAR_LOAD]);
-    tma_load_2d(smem + OFF_H, &map_h, 0, (int)((chunk_id * p.Hv + hv) * D), &bars[BAR_LOAD]);
-    tma_load_2d(smem + OFF_H + 16384, &map_h, 64, (int)((chunk_id * p.Hv + hv) * D), &bars[BAR_LOAD]);
-    tma_load_2d(smem + OFF_VN, &map_vn, hv * D, y, &bars[BAR_LOAD]);
-    tma_load_2d(smem + OFF_VN + 8192, &map_vn, hv * D + 64, y, &bars[BAR_LOAD]);
-    tma_load_2d(smem + OFF_DU, &map_du, hv * D, y, &bars[BAR_LOAD]);
-    tma_load_2d(smem + OFF_DU + 8192, &map_du, hv * D + 64, y, &bars[BAR_LOAD]);
-    tma_load_2d(smem + OFF_DH, &map_dh, 0, (int)((chunk_id * p.Hv + hv) * D), &bars[BAR_LOAD]);
-    tma_load_2d(smem + OFF_DH + 16384, &map_dh, 64, (int)((chunk_id * p.Hv + hv) * D), &bars[BAR_LOAD]);
-    tma_load_2d(smem + OFF_Q, &map_q, hq * D, y, &bars[BAR_LOAD]);
-    tma_load_2d(smem + OFF_Q + 8192, &map_q, hq * D + 64, y, &bars[BAR_LOAD]);
-    tma_load_2d(smem + OFF_K, &map_k, hq * D, y, &bars[BAR_LOAD]);
-    tma_load_2d(smem + OFF_K + 8192, &map_k, hq * D + 64, y, &bars[BAR_LOAD]);
-    tma_load_2d(smem + OFF_V, &map_v, hv * D, y, &bars[BAR_LOAD]);
-    tma_load_2d(smem + OFF_V + 8192, &map_v, hv * D + 64, y, &bars[BAR_LOAD]);
-    tma_load_2d(smem + OFF_A, &map_a, hv * CHUNK, y, &bars[BAR_LOAD]);
+    load_a(cur);
+    load_b(cur);
+    load_c(cur);
   }
-  if (tid < CHUNK) {
-    const int r = min(tid, valid - 1);
-    const float gv = p.g[(row0 + r) * p.Hv + hv];
-    const float gl = p.g[(row0 + valid - 1) * p.Hv + hv];
-    sG[tid] = gv;
-    sGam[tid] = fast_exp(gv);
-    sRho[tid] = fast_exp(gl - gv);
-    sBeta[tid] = tid < valid ? load_beta(p.beta, p.beta_is_f32, (row0 + tid) * p.Hv + hv) : 0.f;
-    sDg[tid] = 0.f;
-    sDb[tid] = 0.f;
-    if (tid == 0) *sDgLast = 0.f;
-  }
-  bool ok = mbar_wait(&bars[BAR_LOAD], 0, abort_flag);
-  if (ok && valid < CHUNK) {
-    // rows past the end of the sequence belong to the next one: zero them in every row tile
-    for (int blk = 0; blk < 12; ++blk) {
-      unsigned char* base = smem + blk * 8192;  // q, k, v, vn, do, du: two blocks each
-      for (int i = tid; i < (CHUNK - valid) * 8; i += 256)
-        *reinterpret_cast<uint4*>(base + (valid + (i >> 3)) * 128 + ((i & 7) << 4)) = make_uint4(0, 0, 0, 0);
-    }
-    for (int i = tid; i < (CHUNK - valid) * 8; i += 256)
-      *reinterpret_cast<uint4*>(smem + OFF_A + (valid + (i >> 3)) * 128 + ((i & 7) << 4)) = make_uint4(0, 0, 0, 0);
-    fence_proxy_async();
-  }
-  __syncthreads();
-  stamp();
+  fetch_vectors(cur);
 
   // ---- descriptors (low words) ----
   const uint32_t q_lo = desc_lo_kmajor(smem + OFF_Q), k_lo = desc_lo_kmajor(smem + OFF_K);
@@ -204,15 +244,12 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
   constexpr uint32_t ID_MM_64 = idesc_bf16(64, 64, 1, 1);
 
   // ---- per-thread coordinates in the 16-lane accumulator shape ----
-  const int qd = warp & 3, ch = warp >> 2;
+  const int qd = warp & 3, cq = warp >> 2;
   const int row_a = 16 * qd + (lane >> 2), row_b = row_a + 8, cp = 2 * (lane & 3);
   const uint32_t lanes = (uint32_t)(qd * 32) << 16;
-  const int c128 = 64 * ch, c64 = 32 * ch;   // first column of this warp in 128- / 64-wide tiles
-  const float g_a = sG[row_a], g_b = sG[row_b];
-  const float gam_a = sGam[row_a], gam_b = sGam[row_b];
-  const float rho_a = sRho[row_a], rho_b = sRho[row_b];
-  const float beta_a = sBeta[row_a], beta_b = sBeta[row_b];
+  const int c128 = 32 * cq, c64 = 16 * cq;   // first column of this warp in 128- / 64-wide tiles
   uint32_t phase = 0;
+  bool ok = true;
   auto wait_mma = [&]() {
     bool r = mbar_wait(&bars[BAR_MMA], phase, abort_flag);
     phase ^= 1;
@@ -234,209 +271,357 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
     x += __shfl_xor_sync(0xffffffffu, x, 16);
     return x;
   };
-  // store a pair of a [64 x 64] operand tile
   auto st_tile64 = [&](int off, int row, int col, float lo, float hi) {
     *reinterpret_cast<uint32_t*>(smem + off + sw128_offset(row, col)) = pack_bf16(lo, hi);
   };
+  auto round_sync = [&]() {
+    fence_proxy_async();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+  };
 
-  float dq1[32], dkacc[32];
+#pragma unroll 1
+  for (long long w = blockIdx.x; w < total && ok; w += gridDim.x) {
+    const uint32_t lph = (uint32_t)((w / gridDim.x) & 1);
+    const bool has_next = w + gridDim.x < total;
+    Item nxt = cur;
+    if (has_next) nxt = decode(w + gridDim.x);
+    const int valid = cur.valid;
+    if (tid < CHUNK) {
+      sG[tid] = pre_g;
+      sGam[tid] = fast_exp(pre_g);
+      sRho[tid] = fast_exp(pre_gl - pre_g);
+      sBeta[tid] = pre_beta;
+      sDg[tid] = 0.f;
+      sDb[tid] = 0.f;
+    }
+    ok = mbar_wait(&bars[BAR_LOAD_A], lph, abort_flag) && mbar_wait(&bars[BAR_LOAD_B], lph, abort_flag);
+    if (ok && valid < CHUNK) {
+      zero_rows(OFF_Q, 2, valid);
+      zero_rows(OFF_V, 8, valid);  // v, v_new, dO, du
+    }
+    round_sync();
+    stamp();
 
-  // ======================= round 1: products with h and dh, ds, qk =======================
-  if (ok && tid == 0) {
-    umma_group<8, 2, 512, 2, 1024, false>(tmem + T_DQ1, do_lo, h_lo, ID_KK_128);
-    umma_group<8, 2, 512, 2, 1024, false>(tmem + T_DW, du_lo, h_lo, ID_KK_128);
-    umma_group<8, 2, 512, 2, 1024, false>(tmem + T_DK1, vn_lo, dh_lo, ID_KK_128);
-    umma_group<8, 2, 512, 2, 512, false>(tmem + T_DS, do_lo, vn_lo, ID_KK_64);
-    umma_group<8, 2, 512, 2, 512, false>(tmem + T_QK, q_lo, k_lo, ID_KK_64);
-    umma_commit(&bars[BAR_MMA]);
-  }
-  // meanwhile: gamma_last * sum(h * dh) over the whole 128 x 128 tiles (plain shared-memory reads)
-  {
-    float hd = 0.f;
-    for (int i = tid; i < SQ_TILE / 16; i += 256) {
-      const uint4 a = *reinterpret_cast<const uint4*>(smem + OFF_H + i * 16);
-      const uint4 b = *reinterpret_cast<const uint4*>(smem + OFF_DH + i * 16);
-      const uint32_t* pa = &a.x;
-      const uint32_t* pb = &b.x;
+    // ======================= round 1: products with h and dh, ds, qk =======================
+    if (ok && tid == 0) {
+      umma_group<8, 2, 512, 2, 1024, false>(tmem + T_DW, du_lo, h_lo, ID_KK_128);
+      umma_group<8, 2, 512, 2, 512, false>(tmem + T_DS, do_lo, vn_lo, ID_KK_64);
+      umma_group<8, 2, 512, 2, 1024, false>(tmem + T_DQ1, do_lo, h_lo, ID_KK_128);
+      umma_group<8, 2, 512, 2, 1024, false>(tmem + T_DK1, vn_lo, dh_lo, ID_KK_128);
+    }
+    // meanwhile: gamma_last * sum(h * dh) over the whole 128 x 128 tiles (plain shared-memory reads)
+    if (ok) {
+      float hd = 0.f;
+      for (int i = tid; i < SQ_TILE / 16; i += NT) {
+        const uint4 a = *reinterpret_cast<const uint4*>(smem + OFF_H + i * 16);
+        const uint4 b = *reinterpret_cast<const uint4*>(smem + OFF_DH + i * 16);
+        const uint32_t* pa = &a.x;
+        const uint32_t* pb = &b.x;
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        float2 fa = __bfloat1622float2(*reinterpret_cast<const bf162*>(&pa[e]));
-        float2 fb = __bfloat1622float2(*reinterpret_cast<const bf162*>(&pb[e]));
-        hd += fa.x * fb.x + fa.y * fb.y;
+        for (int e = 0; e < 4; ++e) {
+          float2 fa = __bfloat1622float2(*reinterpret_cast<const bf162*>(&pa[e]));
+          float2 fb = __bfloat1622float2(*reinterpret_cast<const bf162*>(&pb[e]));
+          hd += fa.x * fb.x + fa.y * fb.y;
+        }
       }
+#pragma unroll
+      for (int d = 16; d > 0; d >>= 1) hd += __shfl_xor_sync(0xffffffffu, hd, d);
+      if (lane == 0) atomicAdd(sDgLast, sGam[CHUNK - 1] * hd);
     }
+    ok = ok && mbar_wait(&bars[BAR_LOAD_C], lph, abort_flag);
+    if (ok && valid < CHUNK) {
+      zero_rows(OFF_K, 2, valid);
+      zero_rows(OFF_A, 1, valid);
+      fence_proxy_async();
+    }
+    __syncthreads();
+    if (ok && tid == 0) {
+      umma_group<8, 2, 512, 2, 512, false>(tmem + T_QK, q_lo, k_lo, ID_KK_64);
+      umma_commit(&bars[BAR_MMA]);
+    }
+    const float g_a = sG[row_a], g_b = sG[row_b];
+    const float gam_a = sGam[row_a], gam_b = sGam[row_b];
+    const float rho_a = sRho[row_a], rho_b = sRho[row_b];
+    const float beta_a = sBeta[row_a], beta_b = sBeta[row_b];
+    float dq1[16], dkacc[16];
+    ok = ok && wait_mma();
+    stamp();
+    if (ok) {
+      {  // dw = -du h^T as an operand tile
+        float dw[16];
+        tmem_ld_16x32(tmem + lanes + T_DW + c128, dw);
+        tmem_ld_wait();
 #pragma unroll
-    for (int d = 16; d > 0; d >>= 1) hd += __shfl_xor_sync(0xffffffffu, hd, d);
-    if (lane == 0) atomicAdd(sDgLast, sGam[CHUNK - 1] * hd);
-  }
-  ok = ok && wait_mma();
-  stamp();
-  if (ok) {
-    // ds = scale * G * (dO Vn^T); ds2 = ds * (Q K^T)
-    float ds[16], qk[16];
-    tmem_ld_16x32(tmem + lanes + T_DS + c64, ds);
-    tmem_ld_16x32(tmem + lanes + T_QK + c64, qk);
-    tmem_ld_wait();
-    float rs_a = 0.f, rs_b = 0.f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int col = c64 + 8 * i + cp;
-      const float gc0 = sG[col], gc1 = sG[col + 1];
-      const float a0 = col <= row_a ? p.scale * ds[4 * i] * fast_exp(g_a - gc0) : 0.f;
-      const float a1 = col + 1 <= row_a ? p.scale * ds[4 * i + 1] * fast_exp(g_a - gc1) : 0.f;
-      const float b0 = col <= row_b ? p.scale * ds[4 * i + 2] * fast_exp(g_b - gc0) : 0.f;
-      const float b1 = col + 1 <= row_b ? p.scale * ds[4 * i + 3] * fast_exp(g_b - gc1) : 0.f;
-      st_tile64(OFF_DS, row_a, col, a0, a1);
-      st_tile64(OFF_DS, row_b, col, b0, b1);
-      const float s0 = a0 * qk[4 * i], s1 = a1 * qk[4 * i + 1], s2 = b0 * qk[4 * i + 2], s3 = b1 * qk[4 * i + 3];
-      rs_a += s0 + s1;
-      rs_b += s2 + s3;
-      const float c0 = col_sum(s0 + s2), c1 = col_sum(s1 + s3);
-      if (lane < 4) {
-        atomicAdd(sDg + col, -c0);
-        atomicAdd(sDg + col + 1, -c1);
+        for (int i = 0; i < 4; ++i) {
+          const int col = c128 + 8 * i + cp;
+          unsigned char* base = smem + OFF_DW + (col >> 6) * 8192;
+          *reinterpret_cast<uint32_t*>(base + sw128_offset(row_a, col & 63)) = pack_bf16(-dw[4 * i], -dw[4 * i + 1]);
+          *reinterpret_cast<uint32_t*>(base + sw128_offset(row_b, col & 63)) = pack_bf16(-dw[4 * i + 2], -dw[4 * i + 3]);
+        }
       }
-    }
-    rs_a = quad_sum(rs_a);
-    rs_b = quad_sum(rs_b);
-    if ((lane & 3) == 0) {
-      atomicAdd(sDg + row_a, rs_a);
-      atomicAdd(sDg + row_b, rs_b);
-    }
-    // dq1 = scale * gamma * (dO h^T), dg += rowsum(q * dq1)
-    tmem_ld_16x64(tmem + lanes + T_DQ1 + c128, dq1);
-    // dk1 = rho * (Vn dh^T), dg -= rowsum(k * dk1), dg_last += sum(k * dk1)
-    tmem_ld_16x64(tmem + lanes + T_DK1 + c128, dkacc);
-    tmem_ld_wait();
-    float qa = 0.f, qb = 0.f, ka = 0.f, kb = 0.f;
+      {  // ds = scale * G * (dO Vn^T); ds2 = ds * (Q K^T)
+        float ds[8], qk[8];
+        tmem_ld_16x16(tmem + lanes + T_DS + c64, ds);
+        tmem_ld_16x16(tmem + lanes + T_QK + c64, qk);
+        tmem_ld_wait();
+        float rs_a = 0.f, rs_b = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int col = c128 + 8 * i + cp;
-      dq1[4 * i] *= p.scale * gam_a;
-      dq1[4 * i + 1] *= p.scale * gam_a;
-      dq1[4 * i + 2] *= p.scale * gam_b;
-      dq1[4 * i + 3] *= p.scale * gam_b;
-      dkacc[4 * i] *= rho_a;
-      dkacc[4 * i + 1] *= rho_a;
-      dkacc[4 * i + 2] *= rho_b;
-      dkacc[4 * i + 3] *= rho_b;
-      const float2 q_a = tile2(OFF_Q, row_a, col), q_b = tile2(OFF_Q, row_b, col);
-      const float2 k_a = tile2(OFF_K, row_a, col), k_b = tile2(OFF_K, row_b, col);
-      qa += q_a.x * dq1[4 * i] + q_a.y * dq1[4 * i + 1];
-      qb += q_b.x * dq1[4 * i + 2] + q_b.y * dq1[4 * i + 3];
-      ka += k_a.x * dkacc[4 * i] + k_a.y * dkacc[4 * i + 1];
-      kb += k_b.x * dkacc[4 * i + 2] + k_b.y * dkacc[4 * i + 3];
-    }
-    qa = quad_sum(qa - ka);
-    qb = quad_sum(qb - kb);
-    float kt = ka + kb;
-#pragma unroll
-    for (int d = 16; d > 0; d >>= 1) kt += __shfl_xor_sync(0xffffffffu, kt, d);
-    if ((lane & 3) == 0) {
-      atomicAdd(sDg + row_a, qa);
-      atomicAdd(sDg + row_b, qb);
-    }
-    if (lane == 0) atomicAdd(sDgLast, kt);
-  }
-  __syncthreads();  // everybody is done reading h, dh from shared memory: dw may overwrite h
-  if (ok) {
-    float dw[32];
-    tmem_ld_16x64(tmem + lanes + T_DW + c128, dw);
-    tmem_ld_wait();
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int col = c128 + 8 * i + cp;
-      unsigned char* base = smem + OFF_DW + (col >> 6) * 8192;
-      *reinterpret_cast<uint32_t*>(base + sw128_offset(row_a, col & 63)) = pack_bf16(-dw[4 * i], -dw[4 * i + 1]);
-      *reinterpret_cast<uint32_t*>(base + sw128_offset(row_b, col & 63)) = pack_bf16(-dw[4 * i + 2], -dw[4 * i + 3]);
-    }
-  }
-  fence_proxy_async();
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  stamp();
-
-  // ======================= round 2: ds products, dA pieces, A^T dw, A^T du =======================
-  if (ok && tid == 0) {
-    umma_group<4, 2, 0, 128, 0, false>(tmem + T_DQ2, ds_lo, kmn_lo, ID_KM_128);
-    umma_group<4, 128, 0, 128, 0, false>(tmem + T_DK2, dsmn_lo, qmn_lo, ID_MM_128);
-    umma_group<8, 2, 512, 2, 512, false>(tmem + T_X1, dw_lo, k_lo, ID_KK_64);
-    umma_group<8, 2, 512, 2, 512, false>(tmem + T_X2, du_lo, v_lo, ID_KK_64);
-    umma_group<4, 128, 0, 128, 0, false>(tmem + T_T1, amn_lo, dwmn_lo, ID_MM_128);
-    umma_group<4, 128, 0, 128, 0, false>(tmem + T_T2, amn_lo, dumn_lo, ID_MM_128);
-    umma_commit(&bars[BAR_MMA]);
-  }
-  ok = ok && wait_mma();
-  stamp();
-  const long long out_a = ((row0 + row_a) * p.Hv + hv) * D, out_b = ((row0 + row_b) * p.Hv + hv) * D;
-  const bool wr_a = row_a < valid, wr_b = row_b < valid;
-  if (ok) {
-    {  // dq = dq1 + ds K
-      float x[32];
-      tmem_ld_16x64(tmem + lanes + T_DQ2 + c128, x);
+        for (int i = 0; i < 2; ++i) {
+          const int col = c64 + 8 * i + cp;
+          const float gc0 = sG[col], gc1 = sG[col + 1];
+          const float a0 = col <= row_a ? p.scale * ds[4 * i] * fast_exp(g_a - gc0) : 0.f;
+          const float a1 = col + 1 <= row_a ? p.scale * ds[4 * i + 1] * fast_exp(g_a - gc1) : 0.f;
+          const float b0 = col <= row_b ? p.scale * ds[4 * i + 2] * fast_exp(g_b - gc0) : 0.f;
+          const float b1 = col + 1 <= row_b ? p.scale * ds[4 * i + 3] * fast_exp(g_b - gc1) : 0.f;
+          st_tile64(OFF_DS, row_a, col, a0, a1);
+          st_tile64(OFF_DS, row_b, col, b0, b1);
+          const float s0 = a0 * qk[4 * i], s1 = a1 * qk[4 * i + 1], s2 = b0 * qk[4 * i + 2], s3 = b1 * qk[4 * i + 3];
+          rs_a += s0 + s1;
+          rs_b += s2 + s3;
+          const float c0 = col_sum(s0 + s2), c1 = col_sum(s1 + s3);
+          if (lane < 4) {
+            atomicAdd(sDg + col, -c0);
+            atomicAdd(sDg + col + 1, -c1);
+          }
+        }
+        rs_a = quad_sum(rs_a);
+        rs_b = quad_sum(rs_b);
+        if ((lane & 3) == 0) {
+          atomicAdd(sDg + row_a, rs_a);
+          atomicAdd(sDg + row_b, rs_b);
+        }
+      }
+      // dq1 = scale * gamma * (dO h^T), dg += rowsum(q * dq1)
+      // dk1 = rho * (Vn dh^T), dg -= rowsum(k * dk1), dg_last += sum(k * dk1)
+      tmem_ld_16x32(tmem + lanes + T_DQ1 + c128, dq1);
+      tmem_ld_16x32(tmem + lanes + T_DK1 + c128, dkacc);
       tmem_ld_wait();
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int col = c128 + 8 * i + cp;
-        if (wr_a) *reinterpret_cast<uint32_t*>(p.dq + out_a + col) = pack_bf16(dq1[4 * i] + x[4 * i], dq1[4 * i + 1] + x[4 * i + 1]);
-        if (wr_b) *reinterpret_cast<uint32_t*>(p.dq + out_b + col) = pack_bf16(dq1[4 * i + 2] + x[4 * i + 2], dq1[4 * i + 3] + x[4 * i + 3]);
-      }
-    }
-    {  // dA = strict_lower(beta_c (gamma_c x1 + x2))
-      float x1[16], x2[16];
-      tmem_ld_16x32(tmem + lanes + T_X1 + c64, x1);
-      tmem_ld_16x32(tmem + lanes + T_X2 + c64, x2);
-      tmem_ld_wait();
+      float qa = 0.f, qb = 0.f, ka = 0.f, kb = 0.f;
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const int col = c64 + 8 * i + cp;
-        const float b0 = sBeta[col], b1 = sBeta[col + 1], g0 = sGam[col], g1 = sGam[col + 1];
-        st_tile64(OFF_DA, row_a, col, col < row_a ? b0 * (g0 * x1[4 * i] + x2[4 * i]) : 0.f,
-                  col + 1 < row_a ? b1 * (g1 * x1[4 * i + 1] + x2[4 * i + 1]) : 0.f);
-        st_tile64(OFF_DA, row_b, col, col < row_b ? b0 * (g0 * x1[4 * i + 2] + x2[4 * i + 2]) : 0.f,
-                  col + 1 < row_b ? b1 * (g1 * x1[4 * i + 3] + x2[4 * i + 3]) : 0.f);
+        const int col = c128 + 8 * i + cp;
+        dq1[4 * i] *= p.scale * gam_a;
+        dq1[4 * i + 1] *= p.scale * gam_a;
+        dq1[4 * i + 2] *= p.scale * gam_b;
+        dq1[4 * i + 3] *= p.scale * gam_b;
+        dkacc[4 * i] *= rho_a;
+        dkacc[4 * i + 1] *= rho_a;
+        dkacc[4 * i + 2] *= rho_b;
+        dkacc[4 * i + 3] *= rho_b;
+        const float2 q_a = tile2(OFF_Q, row_a, col), q_b = tile2(OFF_Q, row_b, col);
+        const float2 k_a = tile2(OFF_K, row_a, col), k_b = tile2(OFF_K, row_b, col);
+        qa += q_a.x * dq1[4 * i] + q_a.y * dq1[4 * i + 1];
+        qb += q_b.x * dq1[4 * i + 2] + q_b.y * dq1[4 * i + 3];
+        ka += k_a.x * dkacc[4 * i] + k_a.y * dkacc[4 * i + 1];
+        kb += k_b.x * dkacc[4 * i + 2] + k_b.y * dkacc[4 * i + 3];
+      }
+      qa = quad_sum(qa - ka);
+      qb = quad_sum(qb - kb);
+      float kt = ka + kb;
+#pragma unroll
+      for (int d = 16; d > 0; d >>= 1) kt += __shfl_xor_sync(0xffffffffu, kt, d);
+      if ((lane & 3) == 0) {
+        atomicAdd(sDg + row_a, qa);
+        atomicAdd(sDg + row_b, qb);
+      }
+      if (lane == 0) atomicAdd(sDgLast, kt);
+    }
+    round_sync();
+    stamp();
+
+    // ======================= round 2: ds products, dA pieces, A^T dw, A^T du =======================
+    if (ok && tid == 0) {
+      if (has_next) load_a(nxt);  // h, dh, dO, v_new of this item are dead
+      umma_group<8, 2, 512, 2, 512, false>(tmem + T_X1, dw_lo, k_lo, ID_KK_64);
+      umma_group<8, 2, 512, 2, 512, false>(tmem + T_X2, du_lo, v_lo, ID_KK_64);
+      umma_group<4, 2, 0, 128, 0, false>(tmem + T_DQ2, ds_lo, kmn_lo, ID_KM_128);
+      umma_group<4, 128, 0, 128, 0, false>(tmem + T_DK2, dsmn_lo, qmn_lo, ID_MM_128);
+      umma_group<4, 128, 0, 128, 0, false>(tmem + T_T1, amn_lo, dwmn_lo, ID_MM_128);
+      umma_group<4, 128, 0, 128, 0, false>(tmem + T_T2, amn_lo, dumn_lo, ID_MM_128);
+      umma_commit(&bars[BAR_MMA]);
+    }
+    if (has_next) fetch_vectors(nxt);
+    const long long out_a = ((cur.row0 + row_a) * p.Hv + cur.hv) * D, out_b = ((cur.row0 + row_b) * p.Hv + cur.hv) * D;
+    const bool wr_a = row_a < valid, wr_b = row_b < valid;
+    ok = ok && wait_mma();
+    stamp();
+    if (ok) {
+      {  // dA = strict_lower(beta_c (gamma_c x1 + x2))
+        float x1[8], x2[8];
+        tmem_ld_16x16(tmem + lanes + T_X1 + c64, x1);
+        tmem_ld_16x16(tmem + lanes + T_X2 + c64, x2);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int col = c64 + 8 * i + cp;
+          const float b0 = sBeta[col], b1 = sBeta[col + 1], g0 = sGam[col], g1 = sGam[col + 1];
+          st_tile64(OFF_DA, row_a, col, col < row_a ? b0 * (g0 * x1[4 * i] + x2[4 * i]) : 0.f,
+                    col + 1 < row_a ? b1 * (g1 * x1[4 * i + 1] + x2[4 * i + 1]) : 0.f);
+          st_tile64(OFF_DA, row_b, col, col < row_b ? b0 * (g0 * x1[4 * i + 2] + x2[4 * i + 2]) : 0.f,
+                    col + 1 < row_b ? b1 * (g1 * x1[4 * i + 3] + x2[4 * i + 3]) : 0.f);
+        }
       }
     }
-    {  // dk += ds^T Q + beta gamma (A^T dw);  db += gamma rowsum(t1 k);  dg += beta gamma rowsum(t1 k)
-      float x[32], t1[32];
-      tmem_ld_16x64(tmem + lanes + T_DK2 + c128, x);
-      tmem_ld_16x64(tmem + lanes + T_T1 + c128, t1);
+    // the dA tile is all the next product needs: hand it over before the rest of this round
+    round_sync();
+    if (ok && tid == 0) {
+      umma_group<4, 128, 0, 128, 0, false>(tmem + T_T, amn_lo, damn_lo, ID_MM_64);
+      umma_group<8, 2, 512, 2, 512, false>(tmem + T_KK, k_lo, k_lo, ID_KK_64);
+      umma_commit(&bars[BAR_MMA]);
+    }
+    if (ok) {
+      {  // dq = dq1 + ds K
+        float x[16];
+        tmem_ld_16x32(tmem + lanes + T_DQ2 + c128, x);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int col = c128 + 8 * i + cp;
+          if (wr_a) *reinterpret_cast<uint32_t*>(p.dq + out_a + col) = pack_bf16(dq1[4 * i] + x[4 * i], dq1[4 * i + 1] + x[4 * i + 1]);
+          if (wr_b) *reinterpret_cast<uint32_t*>(p.dq + out_b + col) = pack_bf16(dq1[4 * i + 2] + x[4 * i + 2], dq1[4 * i + 3] + x[4 * i + 3]);
+        }
+      }
+      {  // dk += ds^T Q + beta gamma (A^T dw);  db += gamma rowsum(t1 k);  dg += beta gamma rowsum(t1 k)
+        float x[16], t1[16];
+        tmem_ld_16x32(tmem + lanes + T_DK2 + c128, x);
+        tmem_ld_16x32(tmem + lanes + T_T1 + c128, t1);
+        tmem_ld_wait();
+        float sa = 0.f, sb = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int col = c128 + 8 * i + cp;
+          const float2 k_a = tile2(OFF_K, row_a, col), k_b = tile2(OFF_K, row_b, col);
+          sa += k_a.x * t1[4 * i] + k_a.y * t1[4 * i + 1];
+          sb += k_b.x * t1[4 * i + 2] + k_b.y * t1[4 * i + 3];
+          dkacc[4 * i] += x[4 * i] + beta_a * gam_a * t1[4 * i];
+          dkacc[4 * i + 1] += x[4 * i + 1] + beta_a * gam_a * t1[4 * i + 1];
+          dkacc[4 * i + 2] += x[4 * i + 2] + beta_b * gam_b * t1[4 * i + 2];
+          dkacc[4 * i + 3] += x[4 * i + 3] + beta_b * gam_b * t1[4 * i + 3];
+        }
+        sa = quad_sum(sa);
+        sb = quad_sum(sb);
+        if ((lane & 3) == 0) {
+          atomicAdd(sDb + row_a, gam_a * sa);
+          atomicAdd(sDb + row_b, gam_b * sb);
+          atomicAdd(sDg + row_a, beta_a * gam_a * sa);
+          atomicAdd(sDg + row_b, beta_b * gam_b * sb);
+        }
+      }
+      {  // dv = beta (A^T du);  db += rowsum(t2 v)
+        float t2[16];
+        tmem_ld_16x32(tmem + lanes + T_T2 + c128, t2);
+        tmem_ld_wait();
+        float sa = 0.f, sb = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int col = c128 + 8 * i + cp;
+          const float2 v_a = tile2(OFF_V, row_a, col), v_b = tile2(OFF_V, row_b, col);
+          sa += v_a.x * t2[4 * i] + v_a.y * t2[4 * i + 1];
+          sb += v_b.x * t2[4 * i + 2] + v_b.y * t2[4 * i + 3];
+          if (wr_a) *reinterpret_cast<uint32_t*>(p.dv + out_a + col) = pack_bf16(beta_a * t2[4 * i], beta_a * t2[4 * i + 1]);
+          if (wr_b) *reinterpret_cast<uint32_t*>(p.dv + out_b + col) = pack_bf16(beta_b * t2[4 * i + 2], beta_b * t2[4 * i + 3]);
+        }
+        sa = quad_sum(sa);
+        sb = quad_sum(sb);
+        if ((lane & 3) == 0) {
+          atomicAdd(sDb + row_a, sa);
+          atomicAdd(sDb + row_b, sb);
+        }
+      }
+    }
+    stamp();
+
+    // ======================= round 3: T = A^T dA, K K^T (issued above) =======================
+    ok = ok && wait_mma();
+    stamp();
+    if (ok) {
+      float t[8];
+      tmem_ld_16x16(tmem + lanes + T_T + c64, t);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int col = c64 + 8 * i + cp;
+        st_tile64(OFF_DS, row_a, col, t[4 * i], t[4 * i + 1]);
+        st_tile64(OFF_DS, row_b, col, t[4 * i + 2], t[4 * i + 3]);
+      }
+    }
+    round_sync();
+    stamp();
+
+    // ======================= round 4: d3 = T A^T =======================
+    if (ok && tid == 0) {
+      if (has_next) load_b(nxt);  // du, q, v of this item are dead
+      umma_group<4, 2, 0, 2, 0, false>(tmem + T_D3, ds_lo, a_lo, ID_KK_64);
+      umma_commit(&bars[BAR_MMA]);
+    }
+    ok = ok && wait_mma();
+    stamp();
+    if (ok) {
+      float d3[8], kk[8];
+      tmem_ld_16x16(tmem + lanes + T_D3 + c64, d3);
+      tmem_ld_16x16(tmem + lanes + T_KK + c64, kk);
+      tmem_ld_wait();
+      float rs_a = 0.f, rs_b = 0.f;
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int col = c64 + 8 * i + cp;
+        const float gc0 = sG[col], gc1 = sG[col + 1];
+        const float a0 = col < row_a ? -d3[4 * i] * fast_exp(g_a - gc0) : 0.f;
+        const float a1 = col + 1 < row_a ? -d3[4 * i + 1] * fast_exp(g_a - gc1) : 0.f;
+        const float b0 = col < row_b ? -d3[4 * i + 2] * fast_exp(g_b - gc0) : 0.f;
+        const float b1 = col + 1 < row_b ? -d3[4 * i + 3] * fast_exp(g_b - gc1) : 0.f;
+        st_tile64(OFF_D3, row_a, col, a0, a1);
+        st_tile64(OFF_D3, row_b, col, b0, b1);
+        st_tile64(OFF_D3B, row_a, col, beta_a * a0, beta_a * a1);
+        st_tile64(OFF_D3B, row_b, col, beta_b * b0, beta_b * b1);
+        const float s0 = a0 * beta_a * kk[4 * i], s1 = a1 * beta_a * kk[4 * i + 1];
+        const float s2 = b0 * beta_b * kk[4 * i + 2], s3 = b1 * beta_b * kk[4 * i + 3];
+        rs_a += s0 + s1;
+        rs_b += s2 + s3;
+        const float c0 = col_sum(s0 + s2), c1 = col_sum(s1 + s3);
+        if (lane < 4) {
+          atomicAdd(sDg + col, -c0);
+          atomicAdd(sDg + col + 1, -c1);
+        }
+      }
+      rs_a = quad_sum(rs_a);
+      rs_b = quad_sum(rs_b);
+      if ((lane & 3) == 0) {
+        atomicAdd(sDg + row_a, rs_a);
+        atomicAdd(sDg + row_b, rs_b);
+      }
+    }
+    round_sync();
+    stamp();
+
+    // ======================= round 5: dA3 K and (beta dA3)^T K =======================
+    if (ok && tid == 0) {
+      umma_group<4, 2, 0, 128, 0, false>(tmem + T_T3, d3_lo, kmn_lo, ID_KM_128);
+      umma_group<4, 128, 0, 128, 0, false>(tmem + T_DK5, d3bmn_lo, kmn_lo, ID_MM_128);
+      umma_commit(&bars[BAR_MMA]);
+    }
+    ok = ok && wait_mma();
+    stamp();
+    if (ok) {
+      float t3[16], x[16];
+      tmem_ld_16x32(tmem + lanes + T_T3 + c128, t3);
+      tmem_ld_16x32(tmem + lanes + T_DK5 + c128, x);
       tmem_ld_wait();
       float sa = 0.f, sb = 0.f;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
+      for (int i = 0; i < 4; ++i) {
         const int col = c128 + 8 * i + cp;
         const float2 k_a = tile2(OFF_K, row_a, col), k_b = tile2(OFF_K, row_b, col);
-        sa += k_a.x * t1[4 * i] + k_a.y * t1[4 * i + 1];
-        sb += k_b.x * t1[4 * i + 2] + k_b.y * t1[4 * i + 3];
-        dkacc[4 * i] += x[4 * i] + beta_a * gam_a * t1[4 * i];
-        dkacc[4 * i + 1] += x[4 * i + 1] + beta_a * gam_a * t1[4 * i + 1];
-        dkacc[4 * i + 2] += x[4 * i + 2] + beta_b * gam_b * t1[4 * i + 2];
-        dkacc[4 * i + 3] += x[4 * i + 3] + beta_b * gam_b * t1[4 * i + 3];
-      }
-      sa = quad_sum(sa);
-      sb = quad_sum(sb);
-      if ((lane & 3) == 0) {
-        atomicAdd(sDb + row_a, gam_a * sa);
-        atomicAdd(sDb + row_b, gam_b * sb);
-        atomicAdd(sDg + row_a, beta_a * gam_a * sa);
-        atomicAdd(sDg + row_b, beta_b * gam_b * sb);
-      }
-    }
-    {  // dv = beta (A^T du);  db += rowsum(t2 v)
-      float t2[32];
-      tmem_ld_16x64(tmem + lanes + T_T2 + c128, t2);
-      tmem_ld_wait();
-      float sa = 0.f, sb = 0.f;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int col = c128 + 8 * i + cp;
-        const float2 v_a = tile2(OFF_V, row_a, col), v_b = tile2(OFF_V, row_b, col);
-        sa += v_a.x * t2[4 * i] + v_a.y * t2[4 * i + 1];
-        sb += v_b.x * t2[4 * i + 2] + v_b.y * t2[4 * i + 3];
-        if (wr_a) *reinterpret_cast<uint32_t*>(p.dv + out_a + col) = pack_bf16(beta_a * t2[4 * i], beta_a * t2[4 * i + 1]);
-        if (wr_b) *reinterpret_cast<uint32_t*>(p.dv + out_b + col) = pack_bf16(beta_b * t2[4 * i + 2], beta_b * t2[4 * i + 3]);
+        sa += k_a.x * t3[4 * i] + k_a.y * t3[4 * i + 1];
+        sb += k_b.x * t3[4 * i + 2] + k_b.y * t3[4 * i + 3];
+        if (wr_a)
+          *reinterpret_cast<uint32_t*>(p.dk + out_a + col) =
+              pack_bf16(dkacc[4 * i] + beta_a * t3[4 * i] + x[4 * i], dkacc[4 * i + 1] + beta_a * t3[4 * i + 1] + x[4 * i + 1]);
+        if (wr_b)
+          *reinterpret_cast<uint32_t*>(p.dk + out_b + col) =
+              pack_bf16(dkacc[4 * i + 2] + beta_b * t3[4 * i + 2] + x[4 * i + 2], dkacc[4 * i + 3] + beta_b * t3[4 * i + 3] + x[4 * i + 3]);
       }
       sa = quad_sum(sa);
       sb = quad_sum(sb);
@@ -445,129 +630,23 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
         atomicAdd(sDb + row_b, sb);
       }
     }
-  }
-  fence_proxy_async();
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  stamp();
-
-  // ======================= round 3: T = A^T dA, K K^T =======================
-  if (ok && tid == 0) {
-    umma_group<4, 128, 0, 128, 0, false>(tmem + T_T, amn_lo, damn_lo, ID_MM_64);
-    umma_group<8, 2, 512, 2, 512, false>(tmem + T_KK, k_lo, k_lo, ID_KK_64);
-    umma_commit(&bars[BAR_MMA]);
-  }
-  ok = ok && wait_mma();
-  stamp();
-  if (ok) {
-    float t[16];
-    tmem_ld_16x32(tmem + lanes + T_T + c64, t);
-    tmem_ld_wait();
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int col = c64 + 8 * i + cp;
-      st_tile64(OFF_DS, row_a, col, t[4 * i], t[4 * i + 1]);
-      st_tile64(OFF_DS, row_b, col, t[4 * i + 2], t[4 * i + 3]);
-    }
-  }
-  fence_proxy_async();
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  stamp();
-
-  // ======================= round 4: d3 = T A^T =======================
-  if (ok && tid == 0) {
-    umma_group<4, 2, 0, 2, 0, false>(tmem + T_D3, ds_lo, a_lo, ID_KK_64);
-    umma_commit(&bars[BAR_MMA]);
-  }
-  ok = ok && wait_mma();
-  stamp();
-  if (ok) {
-    float d3[16], kk[16];
-    tmem_ld_16x32(tmem + lanes + T_D3 + c64, d3);
-    tmem_ld_16x32(tmem + lanes + T_KK + c64, kk);
-    tmem_ld_wait();
-    float rs_a = 0.f, rs_b = 0.f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int col = c64 + 8 * i + cp;
-      const float gc0 = sG[col], gc1 = sG[col + 1];
-      const float a0 = col < row_a ? -d3[4 * i] * fast_exp(g_a - gc0) : 0.f;
-      const float a1 = col + 1 < row_a ? -d3[4 * i + 1] * fast_exp(g_a - gc1) : 0.f;
-      const float b0 = col < row_b ? -d3[4 * i + 2] * fast_exp(g_b - gc0) : 0.f;
-      const float b1 = col + 1 < row_b ? -d3[4 * i + 3] * fast_exp(g_b - gc1) : 0.f;
-      st_tile64(OFF_D3, row_a, col, a0, a1);
-      st_tile64(OFF_D3, row_b, col, b0, b1);
-      st_tile64(OFF_D3B, row_a, col, beta_a * a0, beta_a * a1);
-      st_tile64(OFF_D3B, row_b, col, beta_b * b0, beta_b * b1);
-      const float s0 = a0 * beta_a * kk[4 * i], s1 = a1 * beta_a * kk[4 * i + 1];
-      const float s2 = b0 * beta_b * kk[4 * i + 2], s3 = b1 * beta_b * kk[4 * i + 3];
-      rs_a += s0 + s1;
-      rs_b += s2 + s3;
-      const float c0 = col_sum(s0 + s2), c1 = col_sum(s1 + s3);
-      if (lane < 4) {
-        atomicAdd(sDg + col, -c0);
-        atomicAdd(sDg + col + 1, -c1);
+    tc_fence_before();
+    ok = __syncthreads_and(ok);  // a wait given up by one thread ends the loop for all of them
+    tc_fence_after();
+    stamp();
+    if (ok && tid == 0 && has_next) load_c(nxt);  // k, A of this item are dead
+    if (tid < valid) {
+      float dgv = sDg[tid];
+      if (tid == valid - 1) {  // the only reader of the chunk total also clears it for the next item
+        dgv += *sDgLast;
+        *sDgLast = 0.f;
       }
+      p.dg[(cur.row0 + tid) * p.Hv + cur.hv] = dgv;
+      p.db[(cur.row0 + tid) * p.Hv + cur.hv] = sDb[tid];
     }
-    rs_a = quad_sum(rs_a);
-    rs_b = quad_sum(rs_b);
-    if ((lane & 3) == 0) {
-      atomicAdd(sDg + row_a, rs_a);
-      atomicAdd(sDg + row_b, rs_b);
-    }
+    cur = nxt;
   }
-  fence_proxy_async();
-  tc_fence_before();
   __syncthreads();
-  tc_fence_after();
-  stamp();
-
-  // ======================= round 5: dA3 K and (beta dA3)^T K =======================
-  if (ok && tid == 0) {
-    umma_group<4, 2, 0, 128, 0, false>(tmem + T_T3, d3_lo, kmn_lo, ID_KM_128);
-    umma_group<4, 128, 0, 128, 0, false>(tmem + T_DK5, d3bmn_lo, kmn_lo, ID_MM_128);
-    umma_commit(&bars[BAR_MMA]);
-  }
-  ok = ok && wait_mma();
-  stamp();
-  if (ok) {
-    float t3[32], x[32];
-    tmem_ld_16x64(tmem + lanes + T_T3 + c128, t3);
-    tmem_ld_16x64(tmem + lanes + T_DK5 + c128, x);
-    tmem_ld_wait();
-    float sa = 0.f, sb = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int col = c128 + 8 * i + cp;
-      const float2 k_a = tile2(OFF_K, row_a, col), k_b = tile2(OFF_K, row_b, col);
-      sa += k_a.x * t3[4 * i] + k_a.y * t3[4 * i + 1];
-      sb += k_b.x * t3[4 * i + 2] + k_b.y * t3[4 * i + 3];
-      if (wr_a)
-        *reinterpret_cast<uint32_t*>(p.dk + out_a + col) =
-            pack_bf16(dkacc[4 * i] + beta_a * t3[4 * i] + x[4 * i], dkacc[4 * i + 1] + beta_a * t3[4 * i + 1] + x[4 * i + 1]);
-      if (wr_b)
-        *reinterpret_cast<uint32_t*>(p.dk + out_b + col) =
-            pack_bf16(dkacc[4 * i + 2] + beta_b * t3[4 * i + 2] + x[4 * i + 2], dkacc[4 * i + 3] + beta_b * t3[4 * i + 3] + x[4 * i + 3]);
-    }
-    sa = quad_sum(sa);
-    sb = quad_sum(sb);
-    if ((lane & 3) == 0) {
-      atomicAdd(sDb + row_a, sa);
-      atomicAdd(sDb + row_b, sb);
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  stamp();
-  if (ok && tid < valid) {
-    float dgv = sDg[tid];
-    if (tid == valid - 1) dgv += *sDgLast;
-    p.dg[(row0 + tid) * p.Hv + hv] = dgv;
-    p.db[(row0 + tid) * p.Hv + hv] = sDb[tid];
-  }
   if (warp == 0) tmem_dealloc(tmem, 512);
   if (tid == 0 && (*abort_flag || !ok)) atomicCAS(&g_bwd_main_status, 0, 1);
 }
@@ -636,12 +715,20 @@ int launch_bwd_main_tc(const void* q, const void* k, const void* v, const void* 
   p.g = g; p.beta = beta; p.beta_is_f32 = beta_is_f32;
   p.dq = (bf16*)dq; p.dk = (bf16*)dk; p.dv = (bf16*)dv; p.db = db; p.dg = dg;
   p.Hq = Hq; p.Hv = Hv; p.scale = scale; p.lay = lay; p.chunk_indices = chunk_indices;
+  p.n_chunks = n_chunks;
   static const bool profile = getenv("FQLA_PROFILE") != nullptr;
   p.profile = profile;
   rc = configure_smem((const void*)bwd_main_tc_kernel, SMEM_BYTES);
   if (rc != 0) return rc;
-  bwd_main_tc_kernel<<<dim3((unsigned)n_chunks, Hv), 256, SMEM_BYTES, st>>>(p, mq, mk, mv, mvn, mdo,
-                                                                            mdu, mh, mdh, ma);
+  static const int n_sm = [] {
+    int dev = 0, n = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    return n > 0 ? n : 148;
+  }();
+  const long long total = n_chunks * Hv;
+  const unsigned grid = (unsigned)(total < n_sm ? total : n_sm);
+  bwd_main_tc_kernel<<<grid, NT, SMEM_BYTES, st>>>(p, mq, mk, mv, mvn, mdo, mdu, mh, mdh, ma);
   return (int)cudaGetLastError();
 }
 
