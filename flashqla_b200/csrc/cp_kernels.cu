@@ -93,14 +93,28 @@ __global__ void __launch_bounds__(D) merge_kernel(const float* __restrict__ loca
   }
   __syncthreads();
   const int n = s1 - s0;
+  // the local state (and the flag) of the next step are fetched one step ahead into registers:
+  // the chain itself then only waits for shared memory
+  constexpr int RPW = D / (D / 32);  // rows per warp
+  float pre[RPW];
+  int pre_m = 0;
+  auto prefetch = [&](int step) {
+    const int i = reverse ? s1 - 1 - step : s0 + step;
+    const float* loc = state(local, i);
+#pragma unroll
+    for (int t = 0; t < RPW; ++t) pre[t] = loc[(long long)(warp + t * (D / 32)) * D + v0 + lane];
+    pre_m = use_m == nullptr ? 1 : use_m[i * Hv + hv];
+  };
+  if (n > 1) prefetch(0);
   for (int step = 0; step < n; ++step) {
     const int i = reverse ? s1 - 1 - step : s0 + step;
     float* dst = const_cast<float*>(state(out, i));
     for (int row = warp; row < D; row += D / 32) dst[(long long)row * D + v0 + lane] = cur[row * LDC + lane];
     if (step == n - 1) break;
-    const float* loc = state(local, i);
-    for (int row = warp; row < D; row += D / 32) panel[row * LDC + lane] = loc[(long long)row * D + v0 + lane];
-    const bool with_m = use_m == nullptr || use_m[i * Hv + hv] != 0;
+#pragma unroll
+    for (int t = 0; t < RPW; ++t) panel[(warp + t * (D / 32)) * LDC + lane] = pre[t];
+    const bool with_m = pre_m != 0;
+    if (step + 1 < n - 1) prefetch(step + 1);
     __syncthreads();
     float acc[BV];
 #pragma unroll
