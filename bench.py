@@ -343,6 +343,11 @@ def run_ours(args):
     for _ in range(3):
         dominant()
     k_ms = timed(dominant, args.steps) / args.steps
+    # DRAM bytes per (token, value head) of one launch, from the ncu capture of the quarter-size
+    # workload (profiles/kernels__c1_quarter.md: read + write counters / 131072 pairs); traffic
+    # grows in proportion to the pairs processed
+    traffic_per_th = {"fwd_tc_kernel": 141.1e6 / 131072, "bwd_main_tc_kernel": 431.1e6 / 131072}
+    traffic = traffic_per_th[kernel_name] * tokens * x["Hv"] if G == 1 else None
     alg_bytes = tokens * x["Hv"] * bytes_per_th
     peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(peaks_path):
@@ -352,7 +357,10 @@ def run_ours(args):
     achieved = alg_bytes / (k_ms * 1e-3) / 1e9
     roofline = {"kernel": kernel_name, "bound": "hbm", "achieved": round(achieved, 1),
                 "peak": peak, "peak_source": peak_src, "unit": "GB/s",
-                "frac": round(achieved / peak, 4), "traffic": None,
+                "frac": round(achieved / peak, 4),
+                "traffic": None if traffic is None else round(traffic),
+                "traffic_source": "ncu dram__bytes_read+write on c1_quarter, scaled by (token, head) pairs",
+                "algorithmic_bytes": round(alg_bytes),
                 "kernel_ms": round(k_ms, 4),
                 "tensor_tflops": round(tokens * x["Hv"] * flop_per_th / (k_ms * 1e-3) / 1e12, 1)}
 

@@ -290,6 +290,12 @@ static int launch_bwd_dh(const BwdDhParams& p, cudaStream_t st) {
   return (int)cudaGetLastError();
 }
 
+// tcgen05 version for K = V = 128, full walks only (bwd_dh_tc.cu)
+int launch_bwd_dh_tc(const void* q, const void* k, const void* A, const float* g, const void* beta,
+                     int beta_is_f32, const void* dO, const float* dht, void* dh, void* du,
+                     float* dh0, int N, int Hq, int Hv, long long T_rows, float scale,
+                     SeqLayout lay, cudaStream_t st);
+
 }  // namespace fqla
 
 using namespace fqla;
@@ -311,6 +317,10 @@ extern "C" int fqla_bwd_dh(const void* q, const void* k, const void* A, const fl
   p.lay = SeqLayout{{cu_seqlens, idx_is64}, {chunk_offsets, idx_is64}, T};
   if (p.N <= 0) return FQLA_OK;
   cudaStream_t st = (cudaStream_t)stream;
+  static const bool force_legacy = getenv("FQLA_FORCE_MMA_SYNC") != nullptr;
+  if (D == 128 && !warm_chunks && !force_legacy)
+    return launch_bwd_dh_tc(q, k, A, g_cum, beta, beta_is_f32, dO, dht, dh, du, dh0, p.N, Hq, Hv,
+                            (long long)B * T, scale, p.lay, st);
   if (D == 128) return launch_bwd_dh<128>(p, st);
   if (D == 64) return launch_bwd_dh<64>(p, st);
   return FQLA_ERR_UNSUPPORTED_DIM;

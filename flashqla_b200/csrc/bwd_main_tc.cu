@@ -675,7 +675,8 @@ typedef CUresult (*EncodeTiledFn2)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
                                    const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-static int make_map2(CUtensorMap* m, const void* ptr, long long rows, long long cols, int box_rows) {
+// 2-D bf16 tensor map, rows x cols (row-major), box = 64 columns x box_rows rows, 128-byte swizzle
+int make_tile_map(CUtensorMap* m, const void* ptr, long long rows, long long cols, int box_rows) {
   static EncodeTiledFn2 fn = [] {
     void* f = nullptr;
     cudaDriverEntryPointQueryResult q;
@@ -702,15 +703,15 @@ int launch_bwd_main_tc(const void* q, const void* k, const void* v, const void* 
   using namespace bmtc;
   CUtensorMap mq, mk, mv, mvn, mdo, mdu, mh, mdh, ma;
   int rc;
-  if ((rc = make_map2(&mq, q, T_rows, (long long)Hq * D, 64))) return rc;
-  if ((rc = make_map2(&mk, k, T_rows, (long long)Hq * D, 64))) return rc;
-  if ((rc = make_map2(&mv, v, T_rows, (long long)Hv * D, 64))) return rc;
-  if ((rc = make_map2(&mvn, vnew, T_rows, (long long)Hv * D, 64))) return rc;
-  if ((rc = make_map2(&mdo, dO, T_rows, (long long)Hv * D, 64))) return rc;
-  if ((rc = make_map2(&mdu, du, T_rows, (long long)Hv * D, 64))) return rc;
-  if ((rc = make_map2(&mh, h, n_chunks * Hv * D, D, 128))) return rc;
-  if ((rc = make_map2(&mdh, dh, n_chunks * Hv * D, D, 128))) return rc;
-  if ((rc = make_map2(&ma, A, T_rows, (long long)Hv * CHUNK, 64))) return rc;
+  if ((rc = make_tile_map(&mq, q, T_rows, (long long)Hq * D, 64))) return rc;
+  if ((rc = make_tile_map(&mk, k, T_rows, (long long)Hq * D, 64))) return rc;
+  if ((rc = make_tile_map(&mv, v, T_rows, (long long)Hv * D, 64))) return rc;
+  if ((rc = make_tile_map(&mvn, vnew, T_rows, (long long)Hv * D, 64))) return rc;
+  if ((rc = make_tile_map(&mdo, dO, T_rows, (long long)Hv * D, 64))) return rc;
+  if ((rc = make_tile_map(&mdu, du, T_rows, (long long)Hv * D, 64))) return rc;
+  if ((rc = make_tile_map(&mh, h, n_chunks * Hv * D, D, 128))) return rc;
+  if ((rc = make_tile_map(&mdh, dh, n_chunks * Hv * D, D, 128))) return rc;
+  if ((rc = make_tile_map(&ma, A, T_rows, (long long)Hv * CHUNK, 64))) return rc;
   BwdMainTcParams p;
   p.g = g; p.beta = beta; p.beta_is_f32 = beta_is_f32;
   p.dq = (bf16*)dq; p.dk = (bf16*)dk; p.dv = (bf16*)dv; p.db = db; p.dg = dg;

@@ -731,15 +731,19 @@ extern "C" int fqla_debug_wait_profile(long long* out168) {
 
 namespace fqla {
 int bwd_main_tc_status(int* out, int reset);
+int bwd_dh_tc_status(int* out, int reset);
 }
 
 extern "C" int fqla_device_status(int* out, int reset) {
   int v = 0, w = 0;
   cudaError_t e = cudaMemcpyFromSymbol(&v, fqla::g_device_status, sizeof(int));
   if (e != cudaSuccess) return (int)e;
+  int u = 0;
   int rc = fqla::bwd_main_tc_status(&w, reset);
   if (rc != 0) return rc;
-  if (out) *out = v | w;
+  rc = fqla::bwd_dh_tc_status(&u, reset);
+  if (rc != 0) return rc;
+  if (out) *out = v | w | u;
   if (reset && v != 0) {
     int z = 0;
     e = cudaMemcpyToSymbol(fqla::g_device_status, &z, sizeof(int));
