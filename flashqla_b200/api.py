@@ -15,6 +15,8 @@ Pipeline (all launches on the current CUDA stream):
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import cp, ops
@@ -147,11 +149,15 @@ def chunk_gated_delta_rule_bwd(
     else:
         run_tables, run_h0, run_dht = tables, h0, dht_k
 
+    # K = V = 128: the sequential kernels hand h, v_new, dh, du to the chunk-parallel kernel as
+    # ready-made operand tiles (written by TMA), not as row-major tensors
+    tiles = D == 128 and os.environ.get("FQLA_FORCE_MMA_SYNC") is None
     fw = ops.fwd_seq(None, k, v, A, g, beta_k, scale, run_h0, output_o=False, output_h=True,
-                     output_vnew=True, tables=run_tables)
-    bw = ops.bwd_dh(q, k, A, g, beta_k, do, scale, run_dht, tables=run_tables)
+                     output_vnew=True, tables=run_tables, operand_tiles=tiles)
+    bw = ops.bwd_dh(q, k, A, g, beta_k, do, scale, run_dht, tables=run_tables,
+                    operand_tiles=tiles)
     dq, dk, dv, db, dg = ops.bwd_main(q, k, v, fw["vnew"], A, g, beta_k, do, bw["du"], fw["h"],
-                                      bw["dh"], scale, tables=run_tables)
+                                      bw["dh"], scale, tables=run_tables, operand_tiles=tiles)
     dh0 = bw["dh0"]
     if plan is not None:
         dh0 = dh0[plan.first_seg_of_raw]

@@ -293,7 +293,7 @@ static int launch_bwd_dh(const BwdDhParams& p, cudaStream_t st) {
 // tcgen05 version for K = V = 128, full walks only (bwd_dh_tc.cu)
 int launch_bwd_dh_tc(const void* q, const void* k, const void* A, const float* g, const void* beta,
                      int beta_is_f32, const void* dO, const float* dht, void* dh, void* du,
-                     float* dh0, int N, int Hq, int Hv, long long T_rows, float scale,
+                     float* dh0, int tiled, int N, int Hq, int Hv, long long T_rows, float scale,
                      SeqLayout lay, cudaStream_t st);
 
 }  // namespace fqla
@@ -304,7 +304,8 @@ extern "C" int fqla_bwd_dh(const void* q, const void* k, const void* A, const fl
                            const void* beta, int beta_is_f32, const void* dO, const float* dht,
                            void* dh, void* du, float* dh0, const int* warm_chunks, int B, int T,
                            int Hq, int Hv, int D, float scale, const void* cu_seqlens,
-                           const void* chunk_offsets, int idx_is64, int N, void* stream) {
+                           const void* chunk_offsets, int idx_is64, int N, int operand_tiles,
+                           void* stream) {
   if (!q || !k || !A || !g_cum || !beta || !dO || Hq <= 0 || Hv % Hq)
     return FQLA_ERR_INVALID_ARG;
   if (cu_seqlens && (!chunk_offsets || B != 1)) return FQLA_ERR_INVALID_ARG;
@@ -319,8 +320,9 @@ extern "C" int fqla_bwd_dh(const void* q, const void* k, const void* A, const fl
   cudaStream_t st = (cudaStream_t)stream;
   static const bool force_legacy = getenv("FQLA_FORCE_MMA_SYNC") != nullptr;
   if (D == 128 && !warm_chunks && !force_legacy)
-    return launch_bwd_dh_tc(q, k, A, g_cum, beta, beta_is_f32, dO, dht, dh, du, dh0, p.N, Hq, Hv,
-                            (long long)B * T, scale, p.lay, st);
+    return launch_bwd_dh_tc(q, k, A, g_cum, beta, beta_is_f32, dO, dht, dh, du, dh0,
+                            operand_tiles, p.N, Hq, Hv, (long long)B * T, scale, p.lay, st);
+  if (operand_tiles) return FQLA_ERR_UNSUPPORTED_DIM;  // only the tcgen05 kernel writes tiles
   if (D == 128) return launch_bwd_dh<128>(p, st);
   if (D == 64) return launch_bwd_dh<64>(p, st);
   return FQLA_ERR_UNSUPPORTED_DIM;

@@ -40,6 +40,7 @@ struct BwdDhTcParams {
   int N, Hq, Hv;
   float scale;
   SeqLayout lay;
+  int tiled;  // dh and du are written as operand tiles (dh^T, du^T per chunk) by TMA
 };
 
 namespace bdtc {
@@ -73,7 +74,8 @@ __device__ __forceinline__ uint32_t scale2(uint32_t packed, float lo, float hi) 
 __global__ void __launch_bounds__(512, 1)
 bwd_dh_tc_kernel(const BwdDhTcParams p, const __grid_constant__ CUtensorMap map_q,
                  const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_do,
-                 const __grid_constant__ CUtensorMap map_a) {
+                 const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_dh,
+                 const __grid_constant__ CUtensorMap map_du) {
   using namespace bdtc;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
@@ -162,7 +164,7 @@ bwd_dh_tc_kernel(const BwdDhTcParams p, const __grid_constant__ CUtensorMap map_
               make_uint4(pack_bf16(y[8 * cc + 0], y[8 * cc + 1]), pack_bf16(y[8 * cc + 2], y[8 * cc + 3]),
                          pack_bf16(y[8 * cc + 4], y[8 * cc + 5]), pack_bf16(y[8 * cc + 6], y[8 * cc + 7]));
         }
-        if (hdst) {
+        if (hdst && !p.tiled) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             hdst[(long long)(kb * 64 + j) * D + v] = __float2bfloat16(x[j]);
@@ -268,7 +270,7 @@ bwd_dh_tc_kernel(const BwdDhTcParams p, const __grid_constant__ CUtensorMap map_
           tc_fence_before();
           mbar_arrive(&bars[DV_READY]);
         }
-        if (p.du) {
+        if (p.du && !p.tiled) {
 #pragma unroll
           for (int j = 0; j < 32; ++j)
             if (32 * h + j < valid)
@@ -362,7 +364,14 @@ bwd_dh_tc_kernel(const BwdDhTcParams p, const __grid_constant__ CUtensorMap map_
         tc_fence_after();
         // X1^T = dS^T K^T   (on the chain)
         umma_group<8, 2, 1024, 2, 512, false>(tmem + TM_X1, st_lo, k0_lo + so, ID_X1);
+        tma_store_wait_read();  // du^T of the chunk before has left its tile
         umma_commit(&bars[X1_DONE]);
+        const int y_tile = (int)(((sp.chunk_base + (n_it - 1 - it)) * p.Hv + hv) * D);
+        if (p.tiled && p.dh) {  // the operand copy of dS^T is dh of this chunk
+          tma_store_2d(&map_dh, 0, y_tile, smem + OFF_ST);
+          tma_store_2d(&map_dh, 64, y_tile, smem + OFF_ST + 16384);
+          tma_store_commit();
+        }
         if (it + 1 < n_it) {
           ok = WAIT(FULL0 + (s ^ 1), ((it + 1) >> 1) & 1);
           if (!ok) break;
@@ -375,7 +384,12 @@ bwd_dh_tc_kernel(const BwdDhTcParams p, const __grid_constant__ CUtensorMap map_
         // dS^T <- dS^T - dv^T w + dO^T (scale gamma q)
         umma_group<4, 2, 0, 128, 0, true>(tmem + TM_S, dvt_lo, wmn_lo, ID_UPD_W);
         umma_group<4, 128, 0, 128, 0, true>(tmem + TM_S, domn0_lo + so, qsmn_lo, ID_UPD_Q);
+        tma_store_wait_read();  // the dS^T tile may be rewritten after this
         umma_commit(&bars[S_DONE]);
+        if (p.tiled && p.du) {
+          tma_store_2d(&map_du, 0, y_tile, smem + OFF_DVT);
+          tma_store_commit();
+        }
         umma_commit(&bars[EMPTY0 + s]);
         if (it + 1 < n_it) {
           ok = WAIT(AP_READY, (it + 1) & 1);
@@ -388,6 +402,7 @@ bwd_dh_tc_kernel(const BwdDhTcParams p, const __grid_constant__ CUtensorMap map_
           issue_x2(so_next);
         }
       }
+      tma_store_wait_all();
     }
   } else if (warp == 1) {
     // =============================== producer ===============================
@@ -528,22 +543,31 @@ int make_tile_map(CUtensorMap* m, const void* ptr, long long rows, long long col
 
 int launch_bwd_dh_tc(const void* q, const void* k, const void* A, const float* g, const void* beta,
                      int beta_is_f32, const void* dO, const float* dht, void* dh, void* du,
-                     float* dh0, int N, int Hq, int Hv, long long T_rows, float scale,
+                     float* dh0, int tiled, int N, int Hq, int Hv, long long T_rows, float scale,
                      SeqLayout lay, cudaStream_t st) {
   using namespace bdtc;
-  CUtensorMap mq, mk, mdo, ma;
+  CUtensorMap mq, mk, mdo, ma, mdh, mdu;
   int rc;
   if ((rc = make_tile_map(&mq, q, T_rows, (long long)Hq * D, 64))) return rc;
   if ((rc = make_tile_map(&mk, k, T_rows, (long long)Hq * D, 64))) return rc;
   if ((rc = make_tile_map(&mdo, dO, T_rows, (long long)Hv * D, 64))) return rc;
   if ((rc = make_tile_map(&ma, A, T_rows, (long long)Hv * CHUNK, 64))) return rc;
+  mdh = mq;
+  mdu = mq;
+  if (tiled) {
+    // an upper bound of the chunk count: the maps only have to cover what the kernel stores
+    const long long max_chunks = (T_rows + CHUNK - 1) / CHUNK + N;
+    if (dh && (rc = make_tile_map(&mdh, dh, max_chunks * Hv * D, D, 128))) return rc;
+    if (du && (rc = make_tile_map(&mdu, du, max_chunks * Hv * D, CHUNK, 128))) return rc;
+  }
   BwdDhTcParams p;
+  p.tiled = tiled;
   p.g = g; p.beta = beta; p.beta_is_f32 = beta_is_f32; p.dht = dht;
   p.dh = (bf16*)dh; p.du = (bf16*)du; p.dh0 = dh0;
   p.N = N; p.Hq = Hq; p.Hv = Hv; p.scale = scale; p.lay = lay;
   rc = configure_smem((const void*)bwd_dh_tc_kernel, SMEM_BYTES);
   if (rc != 0) return rc;
-  bwd_dh_tc_kernel<<<(unsigned)(N * Hv), 512, SMEM_BYTES, st>>>(p, mq, mk, mdo, ma);
+  bwd_dh_tc_kernel<<<(unsigned)(N * Hv), 512, SMEM_BYTES, st>>>(p, mq, mk, mdo, ma, mdh, mdu);
   return (int)cudaGetLastError();
 }
 

@@ -479,7 +479,7 @@ static int launch_bwd_main(const BwdMainParams& p, long long n_chunks, cudaStrea
 int launch_bwd_main_tc(const void* q, const void* k, const void* v, const void* vnew, const void* A,
                        const float* g, const void* beta, int beta_is_f32, const void* dO,
                        const void* du, const void* h, const void* dh, void* dq, void* dk, void* dv,
-                       float* db, float* dg, int Hq, int Hv, long long T_rows, long long n_chunks,
+                       float* db, float* dg, int tiled, int Hq, int Hv, long long T_rows, long long n_chunks,
                        float scale, SeqLayout lay, IndexTable chunk_indices, cudaStream_t st);
 }  // namespace fqla
 using namespace fqla;
@@ -491,7 +491,7 @@ extern "C" int fqla_bwd_main(const void* q, const void* k, const void* v, const 
                              int B, int T, int Hq, int Hv, int D, float scale,
                              const void* cu_seqlens, const void* chunk_offsets,
                              const void* chunk_indices, int idx_is64, long long num_chunks,
-                             void* stream) {
+                             int operand_tiles, void* stream) {
   if (!q || !k || !v || !vnew || !A || !g_cum || !beta || !dO || !du || !h || !dh || !dq ||
       !dk || !dv || !db || !dg || Hq <= 0 || Hv % Hq)
     return FQLA_ERR_INVALID_ARG;
@@ -510,7 +510,9 @@ extern "C" int fqla_bwd_main(const void* q, const void* k, const void* v, const 
   static const bool force_legacy = getenv("FQLA_FORCE_MMA_SYNC") != nullptr;
   if (D == 128 && !force_legacy)
     return launch_bwd_main_tc(q, k, v, vnew, A, g_cum, beta, beta_is_f32, dO, du, h, dh, dq, dk, dv,
-                              db, dg, Hq, Hv, (long long)B * T, n, scale, p.lay, p.chunk_indices, st);
+                              db, dg, operand_tiles, Hq, Hv, (long long)B * T, n, scale, p.lay,
+                              p.chunk_indices, st);
+  if (operand_tiles) return FQLA_ERR_UNSUPPORTED_DIM;  // only the tcgen05 kernel reads tiles
   if (D == 128) return launch_bwd_main<128>(p, n, st);
   if (D == 64) return launch_bwd_main<64>(p, n, st);
   return FQLA_ERR_UNSUPPORTED_DIM;

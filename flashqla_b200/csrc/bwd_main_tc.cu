@@ -103,6 +103,9 @@ __device__ __forceinline__ void tmem_ld_16x16(uint32_t taddr, float (&v)[8]) {
 
 // Persistent: CTA b handles work items b, b + gridDim.x, ...; item w = (chunk w / Hv, head w % Hv),
 // so neighbouring CTAs share q and k of a grouped-value-attention group through L2.
+// TILED: h, dh, vnew and du arrive in the operand layouts written by the sequential kernels
+// (h^T, dh^T as [V][K] per chunk; vnew^T, du^T as [V][64] per chunk) instead of row-major.
+template <bool TILED>
 __global__ void __launch_bounds__(bmtc::NT, 1)
 bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap map_q,
                    const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
@@ -158,16 +161,24 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
     tma_load_2d(smem + OFF_DO + 8192, &map_do, t.hv * D + 64, y, &bars[BAR_LOAD_A]);
     tma_load_2d(smem + OFF_H, &map_h, 0, ys, &bars[BAR_LOAD_A]);
     tma_load_2d(smem + OFF_H + 16384, &map_h, 64, ys, &bars[BAR_LOAD_A]);
-    tma_load_2d(smem + OFF_VN, &map_vn, t.hv * D, y, &bars[BAR_LOAD_A]);
-    tma_load_2d(smem + OFF_VN + 8192, &map_vn, t.hv * D + 64, y, &bars[BAR_LOAD_A]);
+    if constexpr (TILED) {
+      tma_load_2d(smem + OFF_VN, &map_vn, 0, ys, &bars[BAR_LOAD_A]);
+    } else {
+      tma_load_2d(smem + OFF_VN, &map_vn, t.hv * D, y, &bars[BAR_LOAD_A]);
+      tma_load_2d(smem + OFF_VN + 8192, &map_vn, t.hv * D + 64, y, &bars[BAR_LOAD_A]);
+    }
     tma_load_2d(smem + OFF_DH, &map_dh, 0, ys, &bars[BAR_LOAD_A]);
     tma_load_2d(smem + OFF_DH + 16384, &map_dh, 64, ys, &bars[BAR_LOAD_A]);
   };
   auto load_b = [&](const Item& t) {
     const int y = (int)t.row0;
     mbar_arrive_expect_tx(&bars[BAR_LOAD_B], TX_B);
-    tma_load_2d(smem + OFF_DU, &map_du, t.hv * D, y, &bars[BAR_LOAD_B]);
-    tma_load_2d(smem + OFF_DU + 8192, &map_du, t.hv * D + 64, y, &bars[BAR_LOAD_B]);
+    if constexpr (TILED) {
+      tma_load_2d(smem + OFF_DU, &map_du, 0, (int)((t.chunk_id * p.Hv + t.hv) * D), &bars[BAR_LOAD_B]);
+    } else {
+      tma_load_2d(smem + OFF_DU, &map_du, t.hv * D, y, &bars[BAR_LOAD_B]);
+      tma_load_2d(smem + OFF_DU + 8192, &map_du, t.hv * D + 64, y, &bars[BAR_LOAD_B]);
+    }
     tma_load_2d(smem + OFF_Q, &map_q, t.hq * D, y, &bars[BAR_LOAD_B]);
     tma_load_2d(smem + OFF_Q + 8192, &map_q, t.hq * D + 64, y, &bars[BAR_LOAD_B]);
     tma_load_2d(smem + OFF_V, &map_v, t.hv * D, y, &bars[BAR_LOAD_B]);
@@ -242,6 +253,11 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
   constexpr uint32_t ID_KK_128 = idesc_bf16(64, 128, 0, 0), ID_KK_64 = idesc_bf16(64, 64, 0, 0);
   constexpr uint32_t ID_KM_128 = idesc_bf16(64, 128, 0, 1), ID_MM_128 = idesc_bf16(64, 128, 1, 1);
   constexpr uint32_t ID_MM_64 = idesc_bf16(64, 64, 1, 1);
+  // operand-tile layouts: [V rows][K or token columns], read MN-major with the contraction over rows
+  constexpr uint32_t ID_KM_64 = idesc_bf16(64, 64, 0, 1), ID_MK_64 = idesc_bf16(64, 64, 1, 0);
+  constexpr uint32_t ID_MK_128 = idesc_bf16(64, 128, 1, 0);
+  const uint32_t hT_lo = desc_lo_mnmajor(smem + OFF_H, 16384), dhT_lo = desc_lo_mnmajor(smem + OFF_DH, 16384);
+  const uint32_t vnT_lo = desc_lo_mnmajor(smem + OFF_VN, 16384), duT_lo = desc_lo_mnmajor(smem + OFF_DU, 16384);
 
   // ---- per-thread coordinates in the 16-lane accumulator shape ----
   const int qd = warp & 3, cq = warp >> 2;
@@ -299,17 +315,29 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
     ok = mbar_wait(&bars[BAR_LOAD_A], lph, abort_flag) && mbar_wait(&bars[BAR_LOAD_B], lph, abort_flag);
     if (ok && valid < CHUNK) {
       zero_rows(OFF_Q, 2, valid);
-      zero_rows(OFF_V, 8, valid);  // v, v_new, dO, du
+      if constexpr (TILED) {  // the transposed tiles already hold zeros past the sequence end
+        zero_rows(OFF_V, 2, valid);
+        zero_rows(OFF_DO, 2, valid);
+      } else {
+        zero_rows(OFF_V, 8, valid);  // v, v_new, dO, du
+      }
     }
     round_sync();
     stamp();
 
     // ======================= round 1: products with h and dh, ds, qk =======================
     if (ok && tid == 0) {
-      umma_group<8, 2, 512, 2, 1024, false>(tmem + T_DW, du_lo, h_lo, ID_KK_128);
-      umma_group<8, 2, 512, 2, 512, false>(tmem + T_DS, do_lo, vn_lo, ID_KK_64);
-      umma_group<8, 2, 512, 2, 1024, false>(tmem + T_DQ1, do_lo, h_lo, ID_KK_128);
-      umma_group<8, 2, 512, 2, 1024, false>(tmem + T_DK1, vn_lo, dh_lo, ID_KK_128);
+      if constexpr (TILED) {
+        umma_group<8, 128, 512, 128, 512, false>(tmem + T_DW, duT_lo, hT_lo, ID_MM_128);
+        umma_group<8, 2, 512, 128, 512, false>(tmem + T_DS, do_lo, vnT_lo, ID_KM_64);
+        umma_group<8, 2, 512, 128, 512, false>(tmem + T_DQ1, do_lo, hT_lo, ID_KM_128);
+        umma_group<8, 128, 512, 128, 512, false>(tmem + T_DK1, vnT_lo, dhT_lo, ID_MM_128);
+      } else {
+        umma_group<8, 2, 512, 2, 1024, false>(tmem + T_DW, du_lo, h_lo, ID_KK_128);
+        umma_group<8, 2, 512, 2, 512, false>(tmem + T_DS, do_lo, vn_lo, ID_KK_64);
+        umma_group<8, 2, 512, 2, 1024, false>(tmem + T_DQ1, do_lo, h_lo, ID_KK_128);
+        umma_group<8, 2, 512, 2, 1024, false>(tmem + T_DK1, vn_lo, dh_lo, ID_KK_128);
+      }
     }
     // meanwhile: gamma_last * sum(h * dh) over the whole 128 x 128 tiles (plain shared-memory reads)
     if (ok) {
@@ -435,11 +463,13 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
     if (ok && tid == 0) {
       if (has_next) load_a(nxt);  // h, dh, dO, v_new of this item are dead
       umma_group<8, 2, 512, 2, 512, false>(tmem + T_X1, dw_lo, k_lo, ID_KK_64);
-      umma_group<8, 2, 512, 2, 512, false>(tmem + T_X2, du_lo, v_lo, ID_KK_64);
+      if constexpr (TILED) umma_group<8, 128, 512, 2, 512, false>(tmem + T_X2, duT_lo, v_lo, ID_MK_64);
+      else umma_group<8, 2, 512, 2, 512, false>(tmem + T_X2, du_lo, v_lo, ID_KK_64);
       umma_group<4, 2, 0, 128, 0, false>(tmem + T_DQ2, ds_lo, kmn_lo, ID_KM_128);
       umma_group<4, 128, 0, 128, 0, false>(tmem + T_DK2, dsmn_lo, qmn_lo, ID_MM_128);
       umma_group<4, 128, 0, 128, 0, false>(tmem + T_T1, amn_lo, dwmn_lo, ID_MM_128);
-      umma_group<4, 128, 0, 128, 0, false>(tmem + T_T2, amn_lo, dumn_lo, ID_MM_128);
+      if constexpr (TILED) umma_group<4, 128, 0, 2, 0, false>(tmem + T_T2, amn_lo, du_lo, ID_MK_128);
+      else umma_group<4, 128, 0, 128, 0, false>(tmem + T_T2, amn_lo, dumn_lo, ID_MM_128);
       umma_commit(&bars[BAR_MMA]);
     }
     if (has_next) fetch_vectors(nxt);
@@ -698,7 +728,7 @@ int make_tile_map(CUtensorMap* m, const void* ptr, long long rows, long long col
 int launch_bwd_main_tc(const void* q, const void* k, const void* v, const void* vnew, const void* A,
                        const float* g, const void* beta, int beta_is_f32, const void* dO,
                        const void* du, const void* h, const void* dh, void* dq, void* dk, void* dv,
-                       float* db, float* dg, int Hq, int Hv, long long T_rows, long long n_chunks,
+                       float* db, float* dg, int tiled, int Hq, int Hv, long long T_rows, long long n_chunks,
                        float scale, SeqLayout lay, IndexTable chunk_indices, cudaStream_t st) {
   using namespace bmtc;
   CUtensorMap mq, mk, mv, mvn, mdo, mdu, mh, mdh, ma;
@@ -706,9 +736,14 @@ int launch_bwd_main_tc(const void* q, const void* k, const void* v, const void* 
   if ((rc = make_tile_map(&mq, q, T_rows, (long long)Hq * D, 64))) return rc;
   if ((rc = make_tile_map(&mk, k, T_rows, (long long)Hq * D, 64))) return rc;
   if ((rc = make_tile_map(&mv, v, T_rows, (long long)Hv * D, 64))) return rc;
-  if ((rc = make_tile_map(&mvn, vnew, T_rows, (long long)Hv * D, 64))) return rc;
+  if (tiled) {
+    if ((rc = make_tile_map(&mvn, vnew, n_chunks * Hv * D, CHUNK, 128))) return rc;
+    if ((rc = make_tile_map(&mdu, du, n_chunks * Hv * D, CHUNK, 128))) return rc;
+  } else {
+    if ((rc = make_tile_map(&mvn, vnew, T_rows, (long long)Hv * D, 64))) return rc;
+    if ((rc = make_tile_map(&mdu, du, T_rows, (long long)Hv * D, 64))) return rc;
+  }
   if ((rc = make_tile_map(&mdo, dO, T_rows, (long long)Hv * D, 64))) return rc;
-  if ((rc = make_tile_map(&mdu, du, T_rows, (long long)Hv * D, 64))) return rc;
   if ((rc = make_tile_map(&mh, h, n_chunks * Hv * D, D, 128))) return rc;
   if ((rc = make_tile_map(&mdh, dh, n_chunks * Hv * D, D, 128))) return rc;
   if ((rc = make_tile_map(&ma, A, T_rows, (long long)Hv * CHUNK, 64))) return rc;
@@ -719,7 +754,8 @@ int launch_bwd_main_tc(const void* q, const void* k, const void* v, const void* 
   p.n_chunks = n_chunks;
   static const bool profile = getenv("FQLA_PROFILE") != nullptr;
   p.profile = profile;
-  rc = configure_smem((const void*)bwd_main_tc_kernel, SMEM_BYTES);
+  rc = configure_smem(tiled ? (const void*)bwd_main_tc_kernel<true> : (const void*)bwd_main_tc_kernel<false>,
+                      SMEM_BYTES);
   if (rc != 0) return rc;
   static const int n_sm = [] {
     int dev = 0, n = 0;
@@ -729,7 +765,10 @@ int launch_bwd_main_tc(const void* q, const void* k, const void* v, const void* 
   }();
   const long long total = n_chunks * Hv;
   const unsigned grid = (unsigned)(total < n_sm ? total : n_sm);
-  bwd_main_tc_kernel<<<grid, NT, SMEM_BYTES, st>>>(p, mq, mk, mv, mvn, mdo, mdu, mh, mdh, ma);
+  if (tiled)
+    bwd_main_tc_kernel<true><<<grid, NT, SMEM_BYTES, st>>>(p, mq, mk, mv, mvn, mdo, mdu, mh, mdh, ma);
+  else
+    bwd_main_tc_kernel<false><<<grid, NT, SMEM_BYTES, st>>>(p, mq, mk, mv, mvn, mdo, mdu, mh, mdh, ma);
   return (int)cudaGetLastError();
 }
 

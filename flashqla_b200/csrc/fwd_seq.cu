@@ -26,8 +26,8 @@ namespace fqla {
 // tcgen05 implementation of the full forward (fwd_tc.cu)
 int launch_fwd_tc(const void* q, const void* k, const void* v, const void* A, const float* g,
                   const void* beta, int beta_is_f32, const float* h0, float* ht, void* o, void* h,
-                  void* vnew, int N, int Hq, int Hv, long long T_rows, float scale, SeqLayout lay,
-                  cudaStream_t st);
+                  void* vnew, int tiled, int N, int Hq, int Hv, long long T_rows, float scale,
+                  SeqLayout lay, cudaStream_t st);
 
 struct FwdSeqParams {
   const bf16* q;      // may be null (state-only pass)
@@ -346,7 +346,8 @@ extern "C" int fqla_fwd_seq(const void* q, const void* k, const void* v, const v
                             const float* h0, float* ht, void* o, void* h, void* vnew, float* M,
                             const int* warm_chunks, const int* m_mask, int B, int T, int Hq,
                             int Hv, int D, float scale, const void* cu_seqlens,
-                            const void* chunk_offsets, int idx_is64, int N, void* stream) {
+                            const void* chunk_offsets, int idx_is64, int N, int operand_tiles,
+                            void* stream) {
   if (!k || !v || !A || !g_cum || !beta || Hq <= 0 || Hv % Hq) return FQLA_ERR_INVALID_ARG;
   if (cu_seqlens && (!chunk_offsets || B != 1)) return FQLA_ERR_INVALID_ARG;
   if (o && !q) return FQLA_ERR_INVALID_ARG;
@@ -369,8 +370,9 @@ extern "C" int fqla_fwd_seq(const void* q, const void* k, const void* v, const v
   static const bool force_legacy = getenv("FQLA_FORCE_MMA_SYNC") != nullptr;
   const bool full = q && o, recompute = !q && !o && (h || vnew);
   if (D == 128 && (full || recompute) && !M && !warm_chunks && !m_mask && !force_legacy)
-    return launch_fwd_tc(q, k, v, A, g_cum, beta, beta_is_f32, h0, ht, o, h, vnew, p.N, Hq, Hv,
-                         p.T_rows, scale, p.lay, st);
+    return launch_fwd_tc(q, k, v, A, g_cum, beta, beta_is_f32, h0, ht, o, h, vnew, operand_tiles,
+                         p.N, Hq, Hv, p.T_rows, scale, p.lay, st);
+  if (operand_tiles) return FQLA_ERR_UNSUPPORTED_DIM;  // only the tcgen05 kernel writes tiles
   if (D == 128) return launch_fwd_seq<128>(p, st);
   if (D == 64) return launch_fwd_seq<64>(p, st);
   return FQLA_ERR_UNSUPPORTED_DIM;

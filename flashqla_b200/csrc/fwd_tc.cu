@@ -63,6 +63,7 @@ struct FwdTcParams {
   float scale;
   SeqLayout lay;
   int profile;
+  int tiled;  // h and vnew are written as operand tiles (h^T per chunk, v_new^T per chunk) by TMA
 };
 
 namespace fwdtc {
@@ -107,7 +108,8 @@ template <bool PROFILE, bool EXTRA>
 __global__ void __launch_bounds__(512, 1)
 fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
               const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
-              const __grid_constant__ CUtensorMap map_a) {
+              const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_h,
+              const __grid_constant__ CUtensorMap map_vn) {
   using namespace fwdtc;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
@@ -220,7 +222,7 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
               make_uint4(pack_bf16(y[8 * c + 0], y[8 * c + 1]), pack_bf16(y[8 * c + 2], y[8 * c + 3]),
                          pack_bf16(y[8 * c + 4], y[8 * c + 5]), pack_bf16(y[8 * c + 6], y[8 * c + 7]));
         }
-        if (EXTRA && hdst) {
+        if (EXTRA && hdst && !p.tiled) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             hdst[(long long)(kb * 64 + j) * D + v] = __float2bfloat16(x[j]);
@@ -348,7 +350,7 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
         }
         fence_proxy_async();
         mbar_arrive(&bars[VN_READY]);
-        if (EXTRA && p.vnew) {
+        if (EXTRA && p.vnew && !p.tiled) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             if (j < valid) p.vnew[((row0 + j) * p.Hv + hv) * D + v] = __float2bfloat16(x[j]);
@@ -485,6 +487,12 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
         umma_group<8, 2, 512, 2, 512, false>(tmem + TM_P, q0_lo + so, k0_lo + so, ID_P);
         umma_commit(&bars[P_DONE]);
       };
+      auto store_vn = [&](int it) {  // after VN_READY: the v_new^T tile is complete
+        if (p.tiled && p.vnew) {
+          tma_store_2d(&map_vn, 0, (int)(((sp.chunk_base + it) * p.Hv + hv) * D), smem + OFF_VNT);
+          tma_store_commit();
+        }
+      };
       for (int it = 0; it < n_it && ok; ++it) {
         const int s = it & 1;
         const uint32_t so = s ? STAGE_LO : 0u, so_next = s ? 0u : STAGE_LO;
@@ -501,7 +509,16 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
         SEC_BEGIN();
         // Vn^T = u^T - S^T w^T   (accumulates onto u^T)
         umma_group<8, 2, 1024, 2, 512, true>(tmem + TM_UV, st_lo, w_lo, ID_VN);
+        if constexpr (EXTRA) tma_store_wait_read();  // v_new^T of the chunk before has left its tile
         umma_commit(&bars[VN_DONE]);
+        if constexpr (EXTRA) {
+          if (p.tiled && p.h) {  // the operand copy of S^T is the state entering this chunk
+            const int y = (int)(((sp.chunk_base + it) * p.Hv + hv) * D);
+            tma_store_2d(&map_h, 0, y, smem + OFF_ST);
+            tma_store_2d(&map_h, 64, y, smem + OFF_ST + 16384);
+            tma_store_commit();
+          }
+        }
         SEC_END(SEC_A);
         if (it > 0) {
           ok = WAIT(O_FREE, (it - 1) & 1);
@@ -518,6 +535,7 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
         SEC_BEGIN();
         // S^T += (rho Vn)^T K      (B = K tile read MN-major: contraction over its 64 rows)
         umma_group<4, 2, 0, 128, 0, true>(tmem + TM_S, vrt_lo, kmn0_lo + so, ID_S);
+        if constexpr (EXTRA) tma_store_wait_read();  // the S^T tile may be rewritten after this
         umma_commit(&bars[S_DONE]);
         SEC_END(SEC_C);
         if (it + 1 < n_it) {
@@ -528,10 +546,14 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
           SEC_BEGIN();
           issue_u_w(so_next);
           SEC_END(SEC_D);
+          if constexpr (EXTRA) store_vn(it);
         }
         ok = WAIT(P_READY, it & 1) && (it + 1 < n_it || WAIT(VN_READY, it & 1));
         if (!ok) break;
         tc_fence_after();
+        if constexpr (EXTRA) {
+          if (it + 1 >= n_it) store_vn(it);
+        }
         SEC_BEGIN();
         // O2 = Pg Vn     (B = Vn^T copy: N = v rows, K = tok')
         umma_group<4, 2, 0, 2, 0, false>(tmem + TM_O2, p_lo, vnt_lo, ID_O);
@@ -540,6 +562,7 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
         if (it + 1 < n_it) issue_p(so_next);
         SEC_END(SEC_E);
       }
+      if constexpr (EXTRA) tma_store_wait_all();
     }
   } else if (warp == 1) {
     // =============================== producer ===============================
@@ -679,6 +702,8 @@ static EncodeTiledFn encode_fn() {
 }
 
 // 2-D bf16 tensor [rows][cols] (row pitch = cols), box = 64 columns x 64 rows, 128-byte swizzle.
+int make_tile_map(CUtensorMap* m, const void* ptr, long long rows, long long cols, int box_rows);
+
 static int make_map(CUtensorMap* m, const void* ptr, long long rows, long long cols) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return FQLA_ERR_INVALID_ARG;
@@ -694,10 +719,10 @@ static int make_map(CUtensorMap* m, const void* ptr, long long rows, long long c
 
 int launch_fwd_tc(const void* q, const void* k, const void* v, const void* A, const float* g,
                   const void* beta, int beta_is_f32, const float* h0, float* ht, void* o, void* h,
-                  void* vnew, int N, int Hq, int Hv, long long T_rows, float scale, SeqLayout lay,
-                  cudaStream_t st) {
+                  void* vnew, int tiled, int N, int Hq, int Hv, long long T_rows, float scale,
+                  SeqLayout lay, cudaStream_t st) {
   using namespace fwdtc;
-  CUtensorMap mq, mk, mv, ma;
+  CUtensorMap mq, mk, mv, ma, mh, mvn;
   int rc;
   // without q (recomputation of h and v_new for the backward pass) the output products run on
   // k instead; their result is never stored
@@ -705,7 +730,16 @@ int launch_fwd_tc(const void* q, const void* k, const void* v, const void* A, co
   if ((rc = make_map(&mk, k, T_rows, (long long)Hq * D))) return rc;
   if ((rc = make_map(&mv, v, T_rows, (long long)Hv * D))) return rc;
   if ((rc = make_map(&ma, A, T_rows, (long long)Hv * CHUNK))) return rc;
+  mh = mq;
+  mvn = mq;
+  if (tiled) {
+    // an upper bound of the chunk count: the maps only have to cover what the kernel stores
+    const long long max_chunks = (T_rows + CHUNK - 1) / CHUNK + N;
+    if (h && (rc = make_tile_map(&mh, h, max_chunks * Hv * D, D, 128))) return rc;
+    if (vnew && (rc = make_tile_map(&mvn, vnew, max_chunks * Hv * D, CHUNK, 128))) return rc;
+  }
   FwdTcParams p;
+  p.tiled = tiled;
   p.g = g; p.beta = beta; p.beta_is_f32 = beta_is_f32; p.h0 = h0; p.ht = ht;
   p.o = (bf16*)o; p.h = (bf16*)h; p.vnew = (bf16*)vnew;
   p.N = N; p.Hq = Hq; p.Hv = Hv; p.T_rows = T_rows; p.scale = scale; p.lay = lay;
@@ -715,7 +749,7 @@ int launch_fwd_tc(const void* q, const void* k, const void* v, const void* A, co
   auto launch = [&](auto kernel) {
     int err = configure_smem((const void*)kernel, SMEM_BYTES);
     if (err != 0) return err;
-    kernel<<<(unsigned)(N * Hv), 512, SMEM_BYTES, st>>>(p, mq, mk, mv, ma);
+    kernel<<<(unsigned)(N * Hv), 512, SMEM_BYTES, st>>>(p, mq, mk, mv, ma, mh, mvn);
     return (int)cudaGetLastError();
   };
   if (p.profile) return launch(fwd_tc_kernel<true, true>);

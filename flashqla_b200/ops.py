@@ -119,10 +119,13 @@ def kkt_solve(k, b, g_cum, cu_seqlens=None, chunk_size: int = CHUNK_SIZE):
 
 def fwd_seq(q, k, v, a, g_cum, b, scale, initial_state=None, *, output_final_state=False,
             output_o=True, output_h=False, output_vnew=False, output_m=False,
-            warm_chunks=None, m_mask=None, cu_seqlens=None, tables: SeqTables | None = None):
+            warm_chunks=None, m_mask=None, cu_seqlens=None, tables: SeqTables | None = None,
+            operand_tiles: bool = False):
     """Sequential forward recurrence.  Returns a dict with the requested outputs among
     ``o, h, vnew, ht, M`` (reference: ``blackwell/fused_fwd.py:775-915`` and
-    ``blackwell/prepare_h.py:669-784``)."""
+    ``blackwell/prepare_h.py:669-784``).  With ``operand_tiles`` (K = V = 128 only) ``h`` comes
+    out as ``[chunks, Hv, V, K]`` and ``vnew`` as ``[chunks, Hv, V, 64]``: the layouts
+    ``bwd_main(..., operand_tiles=True)`` reads as tensor-core operands."""
     _require_cuda(k, v, a, g_cum, b)
     _check_bf16(q=q, k=k, v=v, a=a)
     B, T, Hq, D = k.shape
@@ -136,7 +139,8 @@ def fwd_seq(q, k, v, a, g_cum, b, scale, initial_state=None, *, output_final_sta
     if output_h:
         out["h"] = torch.empty(tb.num_chunks, Hv, D, D, dtype=k.dtype, device=dev)
     if output_vnew:
-        out["vnew"] = torch.empty_like(v)
+        out["vnew"] = (torch.empty(tb.num_chunks, Hv, D, CHUNK_SIZE, dtype=k.dtype, device=dev)
+                       if operand_tiles else torch.empty_like(v))
     if output_final_state:
         out["ht"] = torch.empty(tb.N, Hv, D, D, dtype=torch.float32, device=dev)
     if output_m:
@@ -150,15 +154,18 @@ def fwd_seq(q, k, v, a, g_cum, b, scale, initial_state=None, *, output_final_sta
         _ptr(q) if output_o else None, _ptr(k), _ptr(v), _ptr(a), _ptr(g_cum), _ptr(b),
         _beta_flag(b), _ptr(initial_state), _ptr(out.get("ht")), _ptr(out.get("o")),
         _ptr(out.get("h")), _ptr(out.get("vnew")), _ptr(out.get("M")), _ptr(warm_chunks),
-        _ptr(m_mask), tb.B, tb.T, Hq, Hv, D, float(scale), cu, offs, is64, N, _stream(k))
+        _ptr(m_mask), tb.B, tb.T, Hq, Hv, D, float(scale), cu, offs, is64, N, int(operand_tiles),
+        _stream(k))
     _lib.check(st, "fwd_seq")
     return out
 
 
 def bwd_dh(q, k, a, g_cum, b, do, scale, dht=None, *, output_dh=True, output_du=True,
-           output_dh0=True, warm_chunks=None, cu_seqlens=None, tables: SeqTables | None = None):
+           output_dh0=True, warm_chunks=None, cu_seqlens=None, tables: SeqTables | None = None,
+           operand_tiles: bool = False):
     """Reverse recurrence of the state gradient; returns a dict with ``dh, du, dh0``
-    (reference: ``blackwell/cp_bwd.py:592-701`` and the dS chain of ``blackwell/fused_bwd.py``)."""
+    (reference: ``blackwell/cp_bwd.py:592-701`` and the dS chain of ``blackwell/fused_bwd.py``).
+    ``operand_tiles``: ``dh`` as ``[chunks, Hv, V, K]``, ``du`` as ``[chunks, Hv, V, 64]``."""
     _require_cuda(q, k, a, g_cum, b, do)
     _check_bf16(q=q, k=k, a=a, do=do)
     B, T, Hq, D = k.shape
@@ -169,7 +176,8 @@ def bwd_dh(q, k, a, g_cum, b, do, scale, dht=None, *, output_dh=True, output_du=
     if output_dh:
         out["dh"] = torch.empty(tb.num_chunks, Hv, D, D, dtype=k.dtype, device=dev)
     if output_du:
-        out["du"] = torch.empty_like(do)
+        out["du"] = (torch.empty(tb.num_chunks, Hv, D, CHUNK_SIZE, dtype=k.dtype, device=dev)
+                     if operand_tiles else torch.empty_like(do))
     if output_dh0:
         out["dh0"] = torch.empty(tb.N, Hv, D, D, dtype=torch.float32, device=dev)
     if dht is not None:
@@ -179,13 +187,13 @@ def bwd_dh(q, k, a, g_cum, b, do, scale, dht=None, *, output_dh=True, output_du=
     st = _lib.load().fqla_bwd_dh(
         _ptr(q), _ptr(k), _ptr(a), _ptr(g_cum), _ptr(b), _beta_flag(b), _ptr(do), _ptr(dht),
         _ptr(out.get("dh")), _ptr(out.get("du")), _ptr(out.get("dh0")), _ptr(warm_chunks),
-        tb.B, tb.T, Hq, Hv, D, float(scale), cu, offs, is64, N, _stream(k))
+        tb.B, tb.T, Hq, Hv, D, float(scale), cu, offs, is64, N, int(operand_tiles), _stream(k))
     _lib.check(st, "bwd_dh")
     return out
 
 
 def bwd_main(q, k, v, vnew, a, g_cum, b, do, du, h, dh, scale, cu_seqlens=None,
-             tables: SeqTables | None = None):
+             tables: SeqTables | None = None, operand_tiles: bool = False):
     """Chunk-parallel backward.  Returns ``(dq_v, dk_v, dv, db, dg)`` with dq_v/dk_v per value
     head and ``dg`` before its reverse cumsum (reference: ``blackwell/fused_bwd.py:1325-1413``)."""
     _require_cuda(q, k, v, vnew, a, g_cum, b, do, du, h, dh)
@@ -207,7 +215,7 @@ def bwd_main(q, k, v, vnew, a, g_cum, b, do, du, h, dh, scale, cu_seqlens=None,
         _ptr(q), _ptr(k), _ptr(v), _ptr(vnew), _ptr(a), _ptr(g_cum), _ptr(b), _beta_flag(b),
         _ptr(do), _ptr(du), _ptr(h), _ptr(dh), _ptr(dq), _ptr(dk), _ptr(dv), _ptr(db), _ptr(dg),
         tb.B, tb.T, Hq, Hv, D, float(scale), cu, offs, _ptr(tb.chunk_indices), is64, tb.num_chunks,
-        _stream(k))
+        int(operand_tiles), _stream(k))
     _lib.check(st, "bwd_main")
     return dq, dk, dv, db, dg
 

@@ -60,35 +60,43 @@ int fqla_kkt_solve(const void* k, const void* beta, int beta_is_f32, const float
  * transition matrix M (state_end = state_end|zero start + M state_start).  q may be NULL when
  * o is.  warm_chunks [N,Hv] (int32, optional, state-only calls): walk only the last
  * warm_chunks[n,hv] chunks of each sequence from a zero state.  m_mask [N,Hv] (int32,
- * optional): compute M only where non-zero.
+ * optional): compute M only where non-zero.  operand_tiles != 0 (K = V = 128, no M, no
+ * warm_chunks): h and vnew are written in the layout the backward kernels consume as tensor-core
+ * operands, h as [chunks, Hv, V, K] (each state transposed) and vnew as [chunks, Hv, V, 64]
+ * (each chunk transposed, rows past the sequence end zero); FQLA_ERR_UNSUPPORTED_DIM otherwise.
  * Replaces fused_gdr_fwd (blackwell/fused_fwd.py:775-915) and fused_gdr_h
  * (blackwell/prepare_h.py:669-784). */
 int fqla_fwd_seq(const void* q, const void* k, const void* v, const void* A, const float* g_cum,
                  const void* beta, int beta_is_f32, const float* h0, float* ht, void* o, void* h,
                  void* vnew, float* M, const int* warm_chunks, const int* m_mask, int B, int T,
                  int Hq, int Hv, int D, float scale, const void* cu_seqlens,
-                 const void* chunk_offsets, int idx_is64, int N, void* stream);
+                 const void* chunk_offsets, int idx_is64, int N, int operand_tiles,
+                 void* stream);
 
 /* Sequential reverse recurrence of the state gradient.  Optional outputs: per-chunk dh, du (the
  * gradient of vnew), dh0.  warm_chunks (optional, dh0-only calls): walk only the first
- * warm_chunks[n,hv] chunks from a zero gradient.
+ * warm_chunks[n,hv] chunks from a zero gradient.  operand_tiles != 0 (K = V = 128, no
+ * warm_chunks): dh is written as [chunks, Hv, V, K] and du as [chunks, Hv, V, 64], the operand
+ * layouts of fqla_fwd_seq's h and vnew; FQLA_ERR_UNSUPPORTED_DIM otherwise.
  * Replaces fused_gdr_dh_ws (blackwell/cp_bwd.py:592-701) and the dS chain of fused_gdr_bwd
  * (blackwell/fused_bwd.py:336-474). */
 int fqla_bwd_dh(const void* q, const void* k, const void* A, const float* g_cum, const void* beta,
                 int beta_is_f32, const void* dO, const float* dht, void* dh, void* du, float* dh0,
                 const int* warm_chunks, int B, int T, int Hq, int Hv, int D, float scale,
                 const void* cu_seqlens, const void* chunk_offsets, int idx_is64, int N,
-                void* stream);
+                int operand_tiles, void* stream);
 
 /* Chunk-parallel backward: dq, dk (per VALUE head, [B,T,Hv,D] bf16), dv, dbeta and the
- * pre-cumsum dg (both fp32 [B,T,Hv]) from h, dh, vnew and du.
+ * pre-cumsum dg (both fp32 [B,T,Hv]) from h, dh, vnew and du.  operand_tiles != 0 (K = V = 128):
+ * h, dh, vnew and du are in the operand layouts written by fqla_fwd_seq / fqla_bwd_dh with the
+ * same flag.
  * Replaces the per-chunk body of fused_gdr_bwd (blackwell/fused_bwd.py:1325-1413). */
 int fqla_bwd_main(const void* q, const void* k, const void* v, const void* vnew, const void* A,
                   const float* g_cum, const void* beta, int beta_is_f32, const void* dO,
                   const void* du, const void* h, const void* dh, void* dq, void* dk, void* dv,
                   float* db, float* dg, int B, int T, int Hq, int Hv, int D, float scale,
                   const void* cu_seqlens, const void* chunk_offsets, const void* chunk_indices,
-                  int idx_is64, long long num_chunks, void* stream);
+                  int idx_is64, long long num_chunks, int operand_tiles, void* stream);
 
 /* out[row, hq, :] = sum over the G value heads of group hq of in[row, hq*G + i, :] (bf16, fp32
  * accumulation).  Replaces group_reduce_vector, flash_qla/ops/utils/group_reduce.py:60-79. */
