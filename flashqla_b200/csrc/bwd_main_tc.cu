@@ -1,15 +1,19 @@
 // Chunk-parallel part of the gated-delta-rule backward on Blackwell tensor cores (K = V = 128).
 //
 // Same mathematics and same outputs as bwd_main.cu (the reference's tests/ref_gdr.py:427-600,
-// evaluated by the reference kernels inside blackwell/fused_bwd.py:595-862): one CTA per
-// (chunk, value head), 256 threads.  All sixteen tile products are tcgen05.mma with M = 64 (rows
-// = tokens) and fp32 accumulators in tensor memory; operand tiles arrive by TMA (128-byte
-// swizzle), intermediate operands (ds, dw, dA, ...) are written back to shared memory as bf16 by
-// the threads that read the accumulators.  The work is five rounds of
-//     one thread issues a batch of products -> commit -> everybody waits on the mbarrier ->
-//     every warp reads its quarter of the accumulators (16-lane shape) and does the elementwise
-//     work of the round -> fence -> __syncthreads
-// Two M = 64 accumulators share each column range (lanes +0 and +16 of every 32-lane quarter).
+// evaluated by the reference kernels inside blackwell/fused_bwd.py:595-862).  Persistent CTAs
+// (one per SM) walk the work items (chunk, value head).  All sixteen tile products are
+// tcgen05.mma with M = 64 (rows = tokens) and fp32 accumulators in tensor memory; two M = 64
+// accumulators share each column range (lanes +0 and +16 of every 32-lane quarter).
+//
+// Roles: warp 16 issues every product and every TMA load (one elected thread); warps 0-15 read the
+// accumulators (16-lane shape; 4 lane quarters x 4 column quarters), do the elementwise work and
+// write the intermediate operands (dw, ds, dA, T, dA3) back to shared memory as bf16 tiles.  The
+// two sides are coupled by one mbarrier per product group (commit -> read-out) and one per
+// operand tile (written -> may be multiplied), so that the dependent chain
+//     dw -> dA -> T = A^T dA -> dA3 -> (dA3 K, (beta dA3)^T K)
+// overlaps with the products and read-outs that do not depend on it.  Operand tiles of the next
+// item are fetched as soon as the buffers of the current one are dead (k has two buffers).
 #include <cuda.h>
 
 #include "common.cuh"
@@ -23,8 +27,8 @@ using namespace tc;
 // set to 1 when a CTA of this file's kernel abandoned a bounded wait; read through
 // fqla_device_status together with the forward kernel's word
 __device__ int g_bwd_main_status = 0;
-// Diagnostics (FQLA_PROFILE=1): clock of CTA (0,0) at the end of every step of the kernel
-__device__ long long g_bwd_main_profile[16];
+// Diagnostics (FQLA_PROFILE=1): clock of thread 0 of CTA 0 after every wait and every read-out step
+__device__ long long g_bwd_main_profile[64];
 
 struct BwdMainTcParams {
   const float* g;
@@ -45,28 +49,30 @@ struct BwdMainTcParams {
 
 namespace bmtc {
 constexpr int D = 128;
-constexpr int NT = 512;          // threads: 16 warps = 4 lane quarters x 4 column quarters
+constexpr int N_EPI = 512;       // read-out threads: 16 warps = 4 lane quarters x 4 column quarters
+constexpr int NT = N_EPI + 32;   // + the issue warp
 constexpr int ROW_TILE = 16384;  // [64 x 128] bf16 as two 64-column blocks
 constexpr int SQ_TILE = 32768;   // [128 x 128] bf16 as two 64-column blocks of 128 rows
-constexpr int OFF_Q = 0, OFF_K = OFF_Q + ROW_TILE, OFF_V = OFF_K + ROW_TILE;
+constexpr int OFF_Q = 0, OFF_K = OFF_Q + ROW_TILE;  // k: two buffers
+constexpr int OFF_V = OFF_K + 2 * ROW_TILE;
 constexpr int OFF_VN = OFF_V + ROW_TILE, OFF_DO = OFF_VN + ROW_TILE, OFF_DU = OFF_DO + ROW_TILE;
 constexpr int OFF_H = OFF_DU + ROW_TILE;
 constexpr int OFF_DH = OFF_H + SQ_TILE;
 constexpr int OFF_A = OFF_DH + SQ_TILE;
-constexpr int OFF_DS = OFF_A + 8192;       // ds, later T = A^T dA
-constexpr int OFF_DA = OFF_DS + 8192;
-constexpr int OFF_D3 = OFF_DA + 8192;      // dA3
-constexpr int OFF_D3B = OFF_D3 + 8192;     // diag(beta) dA3
-constexpr int OFF_DW = OFF_D3B + 8192;     // -du h^T
-constexpr int OFF_VEC = OFF_DW + ROW_TILE;  // g, gamma, rho, beta, dg, db (64 floats each) + dg_last
-constexpr int OFF_BAR = OFF_VEC + (6 * 64 + 4) * 4;
-constexpr int OFF_MISC = OFF_BAR + 8 * 8;
+constexpr int OFF_DS = OFF_A + 8192;        // ds, later diag(beta) dA3
+constexpr int OFF_DA = OFF_DS + 8192;       // dA, then T = A^T dA, then dA3
+constexpr int OFF_DW = OFF_DA + 8192;       // -du h^T
+// g, gamma, rho, beta (64 floats each); per-warp partial sums of dg (rows: 4 column quarters x 64,
+// columns: 4 lane quarters x 64), of db (4 x 64) and of the chunk total (16)
+constexpr int OFF_VEC = OFF_DW + ROW_TILE;
+constexpr int OFF_BAR = OFF_VEC + (4 * 64 + 3 * 256 + 16) * 4;
+constexpr int N_BARS = 20;
+constexpr int OFF_MISC = OFF_BAR + N_BARS * 8;
 constexpr int SMEM_BYTES = OFF_MISC + 16 + 1024;
-// the operand tiles of one work item arrive in three groups, in the order their buffers of the
-// previous item become free
-constexpr uint32_t TX_A = 2 * SQ_TILE + 2 * ROW_TILE;  // h, dh, dO, v_new
+// the operand tiles of one item arrive in three groups, in the order their buffers become free
+constexpr uint32_t TX_A = 2 * SQ_TILE + 3 * ROW_TILE;  // h, dh, dO, v_new, k (other buffer)
 constexpr uint32_t TX_B = 3 * ROW_TILE;                // du, q, v
-constexpr uint32_t TX_C = ROW_TILE + 8192;             // k, A
+constexpr uint32_t TX_C = 8192;                        // A
 // tensor memory: (column, lane half) of every accumulator
 constexpr uint32_t HI = 16u << 16;
 constexpr uint32_t T_DQ1 = 0, T_DK1 = 128, T_DW = 256, T_T1 = 384;
@@ -75,7 +81,11 @@ constexpr uint32_t T_X1 = 256, T_X2 = 320;            // after dw has been read
 constexpr uint32_t T_T = 384 + HI, T_KK = 448 + HI;    // after ds, qk have been read
 constexpr uint32_t T_D3 = 256;                         // after x1 has been read
 constexpr uint32_t T_T3 = 0, T_DK5 = 0 + HI;           // after dq1, dq2 have been read
-enum { BAR_LOAD_A = 0, BAR_LOAD_B, BAR_LOAD_C, BAR_MMA };
+enum {
+  L_A = 0, L_B, L_C,                                       // TMA groups landed
+  C_DW, C_DSQK, C_1B, C_X, C_2B, C_T, C_D3, C_5,           // product groups complete (commit)
+  R_ZERO, R_HD, R_DW, R_DS, R_DA, R_T, R_E6, R_D3, R_END   // read-out side -> issue warp (16 warps)
+};
 }  // namespace bmtc
 
 // 16 lanes x 32 (x4) or 16 (x2) columns: register 4i+e of lane l holds row l/4 + 8*(e>>1),
@@ -100,6 +110,9 @@ __device__ __forceinline__ void tmem_ld_16x16(uint32_t taddr, float (&v)[8]) {
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void epi_barrier() {  // the 16 read-out warps only
+  asm volatile("bar.sync 1, 512;" ::: "memory");
+}
 
 // Persistent: CTA b handles work items b, b + gridDim.x, ...; item w = (chunk w / Hv, head w % Hv),
 // so neighbouring CTAs share q and k of a grouped-value-attention group through L2.
@@ -119,13 +132,15 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + OFF_MISC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + OFF_MISC + 4);
+  volatile int* stop_flag = reinterpret_cast<volatile int*>(smem + OFF_MISC + 8);
   float* sG = reinterpret_cast<float*>(smem + OFF_VEC);
   float* sGam = sG + 64;
   float* sRho = sGam + 64;
   float* sBeta = sRho + 64;
-  float* sDg = sBeta + 64;
-  float* sDb = sDg + 64;
-  float* sDgLast = sDb + 64;
+  float* sRowDg = sBeta + 64;
+  float* sColDg = sRowDg + 256;
+  float* sRowDb = sColDg + 256;
+  float* sLast = sRowDb + 256;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const long long total = p.n_chunks * p.Hv;
@@ -154,69 +169,12 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
     t.chunk_id = sp.chunk_base + ci;
     return t;
   };
-  auto load_a = [&](const Item& t) {
-    const int y = (int)t.row0, ys = (int)((t.chunk_id * p.Hv + t.hv) * D);
-    mbar_arrive_expect_tx(&bars[BAR_LOAD_A], TX_A);
-    tma_load_2d(smem + OFF_DO, &map_do, t.hv * D, y, &bars[BAR_LOAD_A]);
-    tma_load_2d(smem + OFF_DO + 8192, &map_do, t.hv * D + 64, y, &bars[BAR_LOAD_A]);
-    tma_load_2d(smem + OFF_H, &map_h, 0, ys, &bars[BAR_LOAD_A]);
-    tma_load_2d(smem + OFF_H + 16384, &map_h, 64, ys, &bars[BAR_LOAD_A]);
-    if constexpr (TILED) {
-      tma_load_2d(smem + OFF_VN, &map_vn, 0, ys, &bars[BAR_LOAD_A]);
-    } else {
-      tma_load_2d(smem + OFF_VN, &map_vn, t.hv * D, y, &bars[BAR_LOAD_A]);
-      tma_load_2d(smem + OFF_VN + 8192, &map_vn, t.hv * D + 64, y, &bars[BAR_LOAD_A]);
-    }
-    tma_load_2d(smem + OFF_DH, &map_dh, 0, ys, &bars[BAR_LOAD_A]);
-    tma_load_2d(smem + OFF_DH + 16384, &map_dh, 64, ys, &bars[BAR_LOAD_A]);
-  };
-  auto load_b = [&](const Item& t) {
-    const int y = (int)t.row0;
-    mbar_arrive_expect_tx(&bars[BAR_LOAD_B], TX_B);
-    if constexpr (TILED) {
-      tma_load_2d(smem + OFF_DU, &map_du, 0, (int)((t.chunk_id * p.Hv + t.hv) * D), &bars[BAR_LOAD_B]);
-    } else {
-      tma_load_2d(smem + OFF_DU, &map_du, t.hv * D, y, &bars[BAR_LOAD_B]);
-      tma_load_2d(smem + OFF_DU + 8192, &map_du, t.hv * D + 64, y, &bars[BAR_LOAD_B]);
-    }
-    tma_load_2d(smem + OFF_Q, &map_q, t.hq * D, y, &bars[BAR_LOAD_B]);
-    tma_load_2d(smem + OFF_Q + 8192, &map_q, t.hq * D + 64, y, &bars[BAR_LOAD_B]);
-    tma_load_2d(smem + OFF_V, &map_v, t.hv * D, y, &bars[BAR_LOAD_B]);
-    tma_load_2d(smem + OFF_V + 8192, &map_v, t.hv * D + 64, y, &bars[BAR_LOAD_B]);
-  };
-  auto load_c = [&](const Item& t) {
-    const int y = (int)t.row0;
-    mbar_arrive_expect_tx(&bars[BAR_LOAD_C], TX_C);
-    tma_load_2d(smem + OFF_K, &map_k, t.hq * D, y, &bars[BAR_LOAD_C]);
-    tma_load_2d(smem + OFF_K + 8192, &map_k, t.hq * D + 64, y, &bars[BAR_LOAD_C]);
-    tma_load_2d(smem + OFF_A, &map_a, t.hv * CHUNK, y, &bars[BAR_LOAD_C]);
-  };
-  // per-row scalars of an item, fetched one item ahead into registers by threads 0..63
-  float pre_g = 0.f, pre_gl = 0.f, pre_beta = 0.f;
-  auto fetch_vectors = [&](const Item& t) {
-    if (tid < CHUNK) {
-      const int r = min(tid, t.valid - 1);
-      pre_g = p.g[(t.row0 + r) * p.Hv + t.hv];
-      pre_gl = p.g[(t.row0 + t.valid - 1) * p.Hv + t.hv];
-      pre_beta = tid < t.valid ? load_beta(p.beta, p.beta_is_f32, (t.row0 + tid) * p.Hv + t.hv) : 0.f;
-    }
-  };
-  // rows past the end of the sequence belong to the next one: zero them in n_blocks 8 KB blocks
-  auto zero_rows = [&](int off, int n_blocks, int valid) {
-    for (int blk = 0; blk < n_blocks; ++blk) {
-      unsigned char* base = smem + off + blk * 8192;
-      for (int i = tid; i < (CHUNK - valid) * 8; i += NT)
-        *reinterpret_cast<uint4*>(base + (valid + (i >> 3)) * 128 + ((i & 7) << 4)) = make_uint4(0, 0, 0, 0);
-    }
-  };
 
   if (tid == 0) {
-    mbar_init(&bars[BAR_LOAD_A], 1);
-    mbar_init(&bars[BAR_LOAD_B], 1);
-    mbar_init(&bars[BAR_LOAD_C], 1);
-    mbar_init(&bars[BAR_MMA], 1);
+    for (int i = L_A; i <= C_5; ++i) mbar_init(&bars[i], 1);
+    for (int i = R_ZERO; i <= R_END; ++i) mbar_init(&bars[i], N_EPI / 32);
     *abort_flag = 0;
-    *sDgLast = 0.f;
+    *stop_flag = 0;
     fence_mbar_init();
   }
   if (warp == 0) tmem_alloc(tmem_slot, 512);
@@ -224,160 +182,271 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const bool prof = p.profile && tid == 0 && blockIdx.x == 0;
-  int stamp_i = 0;
-  auto stamp = [&]() {
-    if (prof && stamp_i < 16) g_bwd_main_profile[stamp_i++] = clock64();
-  };
-  stamp();
+  auto WAIT = [&](int idx, uint32_t parity) { return mbar_wait(&bars[idx], parity, abort_flag); };
 
-  Item cur = decode(blockIdx.x);  // the grid never exceeds the number of items
-  if (tid == 0) {
-    load_a(cur);
-    load_b(cur);
-    load_c(cur);
-  }
-  fetch_vectors(cur);
+  if (warp == N_EPI / 32) {
+    // ====================== issue warp: TMA loads and every tcgen05.mma ======================
+    if (lane == 0) {
+      auto load_a = [&](const Item& t, int kbuf) {
+        const int y = (int)t.row0, ys = (int)((t.chunk_id * p.Hv + t.hv) * D);
+        mbar_arrive_expect_tx(&bars[L_A], TX_A);
+        tma_load_2d(smem + OFF_DU - ROW_TILE, &map_do, t.hv * D, y, &bars[L_A]);  // = OFF_DO
+        tma_load_2d(smem + OFF_DO + 8192, &map_do, t.hv * D + 64, y, &bars[L_A]);
+        tma_load_2d(smem + OFF_H, &map_h, 0, ys, &bars[L_A]);
+        tma_load_2d(smem + OFF_H + 16384, &map_h, 64, ys, &bars[L_A]);
+        if constexpr (TILED) {
+          tma_load_2d(smem + OFF_VN, &map_vn, 0, ys, &bars[L_A]);
+        } else {
+          tma_load_2d(smem + OFF_VN, &map_vn, t.hv * D, y, &bars[L_A]);
+          tma_load_2d(smem + OFF_VN + 8192, &map_vn, t.hv * D + 64, y, &bars[L_A]);
+        }
+        tma_load_2d(smem + OFF_K + kbuf * ROW_TILE, &map_k, t.hq * D, y, &bars[L_A]);
+        tma_load_2d(smem + OFF_K + kbuf * ROW_TILE + 8192, &map_k, t.hq * D + 64, y, &bars[L_A]);
+        tma_load_2d(smem + OFF_DH, &map_dh, 0, ys, &bars[L_A]);
+        tma_load_2d(smem + OFF_DH + 16384, &map_dh, 64, ys, &bars[L_A]);
+      };
+      auto load_b = [&](const Item& t) {
+        const int y = (int)t.row0;
+        mbar_arrive_expect_tx(&bars[L_B], TX_B);
+        if constexpr (TILED) {
+          tma_load_2d(smem + OFF_DU, &map_du, 0, (int)((t.chunk_id * p.Hv + t.hv) * D), &bars[L_B]);
+        } else {
+          tma_load_2d(smem + OFF_DU, &map_du, t.hv * D, y, &bars[L_B]);
+          tma_load_2d(smem + OFF_DU + 8192, &map_du, t.hv * D + 64, y, &bars[L_B]);
+        }
+        tma_load_2d(smem + OFF_Q, &map_q, t.hq * D, y, &bars[L_B]);
+        tma_load_2d(smem + OFF_Q + 8192, &map_q, t.hq * D + 64, y, &bars[L_B]);
+        tma_load_2d(smem + OFF_V, &map_v, t.hv * D, y, &bars[L_B]);
+        tma_load_2d(smem + OFF_V + 8192, &map_v, t.hv * D + 64, y, &bars[L_B]);
+      };
+      auto load_c = [&](const Item& t) {
+        mbar_arrive_expect_tx(&bars[L_C], TX_C);
+        tma_load_2d(smem + OFF_A, &map_a, t.hv * CHUNK, (int)t.row0, &bars[L_C]);
+      };
+      // descriptors (low words)
+      const uint32_t q_lo = desc_lo_kmajor(smem + OFF_Q), v_lo = desc_lo_kmajor(smem + OFF_V);
+      const uint32_t k_lo0 = desc_lo_kmajor(smem + OFF_K), kmn_lo0 = desc_lo_mnmajor(smem + OFF_K, 8192);
+      const uint32_t vn_lo = desc_lo_kmajor(smem + OFF_VN);
+      const uint32_t do_lo = desc_lo_kmajor(smem + OFF_DO), du_lo = desc_lo_kmajor(smem + OFF_DU);
+      const uint32_t h_lo = desc_lo_kmajor(smem + OFF_H), dh_lo = desc_lo_kmajor(smem + OFF_DH);
+      const uint32_t a_lo = desc_lo_kmajor(smem + OFF_A), ds_lo = desc_lo_kmajor(smem + OFF_DS);
+      const uint32_t da_lo = desc_lo_kmajor(smem + OFF_DA), dw_lo = desc_lo_kmajor(smem + OFF_DW);
+      const uint32_t qmn_lo = desc_lo_mnmajor(smem + OFF_Q, 8192);
+      const uint32_t dumn_lo = desc_lo_mnmajor(smem + OFF_DU, 8192), dwmn_lo = desc_lo_mnmajor(smem + OFF_DW, 8192);
+      const uint32_t amn_lo = desc_lo_mnmajor(smem + OFF_A, 8192), dsmn_lo = desc_lo_mnmajor(smem + OFF_DS, 8192);
+      const uint32_t damn_lo = desc_lo_mnmajor(smem + OFF_DA, 8192);
+      // operand-tile layouts: [V rows][K or token columns], read MN-major, contraction over rows
+      const uint32_t hT_lo = desc_lo_mnmajor(smem + OFF_H, 16384), dhT_lo = desc_lo_mnmajor(smem + OFF_DH, 16384);
+      const uint32_t vnT_lo = desc_lo_mnmajor(smem + OFF_VN, 16384), duT_lo = desc_lo_mnmajor(smem + OFF_DU, 16384);
+      constexpr uint32_t ID_KK_128 = idesc_bf16(64, 128, 0, 0), ID_KK_64 = idesc_bf16(64, 64, 0, 0);
+      constexpr uint32_t ID_KM_128 = idesc_bf16(64, 128, 0, 1), ID_MM_128 = idesc_bf16(64, 128, 1, 1);
+      constexpr uint32_t ID_MM_64 = idesc_bf16(64, 64, 1, 1);
+      constexpr uint32_t ID_KM_64 = idesc_bf16(64, 64, 0, 1), ID_MK_64 = idesc_bf16(64, 64, 1, 0);
+      constexpr uint32_t ID_MK_128 = idesc_bf16(64, 128, 1, 0);
+      constexpr uint32_t KBUF_LO = ROW_TILE >> 4;
 
-  // ---- descriptors (low words) ----
-  const uint32_t q_lo = desc_lo_kmajor(smem + OFF_Q), k_lo = desc_lo_kmajor(smem + OFF_K);
-  const uint32_t v_lo = desc_lo_kmajor(smem + OFF_V), vn_lo = desc_lo_kmajor(smem + OFF_VN);
-  const uint32_t do_lo = desc_lo_kmajor(smem + OFF_DO), du_lo = desc_lo_kmajor(smem + OFF_DU);
-  const uint32_t h_lo = desc_lo_kmajor(smem + OFF_H), dh_lo = desc_lo_kmajor(smem + OFF_DH);
-  const uint32_t a_lo = desc_lo_kmajor(smem + OFF_A), ds_lo = desc_lo_kmajor(smem + OFF_DS);
-  const uint32_t dw_lo = desc_lo_kmajor(smem + OFF_DW), d3_lo = desc_lo_kmajor(smem + OFF_D3);
-  const uint32_t qmn_lo = desc_lo_mnmajor(smem + OFF_Q, 8192), kmn_lo = desc_lo_mnmajor(smem + OFF_K, 8192);
-  const uint32_t dumn_lo = desc_lo_mnmajor(smem + OFF_DU, 8192), dwmn_lo = desc_lo_mnmajor(smem + OFF_DW, 8192);
-  const uint32_t amn_lo = desc_lo_mnmajor(smem + OFF_A, 8192), dsmn_lo = desc_lo_mnmajor(smem + OFF_DS, 8192);
-  const uint32_t damn_lo = desc_lo_mnmajor(smem + OFF_DA, 8192), d3bmn_lo = desc_lo_mnmajor(smem + OFF_D3B, 8192);
-  constexpr uint32_t ID_KK_128 = idesc_bf16(64, 128, 0, 0), ID_KK_64 = idesc_bf16(64, 64, 0, 0);
-  constexpr uint32_t ID_KM_128 = idesc_bf16(64, 128, 0, 1), ID_MM_128 = idesc_bf16(64, 128, 1, 1);
-  constexpr uint32_t ID_MM_64 = idesc_bf16(64, 64, 1, 1);
-  // operand-tile layouts: [V rows][K or token columns], read MN-major with the contraction over rows
-  constexpr uint32_t ID_KM_64 = idesc_bf16(64, 64, 0, 1), ID_MK_64 = idesc_bf16(64, 64, 1, 0);
-  constexpr uint32_t ID_MK_128 = idesc_bf16(64, 128, 1, 0);
-  const uint32_t hT_lo = desc_lo_mnmajor(smem + OFF_H, 16384), dhT_lo = desc_lo_mnmajor(smem + OFF_DH, 16384);
-  const uint32_t vnT_lo = desc_lo_mnmajor(smem + OFF_VN, 16384), duT_lo = desc_lo_mnmajor(smem + OFF_DU, 16384);
-
-  // ---- per-thread coordinates in the 16-lane accumulator shape ----
-  const int qd = warp & 3, cq = warp >> 2;
-  const int row_a = 16 * qd + (lane >> 2), row_b = row_a + 8, cp = 2 * (lane & 3);
-  const uint32_t lanes = (uint32_t)(qd * 32) << 16;
-  const int c128 = 32 * cq, c64 = 16 * cq;   // first column of this warp in 128- / 64-wide tiles
-  uint32_t phase = 0;
-  bool ok = true;
-  auto wait_mma = [&]() {
-    bool r = mbar_wait(&bars[BAR_MMA], phase, abort_flag);
-    phase ^= 1;
-    tc_fence_after();
-    return r;
-  };
-  // bf16 pair of a [64 x 128] row tile at (row, col), col even
-  auto tile2 = [&](int off, int row, int col) {
-    return ld_bf16x2(reinterpret_cast<const bf16*>(smem + off + (col >> 6) * 8192 + sw128_offset(row, col & 63)));
-  };
-  auto quad_sum = [&](float x) {
-    x += __shfl_xor_sync(0xffffffffu, x, 1);
-    x += __shfl_xor_sync(0xffffffffu, x, 2);
-    return x;
-  };
-  auto col_sum = [&](float x) {
-    x += __shfl_xor_sync(0xffffffffu, x, 4);
-    x += __shfl_xor_sync(0xffffffffu, x, 8);
-    x += __shfl_xor_sync(0xffffffffu, x, 16);
-    return x;
-  };
-  auto st_tile64 = [&](int off, int row, int col, float lo, float hi) {
-    *reinterpret_cast<uint32_t*>(smem + off + sw128_offset(row, col)) = pack_bf16(lo, hi);
-  };
-  auto round_sync = [&]() {
-    fence_proxy_async();
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-  };
-
+      Item cur = decode(blockIdx.x);
+      load_a(cur, 0);
+      load_b(cur);
+      load_c(cur);
+      bool ok = true;
+      uint32_t it = 0;
 #pragma unroll 1
-  for (long long w = blockIdx.x; w < total && ok; w += gridDim.x) {
-    const uint32_t lph = (uint32_t)((w / gridDim.x) & 1);
-    const bool has_next = w + gridDim.x < total;
-    Item nxt = cur;
-    if (has_next) nxt = decode(w + gridDim.x);
-    const int valid = cur.valid;
-    if (tid < CHUNK) {
-      sG[tid] = pre_g;
-      sGam[tid] = fast_exp(pre_g);
-      sRho[tid] = fast_exp(pre_gl - pre_g);
-      sBeta[tid] = pre_beta;
-      sDg[tid] = 0.f;
-      sDb[tid] = 0.f;
-    }
-    ok = mbar_wait(&bars[BAR_LOAD_A], lph, abort_flag) && mbar_wait(&bars[BAR_LOAD_B], lph, abort_flag);
-    if (ok && valid < CHUNK) {
-      zero_rows(OFF_Q, 2, valid);
-      if constexpr (TILED) {  // the transposed tiles already hold zeros past the sequence end
-        zero_rows(OFF_V, 2, valid);
-        zero_rows(OFF_DO, 2, valid);
-      } else {
-        zero_rows(OFF_V, 8, valid);  // v, v_new, dO, du
+      for (long long w = blockIdx.x; w < total && ok; w += gridDim.x, ++it) {
+        const uint32_t ph = it & 1;
+        const bool has_next = w + gridDim.x < total;
+        Item nxt = cur;
+        if (has_next) nxt = decode(w + gridDim.x);
+        const uint32_t k_lo = k_lo0 + (ph ? KBUF_LO : 0u), kmn_lo = kmn_lo0 + (ph ? KBUF_LO : 0u);
+        // the read-out warps have finished the previous item (accumulators free) and have zeroed
+        // the rows past the sequence end in this item's tiles (which also means: tiles landed)
+        ok = (it == 0 || WAIT(R_END, (it - 1) & 1)) && WAIT(R_ZERO, ph);
+        if (!ok) break;
+        tc_fence_after();
+        // ---- products that need only loaded tiles ----
+        if constexpr (TILED) {
+          umma_group<8, 128, 512, 128, 512, false>(tmem + T_DW, duT_lo, hT_lo, ID_MM_128);
+        } else {
+          umma_group<8, 2, 512, 2, 1024, false>(tmem + T_DW, du_lo, h_lo, ID_KK_128);
+        }
+        umma_commit(&bars[C_DW]);
+        if constexpr (TILED) {
+          umma_group<8, 2, 512, 128, 512, false>(tmem + T_DS, do_lo, vnT_lo, ID_KM_64);
+        } else {
+          umma_group<8, 2, 512, 2, 512, false>(tmem + T_DS, do_lo, vn_lo, ID_KK_64);
+        }
+        umma_group<8, 2, 512, 2, 512, false>(tmem + T_QK, q_lo, k_lo, ID_KK_64);
+        umma_commit(&bars[C_DSQK]);
+        // ---- dw is an operand now: the pieces of dA, and A^T dw, A^T du ----
+        ok = WAIT(R_DW, ph);
+        if (!ok) break;
+        tc_fence_after();
+        umma_group<8, 2, 512, 2, 512, false>(tmem + T_X1, dw_lo, k_lo, ID_KK_64);
+        if constexpr (TILED) umma_group<8, 128, 512, 2, 512, false>(tmem + T_X2, duT_lo, v_lo, ID_MK_64);
+        else umma_group<8, 2, 512, 2, 512, false>(tmem + T_X2, du_lo, v_lo, ID_KK_64);
+        umma_commit(&bars[C_X]);
+        // products off the dependent chain go behind the ones the read-out is waiting for
+        if constexpr (TILED) {
+          umma_group<8, 2, 512, 128, 512, false>(tmem + T_DQ1, do_lo, hT_lo, ID_KM_128);
+          umma_group<8, 128, 512, 128, 512, false>(tmem + T_DK1, vnT_lo, dhT_lo, ID_MM_128);
+        } else {
+          umma_group<8, 2, 512, 2, 1024, false>(tmem + T_DQ1, do_lo, h_lo, ID_KK_128);
+          umma_group<8, 2, 512, 2, 1024, false>(tmem + T_DK1, vn_lo, dh_lo, ID_KK_128);
+        }
+        umma_commit(&bars[C_1B]);
+        umma_group<4, 128, 0, 128, 0, false>(tmem + T_T1, amn_lo, dwmn_lo, ID_MM_128);
+        if constexpr (TILED) umma_group<4, 128, 0, 2, 0, false>(tmem + T_T2, amn_lo, du_lo, ID_MK_128);
+        else umma_group<4, 128, 0, 128, 0, false>(tmem + T_T2, amn_lo, dumn_lo, ID_MM_128);
+        // ---- ds is an operand now ----
+        ok = WAIT(R_DS, ph);
+        if (!ok) break;
+        tc_fence_after();
+        umma_group<4, 2, 0, 128, 0, false>(tmem + T_DQ2, ds_lo, kmn_lo, ID_KM_128);
+        umma_group<4, 128, 0, 128, 0, false>(tmem + T_DK2, dsmn_lo, qmn_lo, ID_MM_128);
+        umma_group<8, 2, 512, 2, 512, false>(tmem + T_KK, k_lo, k_lo, ID_KK_64);  // qk has been read
+        umma_commit(&bars[C_2B]);
+        // h, dh, dO, v_new are dead once the first products are complete and the h.dh sum is done
+        if (has_next) {
+          ok = WAIT(C_1B, ph) && WAIT(R_HD, ph);
+          if (!ok) break;
+          load_a(nxt, (int)(ph ^ 1));
+        }
+        // ---- dA -> T = A^T dA (and K K^T) ----
+        ok = WAIT(R_DA, ph);
+        if (!ok) break;
+        tc_fence_after();
+        umma_group<4, 128, 0, 128, 0, false>(tmem + T_T, amn_lo, damn_lo, ID_MM_64);
+        umma_commit(&bars[C_T]);
+        // ---- T -> d3 = T A^T ----
+        ok = WAIT(R_T, ph);
+        if (!ok) break;
+        tc_fence_after();
+        umma_group<4, 2, 0, 2, 0, false>(tmem + T_D3, da_lo, a_lo, ID_KK_64);
+        umma_commit(&bars[C_D3]);
+        if (has_next) {
+          // du, q, v are dead once their products are complete and the read-out has used q, v
+          ok = WAIT(C_2B, ph) && WAIT(R_E6, ph);
+          if (!ok) break;
+          load_b(nxt);
+          ok = WAIT(C_D3, ph);  // last product that reads A
+          if (!ok) break;
+          load_c(nxt);
+        }
+        // ---- dA3 -> dA3 K and (beta dA3)^T K ----
+        ok = WAIT(R_D3, ph);
+        if (!ok) break;
+        tc_fence_after();
+        umma_group<4, 2, 0, 128, 0, false>(tmem + T_T3, da_lo, kmn_lo, ID_KM_128);
+        umma_group<4, 128, 0, 128, 0, false>(tmem + T_DK5, dsmn_lo, kmn_lo, ID_MM_128);
+        umma_commit(&bars[C_5]);
+        cur = nxt;
       }
+      if (!ok) *abort_flag = 1;
     }
-    round_sync();
-    stamp();
-
-    // ======================= round 1: products with h and dh, ds, qk =======================
-    if (ok && tid == 0) {
-      if constexpr (TILED) {
-        umma_group<8, 128, 512, 128, 512, false>(tmem + T_DW, duT_lo, hT_lo, ID_MM_128);
-        umma_group<8, 2, 512, 128, 512, false>(tmem + T_DS, do_lo, vnT_lo, ID_KM_64);
-        umma_group<8, 2, 512, 128, 512, false>(tmem + T_DQ1, do_lo, hT_lo, ID_KM_128);
-        umma_group<8, 128, 512, 128, 512, false>(tmem + T_DK1, vnT_lo, dhT_lo, ID_MM_128);
-      } else {
-        umma_group<8, 2, 512, 2, 1024, false>(tmem + T_DW, du_lo, h_lo, ID_KK_128);
-        umma_group<8, 2, 512, 2, 512, false>(tmem + T_DS, do_lo, vn_lo, ID_KK_64);
-        umma_group<8, 2, 512, 2, 1024, false>(tmem + T_DQ1, do_lo, h_lo, ID_KK_128);
-        umma_group<8, 2, 512, 2, 1024, false>(tmem + T_DK1, vn_lo, dh_lo, ID_KK_128);
+  } else {
+    // ====================== read-out warps ======================
+    const int qd = warp & 3, cq = warp >> 2;
+    const int row_a = 16 * qd + (lane >> 2), row_b = row_a + 8, cp = 2 * (lane & 3);
+    const uint32_t lanes = (uint32_t)(qd * 32) << 16;
+    const int c128 = 32 * cq, c64 = 16 * cq;  // first column of this warp in 128- / 64-wide tiles
+    // bf16 pair of a [64 x 128] row tile at (row, col), col even
+    auto tile2 = [&](int off, int row, int col) {
+      return ld_bf16x2(reinterpret_cast<const bf16*>(smem + off + (col >> 6) * 8192 + sw128_offset(row, col & 63)));
+    };
+    auto quad_sum = [&](float x) {
+      x += __shfl_xor_sync(0xffffffffu, x, 1);
+      x += __shfl_xor_sync(0xffffffffu, x, 2);
+      return x;
+    };
+    auto col_sum = [&](float x) {
+      x += __shfl_xor_sync(0xffffffffu, x, 4);
+      x += __shfl_xor_sync(0xffffffffu, x, 8);
+      x += __shfl_xor_sync(0xffffffffu, x, 16);
+      return x;
+    };
+    auto st_tile64 = [&](int off, int row, int col, float lo, float hi) {
+      *reinterpret_cast<uint32_t*>(smem + off + sw128_offset(row, col)) = pack_bf16(lo, hi);
+    };
+    // this warp's part of a tile (or of the accumulators) is done: tell the issue warp
+    auto signal = [&](int bar) {
+      fence_proxy_async();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars[bar]);
+    };
+    auto zero_rows = [&](int off, int n_blocks, int valid) {
+      for (int blk = 0; blk < n_blocks; ++blk) {
+        unsigned char* base = smem + off + blk * 8192;
+        for (int i = tid; i < (CHUNK - valid) * 8; i += N_EPI)
+          *reinterpret_cast<uint4*>(base + (valid + (i >> 3)) * 128 + ((i & 7) << 4)) = make_uint4(0, 0, 0, 0);
       }
-    }
-    // meanwhile: gamma_last * sum(h * dh) over the whole 128 x 128 tiles (plain shared-memory reads)
-    if (ok) {
-      float hd = 0.f;
-      for (int i = tid; i < SQ_TILE / 16; i += NT) {
-        const uint4 a = *reinterpret_cast<const uint4*>(smem + OFF_H + i * 16);
-        const uint4 b = *reinterpret_cast<const uint4*>(smem + OFF_DH + i * 16);
-        const uint32_t* pa = &a.x;
-        const uint32_t* pb = &b.x;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          float2 fa = __bfloat1622float2(*reinterpret_cast<const bf162*>(&pa[e]));
-          float2 fb = __bfloat1622float2(*reinterpret_cast<const bf162*>(&pb[e]));
-          hd += fa.x * fb.x + fa.y * fb.y;
+    };
+    float pre_g = 0.f, pre_gl = 0.f, pre_beta = 0.f;
+    auto fetch_vectors = [&](const Item& t) {
+      if (tid < CHUNK) {
+        const int r = min(tid, t.valid - 1);
+        pre_g = p.g[(t.row0 + r) * p.Hv + t.hv];
+        pre_gl = p.g[(t.row0 + t.valid - 1) * p.Hv + t.hv];
+        pre_beta = tid < t.valid ? load_beta(p.beta, p.beta_is_f32, (t.row0 + tid) * p.Hv + t.hv) : 0.f;
+      }
+    };
+    Item cur = decode(blockIdx.x);
+    fetch_vectors(cur);
+    uint32_t it = 0;
+    const bool prof = p.profile && tid == 0 && blockIdx.x == 0;
+    int stamp_i = 0;
+    auto stamp = [&]() {
+      if (prof && stamp_i < 64) g_bwd_main_profile[stamp_i++] = clock64();
+    };
+#pragma unroll 1
+    for (long long w = blockIdx.x; w < total; w += gridDim.x, ++it) {
+      const uint32_t ph = it & 1;
+      const bool has_next = w + gridDim.x < total;
+      Item nxt = cur;
+      if (has_next) nxt = decode(w + gridDim.x);
+      const int valid = cur.valid;
+      const int koff = OFF_K + (int)ph * ROW_TILE;
+      if (tid < CHUNK) {
+        sG[tid] = pre_g;
+        sGam[tid] = fast_exp(pre_g);
+        sRho[tid] = fast_exp(pre_gl - pre_g);
+        sBeta[tid] = pre_beta;
+      }
+      stamp();
+      epi_barrier();
+      if (*stop_flag) break;  // written before the barrier by one thread: uniform
+      bool ok = WAIT(L_A, ph) && WAIT(L_B, ph) && WAIT(L_C, ph);
+      if (ok && valid < CHUNK) {
+        zero_rows(OFF_Q, 2, valid);
+        zero_rows(koff, 2, valid);
+        zero_rows(OFF_A, 1, valid);
+        if constexpr (TILED) {  // the transposed tiles already hold zeros past the sequence end
+          zero_rows(OFF_V, 2, valid);
+          zero_rows(OFF_DO, 2, valid);
+        } else {
+          zero_rows(OFF_V, 8, valid);  // v, v_new, dO, du
         }
       }
-#pragma unroll
-      for (int d = 16; d > 0; d >>= 1) hd += __shfl_xor_sync(0xffffffffu, hd, d);
-      if (lane == 0) atomicAdd(sDgLast, sGam[CHUNK - 1] * hd);
-    }
-    ok = ok && mbar_wait(&bars[BAR_LOAD_C], lph, abort_flag);
-    if (ok && valid < CHUNK) {
-      zero_rows(OFF_K, 2, valid);
-      zero_rows(OFF_A, 1, valid);
-      fence_proxy_async();
-    }
-    __syncthreads();
-    if (ok && tid == 0) {
-      umma_group<8, 2, 512, 2, 512, false>(tmem + T_QK, q_lo, k_lo, ID_KK_64);
-      umma_commit(&bars[BAR_MMA]);
-    }
-    const float g_a = sG[row_a], g_b = sG[row_b];
-    const float gam_a = sGam[row_a], gam_b = sGam[row_b];
-    const float rho_a = sRho[row_a], rho_b = sRho[row_b];
-    const float beta_a = sBeta[row_a], beta_b = sBeta[row_b];
-    float dq1[16], dkacc[16];
-    ok = ok && wait_mma();
-    stamp();
-    if (ok) {
-      {  // dw = -du h^T as an operand tile
+      signal(R_ZERO);
+      if (has_next) fetch_vectors(nxt);
+      stamp();
+      const float g_a = sG[row_a], g_b = sG[row_b];
+      const float gam_a = sGam[row_a], gam_b = sGam[row_b];
+      const float rho_a = sRho[row_a], rho_b = sRho[row_b];
+      const float beta_a = sBeta[row_a], beta_b = sBeta[row_b];
+      const long long out_a = ((cur.row0 + row_a) * p.Hv + cur.hv) * D, out_b = ((cur.row0 + row_b) * p.Hv + cur.hv) * D;
+      const bool wr_a = row_a < valid, wr_b = row_b < valid;
+      float dq1[16], dkacc[16];
+      // this thread's share of the row sums (dg, db), column sums (dg) and of the chunk total;
+      // reduced across lanes once, at the end of the item
+      float acc_dg_a = 0.f, acc_dg_b = 0.f, acc_db_a = 0.f, acc_db_b = 0.f, acc_last = 0.f;
+      float acc_col[4] = {0.f, 0.f, 0.f, 0.f};
+
+      // ---- E1: dw = -du h^T as an operand tile ----
+      ok = ok && WAIT(C_DW, ph);
+      stamp();
+      if (ok) {
+        tc_fence_after();
         float dw[16];
         tmem_ld_16x32(tmem + lanes + T_DW + c128, dw);
         tmem_ld_wait();
@@ -389,7 +458,33 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
           *reinterpret_cast<uint32_t*>(base + sw128_offset(row_b, col & 63)) = pack_bf16(-dw[4 * i + 2], -dw[4 * i + 3]);
         }
       }
-      {  // ds = scale * G * (dO Vn^T); ds2 = ds * (Q K^T)
+      signal(R_DW);
+      // gamma_last * sum(h * dh) over the whole 128 x 128 tiles (plain shared-memory reads), while
+      // the issue warp works on the products that wait for dw
+      if (ok) {
+        float hd = 0.f;
+        for (int i = tid; i < SQ_TILE / 16; i += N_EPI) {
+          const uint4 a = *reinterpret_cast<const uint4*>(smem + OFF_H + i * 16);
+          const uint4 b = *reinterpret_cast<const uint4*>(smem + OFF_DH + i * 16);
+          const uint32_t* pa = &a.x;
+          const uint32_t* pb = &b.x;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float2 fa = __bfloat1622float2(*reinterpret_cast<const bf162*>(&pa[e]));
+            float2 fb = __bfloat1622float2(*reinterpret_cast<const bf162*>(&pb[e]));
+            hd += fa.x * fb.x + fa.y * fb.y;
+          }
+        }
+        acc_last += sGam[CHUNK - 1] * hd;
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars[R_HD]);
+
+      // ---- E2: ds = scale * G * (dO Vn^T); ds2 = ds * (Q K^T) ----
+      ok = ok && WAIT(C_DSQK, ph);
+      stamp();
+      if (ok) {
+        tc_fence_after();
         float ds[8], qk[8];
         tmem_ld_16x16(tmem + lanes + T_DS + c64, ds);
         tmem_ld_16x16(tmem + lanes + T_QK + c64, qk);
@@ -408,77 +503,19 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
           const float s0 = a0 * qk[4 * i], s1 = a1 * qk[4 * i + 1], s2 = b0 * qk[4 * i + 2], s3 = b1 * qk[4 * i + 3];
           rs_a += s0 + s1;
           rs_b += s2 + s3;
-          const float c0 = col_sum(s0 + s2), c1 = col_sum(s1 + s3);
-          if (lane < 4) {
-            atomicAdd(sDg + col, -c0);
-            atomicAdd(sDg + col + 1, -c1);
-          }
+          acc_col[2 * i] += s0 + s2;
+          acc_col[2 * i + 1] += s1 + s3;
         }
-        rs_a = quad_sum(rs_a);
-        rs_b = quad_sum(rs_b);
-        if ((lane & 3) == 0) {
-          atomicAdd(sDg + row_a, rs_a);
-          atomicAdd(sDg + row_b, rs_b);
-        }
+        acc_dg_a += rs_a;
+        acc_dg_b += rs_b;
       }
-      // dq1 = scale * gamma * (dO h^T), dg += rowsum(q * dq1)
-      // dk1 = rho * (Vn dh^T), dg -= rowsum(k * dk1), dg_last += sum(k * dk1)
-      tmem_ld_16x32(tmem + lanes + T_DQ1 + c128, dq1);
-      tmem_ld_16x32(tmem + lanes + T_DK1 + c128, dkacc);
-      tmem_ld_wait();
-      float qa = 0.f, qb = 0.f, ka = 0.f, kb = 0.f;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int col = c128 + 8 * i + cp;
-        dq1[4 * i] *= p.scale * gam_a;
-        dq1[4 * i + 1] *= p.scale * gam_a;
-        dq1[4 * i + 2] *= p.scale * gam_b;
-        dq1[4 * i + 3] *= p.scale * gam_b;
-        dkacc[4 * i] *= rho_a;
-        dkacc[4 * i + 1] *= rho_a;
-        dkacc[4 * i + 2] *= rho_b;
-        dkacc[4 * i + 3] *= rho_b;
-        const float2 q_a = tile2(OFF_Q, row_a, col), q_b = tile2(OFF_Q, row_b, col);
-        const float2 k_a = tile2(OFF_K, row_a, col), k_b = tile2(OFF_K, row_b, col);
-        qa += q_a.x * dq1[4 * i] + q_a.y * dq1[4 * i + 1];
-        qb += q_b.x * dq1[4 * i + 2] + q_b.y * dq1[4 * i + 3];
-        ka += k_a.x * dkacc[4 * i] + k_a.y * dkacc[4 * i + 1];
-        kb += k_b.x * dkacc[4 * i + 2] + k_b.y * dkacc[4 * i + 3];
-      }
-      qa = quad_sum(qa - ka);
-      qb = quad_sum(qb - kb);
-      float kt = ka + kb;
-#pragma unroll
-      for (int d = 16; d > 0; d >>= 1) kt += __shfl_xor_sync(0xffffffffu, kt, d);
-      if ((lane & 3) == 0) {
-        atomicAdd(sDg + row_a, qa);
-        atomicAdd(sDg + row_b, qb);
-      }
-      if (lane == 0) atomicAdd(sDgLast, kt);
-    }
-    round_sync();
-    stamp();
+      signal(R_DS);
 
-    // ======================= round 2: ds products, dA pieces, A^T dw, A^T du =======================
-    if (ok && tid == 0) {
-      if (has_next) load_a(nxt);  // h, dh, dO, v_new of this item are dead
-      umma_group<8, 2, 512, 2, 512, false>(tmem + T_X1, dw_lo, k_lo, ID_KK_64);
-      if constexpr (TILED) umma_group<8, 128, 512, 2, 512, false>(tmem + T_X2, duT_lo, v_lo, ID_MK_64);
-      else umma_group<8, 2, 512, 2, 512, false>(tmem + T_X2, du_lo, v_lo, ID_KK_64);
-      umma_group<4, 2, 0, 128, 0, false>(tmem + T_DQ2, ds_lo, kmn_lo, ID_KM_128);
-      umma_group<4, 128, 0, 128, 0, false>(tmem + T_DK2, dsmn_lo, qmn_lo, ID_MM_128);
-      umma_group<4, 128, 0, 128, 0, false>(tmem + T_T1, amn_lo, dwmn_lo, ID_MM_128);
-      if constexpr (TILED) umma_group<4, 128, 0, 2, 0, false>(tmem + T_T2, amn_lo, du_lo, ID_MK_128);
-      else umma_group<4, 128, 0, 128, 0, false>(tmem + T_T2, amn_lo, dumn_lo, ID_MM_128);
-      umma_commit(&bars[BAR_MMA]);
-    }
-    if (has_next) fetch_vectors(nxt);
-    const long long out_a = ((cur.row0 + row_a) * p.Hv + cur.hv) * D, out_b = ((cur.row0 + row_b) * p.Hv + cur.hv) * D;
-    const bool wr_a = row_a < valid, wr_b = row_b < valid;
-    ok = ok && wait_mma();
-    stamp();
-    if (ok) {
-      {  // dA = strict_lower(beta_c (gamma_c x1 + x2))
+      // ---- E3: dA = strict_lower(beta_c (gamma_c x1 + x2)) ----
+      ok = ok && WAIT(C_X, ph);
+      stamp();
+      if (ok) {
+        tc_fence_after();
         float x1[8], x2[8];
         tmem_ld_16x16(tmem + lanes + T_X1 + c64, x1);
         tmem_ld_16x16(tmem + lanes + T_X2 + c64, x2);
@@ -493,192 +530,220 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
                     col + 1 < row_b ? b1 * (g1 * x1[4 * i + 3] + x2[4 * i + 3]) : 0.f);
         }
       }
-    }
-    // the dA tile is all the next product needs: hand it over before the rest of this round
-    round_sync();
-    if (ok && tid == 0) {
-      umma_group<4, 128, 0, 128, 0, false>(tmem + T_T, amn_lo, damn_lo, ID_MM_64);
-      umma_group<8, 2, 512, 2, 512, false>(tmem + T_KK, k_lo, k_lo, ID_KK_64);
-      umma_commit(&bars[BAR_MMA]);
-    }
-    if (ok) {
-      {  // dq = dq1 + ds K
-        float x[16];
-        tmem_ld_16x32(tmem + lanes + T_DQ2 + c128, x);
+      signal(R_DA);
+
+      // ---- E4: dq1 = scale * gamma * (dO h^T), dk1 = rho * (Vn dh^T) and their dg terms ----
+      ok = ok && WAIT(C_1B, ph);
+      stamp();
+      if (ok) {
+        tc_fence_after();
+        tmem_ld_16x32(tmem + lanes + T_DQ1 + c128, dq1);
+        tmem_ld_16x32(tmem + lanes + T_DK1 + c128, dkacc);
         tmem_ld_wait();
+        float qa = 0.f, qb = 0.f, ka = 0.f, kb = 0.f;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int col = c128 + 8 * i + cp;
-          if (wr_a) *reinterpret_cast<uint32_t*>(p.dq + out_a + col) = pack_bf16(dq1[4 * i] + x[4 * i], dq1[4 * i + 1] + x[4 * i + 1]);
-          if (wr_b) *reinterpret_cast<uint32_t*>(p.dq + out_b + col) = pack_bf16(dq1[4 * i + 2] + x[4 * i + 2], dq1[4 * i + 3] + x[4 * i + 3]);
+          dq1[4 * i] *= p.scale * gam_a;
+          dq1[4 * i + 1] *= p.scale * gam_a;
+          dq1[4 * i + 2] *= p.scale * gam_b;
+          dq1[4 * i + 3] *= p.scale * gam_b;
+          dkacc[4 * i] *= rho_a;
+          dkacc[4 * i + 1] *= rho_a;
+          dkacc[4 * i + 2] *= rho_b;
+          dkacc[4 * i + 3] *= rho_b;
+          const float2 q_a = tile2(OFF_Q, row_a, col), q_b = tile2(OFF_Q, row_b, col);
+          const float2 k_a = tile2(koff, row_a, col), k_b = tile2(koff, row_b, col);
+          qa += q_a.x * dq1[4 * i] + q_a.y * dq1[4 * i + 1];
+          qb += q_b.x * dq1[4 * i + 2] + q_b.y * dq1[4 * i + 3];
+          ka += k_a.x * dkacc[4 * i] + k_a.y * dkacc[4 * i + 1];
+          kb += k_b.x * dkacc[4 * i + 2] + k_b.y * dkacc[4 * i + 3];
+        }
+        acc_dg_a += qa - ka;
+        acc_dg_b += qb - kb;
+        acc_last += ka + kb;
+      }
+
+      // ---- E5: T = A^T dA as an operand tile (over dA, which the product has consumed) ----
+      ok = ok && WAIT(C_T, ph);
+      stamp();
+      if (ok) {
+        tc_fence_after();
+        float t[8];
+        tmem_ld_16x16(tmem + lanes + T_T + c64, t);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int col = c64 + 8 * i + cp;
+          st_tile64(OFF_DA, row_a, col, t[4 * i], t[4 * i + 1]);
+          st_tile64(OFF_DA, row_b, col, t[4 * i + 2], t[4 * i + 3]);
         }
       }
-      {  // dk += ds^T Q + beta gamma (A^T dw);  db += gamma rowsum(t1 k);  dg += beta gamma rowsum(t1 k)
-        float x[16], t1[16];
-        tmem_ld_16x32(tmem + lanes + T_DK2 + c128, x);
-        tmem_ld_16x32(tmem + lanes + T_T1 + c128, t1);
+      signal(R_T);
+
+      // ---- E6: dq out; dk += ds^T Q + beta gamma (A^T dw); dv = beta (A^T du); db terms ----
+      ok = ok && WAIT(C_2B, ph);
+      stamp();
+      if (ok) {
+        tc_fence_after();
+        {
+          float x[16];
+          tmem_ld_16x32(tmem + lanes + T_DQ2 + c128, x);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int col = c128 + 8 * i + cp;
+            if (wr_a) *reinterpret_cast<uint32_t*>(p.dq + out_a + col) = pack_bf16(dq1[4 * i] + x[4 * i], dq1[4 * i + 1] + x[4 * i + 1]);
+            if (wr_b) *reinterpret_cast<uint32_t*>(p.dq + out_b + col) = pack_bf16(dq1[4 * i + 2] + x[4 * i + 2], dq1[4 * i + 3] + x[4 * i + 3]);
+          }
+        }
+        {
+          float x[16], t1[16];
+          tmem_ld_16x32(tmem + lanes + T_DK2 + c128, x);
+          tmem_ld_16x32(tmem + lanes + T_T1 + c128, t1);
+          tmem_ld_wait();
+          float sa = 0.f, sb = 0.f;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int col = c128 + 8 * i + cp;
+            const float2 k_a = tile2(koff, row_a, col), k_b = tile2(koff, row_b, col);
+            sa += k_a.x * t1[4 * i] + k_a.y * t1[4 * i + 1];
+            sb += k_b.x * t1[4 * i + 2] + k_b.y * t1[4 * i + 3];
+            dkacc[4 * i] += x[4 * i] + beta_a * gam_a * t1[4 * i];
+            dkacc[4 * i + 1] += x[4 * i + 1] + beta_a * gam_a * t1[4 * i + 1];
+            dkacc[4 * i + 2] += x[4 * i + 2] + beta_b * gam_b * t1[4 * i + 2];
+            dkacc[4 * i + 3] += x[4 * i + 3] + beta_b * gam_b * t1[4 * i + 3];
+          }
+          acc_db_a += gam_a * sa;
+          acc_db_b += gam_b * sb;
+          acc_dg_a += beta_a * gam_a * sa;
+          acc_dg_b += beta_b * gam_b * sb;
+        }
+        {
+          float t2[16];
+          tmem_ld_16x32(tmem + lanes + T_T2 + c128, t2);
+          tmem_ld_wait();
+          float sa = 0.f, sb = 0.f;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int col = c128 + 8 * i + cp;
+            const float2 v_a = tile2(OFF_V, row_a, col), v_b = tile2(OFF_V, row_b, col);
+            sa += v_a.x * t2[4 * i] + v_a.y * t2[4 * i + 1];
+            sb += v_b.x * t2[4 * i + 2] + v_b.y * t2[4 * i + 3];
+            if (wr_a) *reinterpret_cast<uint32_t*>(p.dv + out_a + col) = pack_bf16(beta_a * t2[4 * i], beta_a * t2[4 * i + 1]);
+            if (wr_b) *reinterpret_cast<uint32_t*>(p.dv + out_b + col) = pack_bf16(beta_b * t2[4 * i + 2], beta_b * t2[4 * i + 3]);
+          }
+          acc_db_a += sa;
+          acc_db_b += sb;
+        }
+      }
+      signal(R_E6);
+
+      // ---- E7: dA3 = -G * d3 (over T) and diag(beta) dA3 (over ds), both consumed by now ----
+      ok = ok && WAIT(C_D3, ph);
+      stamp();
+      if (ok) {
+        tc_fence_after();
+        float d3[8], kk[8];
+        tmem_ld_16x16(tmem + lanes + T_D3 + c64, d3);
+        tmem_ld_16x16(tmem + lanes + T_KK + c64, kk);
+        tmem_ld_wait();
+        float rs_a = 0.f, rs_b = 0.f;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const int col = c64 + 8 * i + cp;
+          const float gc0 = sG[col], gc1 = sG[col + 1];
+          const float a0 = col < row_a ? -d3[4 * i] * fast_exp(g_a - gc0) : 0.f;
+          const float a1 = col + 1 < row_a ? -d3[4 * i + 1] * fast_exp(g_a - gc1) : 0.f;
+          const float b0 = col < row_b ? -d3[4 * i + 2] * fast_exp(g_b - gc0) : 0.f;
+          const float b1 = col + 1 < row_b ? -d3[4 * i + 3] * fast_exp(g_b - gc1) : 0.f;
+          st_tile64(OFF_DA, row_a, col, a0, a1);
+          st_tile64(OFF_DA, row_b, col, b0, b1);
+          st_tile64(OFF_DS, row_a, col, beta_a * a0, beta_a * a1);
+          st_tile64(OFF_DS, row_b, col, beta_b * b0, beta_b * b1);
+          const float s0 = a0 * beta_a * kk[4 * i], s1 = a1 * beta_a * kk[4 * i + 1];
+          const float s2 = b0 * beta_b * kk[4 * i + 2], s3 = b1 * beta_b * kk[4 * i + 3];
+          rs_a += s0 + s1;
+          rs_b += s2 + s3;
+          acc_col[2 * i] += s0 + s2;
+          acc_col[2 * i + 1] += s1 + s3;
+        }
+        acc_dg_a += rs_a;
+        acc_dg_b += rs_b;
+      }
+      signal(R_D3);
+
+      // ---- E8: dk out; db += rowsum((dA3 K) k) ----
+      ok = ok && WAIT(C_5, ph);
+      stamp();
+      if (ok) {
+        tc_fence_after();
+        float t3[16], x[16];
+        tmem_ld_16x32(tmem + lanes + T_T3 + c128, t3);
+        tmem_ld_16x32(tmem + lanes + T_DK5 + c128, x);
         tmem_ld_wait();
         float sa = 0.f, sb = 0.f;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int col = c128 + 8 * i + cp;
-          const float2 k_a = tile2(OFF_K, row_a, col), k_b = tile2(OFF_K, row_b, col);
-          sa += k_a.x * t1[4 * i] + k_a.y * t1[4 * i + 1];
-          sb += k_b.x * t1[4 * i + 2] + k_b.y * t1[4 * i + 3];
-          dkacc[4 * i] += x[4 * i] + beta_a * gam_a * t1[4 * i];
-          dkacc[4 * i + 1] += x[4 * i + 1] + beta_a * gam_a * t1[4 * i + 1];
-          dkacc[4 * i + 2] += x[4 * i + 2] + beta_b * gam_b * t1[4 * i + 2];
-          dkacc[4 * i + 3] += x[4 * i + 3] + beta_b * gam_b * t1[4 * i + 3];
+          const float2 k_a = tile2(koff, row_a, col), k_b = tile2(koff, row_b, col);
+          sa += k_a.x * t3[4 * i] + k_a.y * t3[4 * i + 1];
+          sb += k_b.x * t3[4 * i + 2] + k_b.y * t3[4 * i + 3];
+          if (wr_a)
+            *reinterpret_cast<uint32_t*>(p.dk + out_a + col) =
+                pack_bf16(dkacc[4 * i] + beta_a * t3[4 * i] + x[4 * i], dkacc[4 * i + 1] + beta_a * t3[4 * i + 1] + x[4 * i + 1]);
+          if (wr_b)
+            *reinterpret_cast<uint32_t*>(p.dk + out_b + col) =
+                pack_bf16(dkacc[4 * i + 2] + beta_b * t3[4 * i + 2] + x[4 * i + 2], dkacc[4 * i + 3] + beta_b * t3[4 * i + 3] + x[4 * i + 3]);
         }
-        sa = quad_sum(sa);
-        sb = quad_sum(sb);
-        if ((lane & 3) == 0) {
-          atomicAdd(sDb + row_a, gam_a * sa);
-          atomicAdd(sDb + row_b, gam_b * sb);
-          atomicAdd(sDg + row_a, beta_a * gam_a * sa);
-          atomicAdd(sDg + row_b, beta_b * gam_b * sb);
-        }
+        acc_db_a += sa;
+        acc_db_b += sb;
       }
-      {  // dv = beta (A^T du);  db += rowsum(t2 v)
-        float t2[16];
-        tmem_ld_16x32(tmem + lanes + T_T2 + c128, t2);
-        tmem_ld_wait();
-        float sa = 0.f, sb = 0.f;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int col = c128 + 8 * i + cp;
-          const float2 v_a = tile2(OFF_V, row_a, col), v_b = tile2(OFF_V, row_b, col);
-          sa += v_a.x * t2[4 * i] + v_a.y * t2[4 * i + 1];
-          sb += v_b.x * t2[4 * i + 2] + v_b.y * t2[4 * i + 3];
-          if (wr_a) *reinterpret_cast<uint32_t*>(p.dv + out_a + col) = pack_bf16(beta_a * t2[4 * i], beta_a * t2[4 * i + 1]);
-          if (wr_b) *reinterpret_cast<uint32_t*>(p.dv + out_b + col) = pack_bf16(beta_b * t2[4 * i + 2], beta_b * t2[4 * i + 3]);
-        }
-        sa = quad_sum(sa);
-        sb = quad_sum(sb);
-        if ((lane & 3) == 0) {
-          atomicAdd(sDb + row_a, sa);
-          atomicAdd(sDb + row_b, sb);
-        }
-      }
-    }
-    stamp();
-
-    // ======================= round 3: T = A^T dA, K K^T (issued above) =======================
-    ok = ok && wait_mma();
-    stamp();
-    if (ok) {
-      float t[8];
-      tmem_ld_16x16(tmem + lanes + T_T + c64, t);
-      tmem_ld_wait();
-#pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const int col = c64 + 8 * i + cp;
-        st_tile64(OFF_DS, row_a, col, t[4 * i], t[4 * i + 1]);
-        st_tile64(OFF_DS, row_b, col, t[4 * i + 2], t[4 * i + 3]);
-      }
-    }
-    round_sync();
-    stamp();
-
-    // ======================= round 4: d3 = T A^T =======================
-    if (ok && tid == 0) {
-      if (has_next) load_b(nxt);  // du, q, v of this item are dead
-      umma_group<4, 2, 0, 2, 0, false>(tmem + T_D3, ds_lo, a_lo, ID_KK_64);
-      umma_commit(&bars[BAR_MMA]);
-    }
-    ok = ok && wait_mma();
-    stamp();
-    if (ok) {
-      float d3[8], kk[8];
-      tmem_ld_16x16(tmem + lanes + T_D3 + c64, d3);
-      tmem_ld_16x16(tmem + lanes + T_KK + c64, kk);
-      tmem_ld_wait();
-      float rs_a = 0.f, rs_b = 0.f;
-#pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const int col = c64 + 8 * i + cp;
-        const float gc0 = sG[col], gc1 = sG[col + 1];
-        const float a0 = col < row_a ? -d3[4 * i] * fast_exp(g_a - gc0) : 0.f;
-        const float a1 = col + 1 < row_a ? -d3[4 * i + 1] * fast_exp(g_a - gc1) : 0.f;
-        const float b0 = col < row_b ? -d3[4 * i + 2] * fast_exp(g_b - gc0) : 0.f;
-        const float b1 = col + 1 < row_b ? -d3[4 * i + 3] * fast_exp(g_b - gc1) : 0.f;
-        st_tile64(OFF_D3, row_a, col, a0, a1);
-        st_tile64(OFF_D3, row_b, col, b0, b1);
-        st_tile64(OFF_D3B, row_a, col, beta_a * a0, beta_a * a1);
-        st_tile64(OFF_D3B, row_b, col, beta_b * b0, beta_b * b1);
-        const float s0 = a0 * beta_a * kk[4 * i], s1 = a1 * beta_a * kk[4 * i + 1];
-        const float s2 = b0 * beta_b * kk[4 * i + 2], s3 = b1 * beta_b * kk[4 * i + 3];
-        rs_a += s0 + s1;
-        rs_b += s2 + s3;
-        const float c0 = col_sum(s0 + s2), c1 = col_sum(s1 + s3);
-        if (lane < 4) {
-          atomicAdd(sDg + col, -c0);
-          atomicAdd(sDg + col + 1, -c1);
-        }
-      }
-      rs_a = quad_sum(rs_a);
-      rs_b = quad_sum(rs_b);
+      stamp();
+      signal(R_END);  // accumulators and k of this item are free
+      // one reduction per quantity, one plain store per (warp, row or column): no atomics
+      acc_dg_a = quad_sum(acc_dg_a);
+      acc_dg_b = quad_sum(acc_dg_b);
+      acc_db_a = quad_sum(acc_db_a);
+      acc_db_b = quad_sum(acc_db_b);
       if ((lane & 3) == 0) {
-        atomicAdd(sDg + row_a, rs_a);
-        atomicAdd(sDg + row_b, rs_b);
+        sRowDg[cq * 64 + row_a] = acc_dg_a;
+        sRowDg[cq * 64 + row_b] = acc_dg_b;
+        sRowDb[cq * 64 + row_a] = acc_db_a;
+        sRowDb[cq * 64 + row_b] = acc_db_b;
       }
-    }
-    round_sync();
-    stamp();
-
-    // ======================= round 5: dA3 K and (beta dA3)^T K =======================
-    if (ok && tid == 0) {
-      umma_group<4, 2, 0, 128, 0, false>(tmem + T_T3, d3_lo, kmn_lo, ID_KM_128);
-      umma_group<4, 128, 0, 128, 0, false>(tmem + T_DK5, d3bmn_lo, kmn_lo, ID_MM_128);
-      umma_commit(&bars[BAR_MMA]);
-    }
-    ok = ok && wait_mma();
-    stamp();
-    if (ok) {
-      float t3[16], x[16];
-      tmem_ld_16x32(tmem + lanes + T_T3 + c128, t3);
-      tmem_ld_16x32(tmem + lanes + T_DK5 + c128, x);
-      tmem_ld_wait();
-      float sa = 0.f, sb = 0.f;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int col = c128 + 8 * i + cp;
-        const float2 k_a = tile2(OFF_K, row_a, col), k_b = tile2(OFF_K, row_b, col);
-        sa += k_a.x * t3[4 * i] + k_a.y * t3[4 * i + 1];
-        sb += k_b.x * t3[4 * i + 2] + k_b.y * t3[4 * i + 3];
-        if (wr_a)
-          *reinterpret_cast<uint32_t*>(p.dk + out_a + col) =
-              pack_bf16(dkacc[4 * i] + beta_a * t3[4 * i] + x[4 * i], dkacc[4 * i + 1] + beta_a * t3[4 * i + 1] + x[4 * i + 1]);
-        if (wr_b)
-          *reinterpret_cast<uint32_t*>(p.dk + out_b + col) =
-              pack_bf16(dkacc[4 * i + 2] + beta_b * t3[4 * i + 2] + x[4 * i + 2], dkacc[4 * i + 3] + beta_b * t3[4 * i + 3] + x[4 * i + 3]);
+      for (int j = 0; j < 4; ++j) {
+        const float c = col_sum(acc_col[j]);
+        if (lane < 4) sColDg[qd * 64 + c64 + 8 * (j >> 1) + cp + (j & 1)] = c;
       }
-      sa = quad_sum(sa);
-      sb = quad_sum(sb);
-      if ((lane & 3) == 0) {
-        atomicAdd(sDb + row_a, sa);
-        atomicAdd(sDb + row_b, sb);
+#pragma unroll
+      for (int d = 16; d > 0; d >>= 1) acc_last += __shfl_xor_sync(0xffffffffu, acc_last, d);
+      if (lane == 0) sLast[warp] = acc_last;
+      if (!ok) *abort_flag = 1;
+      epi_barrier();  // every contribution to dg, db is in
+      if (tid == 0 && *abort_flag) *stop_flag = 1;
+      if (tid < valid) {
+        float dgv = 0.f, dbv = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          dgv += sRowDg[j * 64 + tid] - sColDg[j * 64 + tid];
+          dbv += sRowDb[j * 64 + tid];
+        }
+        if (tid == valid - 1) {
+#pragma unroll
+          for (int j = 0; j < N_EPI / 32; ++j) dgv += sLast[j];
+        }
+        p.dg[(cur.row0 + tid) * p.Hv + cur.hv] = dgv;
+        p.db[(cur.row0 + tid) * p.Hv + cur.hv] = dbv;
       }
+      cur = nxt;
     }
-    tc_fence_before();
-    ok = __syncthreads_and(ok);  // a wait given up by one thread ends the loop for all of them
-    tc_fence_after();
-    stamp();
-    if (ok && tid == 0 && has_next) load_c(nxt);  // k, A of this item are dead
-    if (tid < valid) {
-      float dgv = sDg[tid];
-      if (tid == valid - 1) {  // the only reader of the chunk total also clears it for the next item
-        dgv += *sDgLast;
-        *sDgLast = 0.f;
-      }
-      p.dg[(cur.row0 + tid) * p.Hv + cur.hv] = dgv;
-      p.db[(cur.row0 + tid) * p.Hv + cur.hv] = sDb[tid];
-    }
-    cur = nxt;
   }
+  tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, 512);
-  if (tid == 0 && (*abort_flag || !ok)) atomicCAS(&g_bwd_main_status, 0, 1);
+  if (tid == 0 && *abort_flag) atomicCAS(&g_bwd_main_status, 0, 1);
 }
 
 int bwd_main_tc_status(int* out, int reset) {
@@ -694,8 +759,8 @@ int bwd_main_tc_status(int* out, int reset) {
 }
 
 }  // namespace fqla
-extern "C" int fqla_debug_bwd_main_profile(long long* out16) {
-  return (int)cudaMemcpyFromSymbol(out16, fqla::g_bwd_main_profile, sizeof(long long) * 16);
+extern "C" int fqla_debug_bwd_main_profile(long long* out64) {
+  return (int)cudaMemcpyFromSymbol(out64, fqla::g_bwd_main_profile, sizeof(long long) * 64);
 }
 namespace fqla {
 
