@@ -326,13 +326,14 @@ def run_ours(args):
     else:
         kernel_name = "bwd_main_tc_kernel"
         fw = ops.fwd_seq(None, x["k"], x["v"], A, g_cum, x["beta"], scale, run_h0, output_o=False,
-                         output_h=True, output_vnew=True, tables=run_tables)
+                         output_h=True, output_vnew=True, tables=run_tables, operand_tiles=True)
         bw = ops.bwd_dh(x["q"], x["k"], A, g_cum, x["beta"], x["do"], scale, None,
-                        tables=run_tables)
+                        tables=run_tables, operand_tiles=True)
 
         def dominant():
             ops.bwd_main(x["q"], x["k"], x["v"], fw["vnew"], A, g_cum, x["beta"], x["do"],
-                         bw["du"], fw["h"], bw["dh"], scale, tables=run_tables)
+                         bw["du"], fw["h"], bw["dh"], scale, tables=run_tables,
+                         operand_tiles=True)
 
         # per (token, value head): q,k / v,vnew,do,du / A / h,dh (2 x 32 KiB per 64 tokens) /
         # g,beta / dq,dk,dv / dg,db

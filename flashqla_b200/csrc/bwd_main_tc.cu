@@ -165,7 +165,8 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
     }
     const SeqSpan sp = p.lay.span(seq);
     t.row0 = sp.bos + (long long)ci * CHUNK;
-    t.valid = min(CHUNK, sp.len - ci * CHUNK);
+    // clamped: a table row that does not belong to its sequence must not index outside the tiles
+    t.valid = max(1, min(CHUNK, sp.len - ci * CHUNK));
     t.chunk_id = sp.chunk_base + ci;
     return t;
   };

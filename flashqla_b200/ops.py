@@ -49,7 +49,7 @@ class SeqTables:
             if B != 1:
                 raise ValueError("packed input (cu_seqlens) needs batch size 1")
             self.N = cu_seqlens.numel() - 1
-            self.chunk_indices = prepare_chunk_indices(cu_seqlens, CHUNK_SIZE)
+            self.chunk_indices = _kernel_chunk_indices(cu_seqlens)
             self.chunk_offsets, self.num_chunks = prepare_chunk_offsets(cu_seqlens, CHUNK_SIZE)
             self.is64 = int(cu_seqlens.dtype == torch.int64)
 
@@ -61,6 +61,24 @@ class SeqTables:
     @property
     def args(self):
         return _ptr(self.cu), _ptr(self.chunk_offsets), self.is64, self.N
+
+
+@tensor_cache
+def _kernel_chunk_indices(cu_seqlens: torch.Tensor) -> torch.Tensor:
+    """``[NT, 2]`` (sequence, chunk in sequence) rows for the chunk-parallel kernels.  The public
+    ``prepare_chunk_indices`` keeps the reference's numbering, in which a zero-length sequence
+    does not consume a sequence id; the kernels index ``cu_seqlens`` with the id, so they get
+    the position of the sequence in ``cu_seqlens`` instead.  Without zero-length sequences the
+    two tables are the same tensor."""
+    table = prepare_chunk_indices(cu_seqlens, CHUNK_SIZE)
+    lens = torch.diff(cu_seqlens)
+    if bool((lens > 0).all()):
+        return table
+    counts = (lens + CHUNK_SIZE - 1) // CHUNK_SIZE
+    seq = torch.repeat_interleave(torch.arange(lens.numel(), device=cu_seqlens.device), counts)
+    fixed = table.clone()
+    fixed[:, 0] = seq.to(table.dtype)
+    return fixed
 
 
 @tensor_cache

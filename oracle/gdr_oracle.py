@@ -143,6 +143,11 @@ def chunk_gdr_fwd(q, k, v, g, beta, scale=None, initial_state=None, cu_seqlens=N
             if initial_state is None
             else initial_state[n].to(v.dtype)
         )
+        if e == s:  # zero-length sequence: no rows, no chunks, the state passes through
+            finals.append(S0)
+            g_out.append(g[b, s:e]), A_out.append(g.new_zeros(0, Hv, chunk_size))
+            o_out.append(v[b, s:e]), h_out.append(v.new_zeros(0, Hv, K, V))
+            continue
         gc, A, o, h, S = _chunk_one_sequence(
             qe[b, s:e], ke[b, s:e], v[b, s:e], g[b, s:e], beta[b, s:e], scale, S0, chunk_size
         )

@@ -1,0 +1,178 @@
+"""Kernel-level checks through the C ABI: the two implementations of each K = V = 128 kernel
+(tcgen05 and mma.sync) against each other, the operand-tile hand-off against the row-major one,
+and the small context-parallel kernels against host restatements."""
+
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from oracle import gdr_oracle as orc
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _inputs(T, Hq, Hv, seed, cu=None):
+    cu_t = None if cu is None else torch.tensor(cu, dtype=torch.int32)
+    x = orc.make_inputs(1, T, Hq, Hv, 128, 128, seed=seed, cu_seqlens=cu_t, with_h0=True)
+    d = {n: t.to(DEV) for n, t in x.items()}
+    for n in ("q", "k", "v", "beta", "do"):
+        d[n] = d[n].bfloat16()
+    d["cu_seqlens"] = None if cu_t is None else cu_t.to(DEV)
+    return d
+
+
+def _prep(d):
+    from flashqla_b200 import ops
+
+    cu = d.get("cu_seqlens")
+    tables = ops.SeqTables(1, d["k"].shape[1], cu)
+    g_cum = ops.chunk_local_cumsum(d["g"], 64, cu)
+    A = ops.kkt_solve(d["k"], d["beta"], g_cum, cu)
+    return tables, g_cum, A
+
+
+@pytest.mark.parametrize("cu", [None, [0, 130, 130, 777, 1000]], ids=["fixed", "varlen"])
+def test_operand_tiles_equal_row_major_outputs(cu):
+    """h, v_new, dh, du written as operand tiles (TMA stores) hold exactly the values of the
+    row-major outputs, transposed per chunk."""
+    from flashqla_b200 import ops
+
+    T = 1000 if cu is not None else 1024
+    d = _inputs(T, 2, 4, seed=31, cu=cu)
+    tables, g_cum, A = _prep(d)
+    scale = 128 ** -0.5
+    kw = dict(output_o=False, output_h=True, output_vnew=True, tables=tables)
+    row = ops.fwd_seq(None, d["k"], d["v"], A, g_cum, d["beta"], scale, d["h0"], **kw)
+    til = ops.fwd_seq(None, d["k"], d["v"], A, g_cum, d["beta"], scale, d["h0"], operand_tiles=True, **kw)
+    assert torch.equal(til["h"].transpose(-1, -2), row["h"])
+    brow = ops.bwd_dh(d["q"], d["k"], A, g_cum, d["beta"], d["do"], scale, d["dht"], tables=tables)
+    btil = ops.bwd_dh(d["q"], d["k"], A, g_cum, d["beta"], d["do"], scale, d["dht"], tables=tables,
+                      operand_tiles=True)
+    assert torch.equal(btil["dh"].transpose(-1, -2), brow["dh"])
+    assert torch.equal(btil["dh0"], brow["dh0"])
+    # per chunk: tile[c, h, v, t] == row-major[token bos + 64 c' + t, h, v]; columns past the
+    # sequence end are zero
+    bounds = cu if cu is not None else [0, T]
+    c = 0
+    for bos, eos in zip(bounds[:-1], bounds[1:]):
+        for t0 in range(bos, eos, 64):
+            n = min(64, eos - t0)
+            for name, tl, rw in (("vnew", til["vnew"], row["vnew"]), ("du", btil["du"], brow["du"])):
+                got = tl[c].transpose(-1, -2)  # [Hv, 64, V]
+                want = rw[0, t0:t0 + n].transpose(0, 1)
+                assert torch.equal(got[:, :n], want), (name, c)
+                assert not got[:, n:].any(), (name, c)
+            c += 1
+    assert c == tables.num_chunks
+    # the chunk-parallel kernel gives the same gradients from either layout
+    a = ops.bwd_main(d["q"], d["k"], d["v"], row["vnew"], A, g_cum, d["beta"], d["do"], brow["du"],
+                     row["h"], brow["dh"], scale, tables=tables)
+    b = ops.bwd_main(d["q"], d["k"], d["v"], til["vnew"], A, g_cum, d["beta"], d["do"], btil["du"],
+                     til["h"], btil["dh"], scale, tables=tables, operand_tiles=True)
+    total = tables.total
+    for x, y, name in zip(a, b, ("dq", "dk", "dv", "db", "dg")):
+        assert orc.rel_err(y[:, :total].float(), x[:, :total].float()) < 1e-5, name
+
+
+_CHILD = r"""
+import sys, torch
+sys.path.insert(0, {root!r})
+from oracle import gdr_oracle as orc
+import flashqla_b200 as fq
+cu = torch.tensor([0, 130, 130, 777, 1000], dtype=torch.int32)
+x = orc.make_inputs(1, 1000, 2, 4, 128, 128, seed=77, cu_seqlens=cu, with_h0=True)
+d = {{n: t.cuda() for n, t in x.items()}}
+for n in ("q", "k", "v", "beta", "do"):
+    d[n] = d[n].bfloat16()
+cu = cu.cuda()
+g_cum, A, o, h, ht, _ = fq.chunk_gated_delta_rule_fwd(d["q"], d["k"], d["v"], d["g"], d["beta"], None,
+                                                      d["h0"], cu, output_h=True)
+grads = fq.chunk_gated_delta_rule_bwd(d["q"], d["k"], d["v"], g_cum, d["beta"], A, d["do"], d["dht"],
+                                      None, d["h0"], cu)
+torch.save([t.cpu() for t in (o, h, ht, *grads)], sys.argv[1])
+"""
+
+
+def test_tcgen05_kernels_match_mma_sync_kernels(tmp_path):
+    """The whole forward + backward with the tcgen05 kernels against the same run with every
+    K = V = 128 kernel forced to its mma.sync implementation (separate process: the switch is
+    read once per process)."""
+    outs = []
+    for force in (False, True):
+        env = dict(os.environ)
+        env.pop("FQLA_FORCE_MMA_SYNC", None)
+        if force:
+            env["FQLA_FORCE_MMA_SYNC"] = "1"
+        path = str(tmp_path / f"out_{int(force)}.pt")
+        subprocess.run([sys.executable, "-c", _CHILD.format(root=ROOT), path], check=True, env=env,
+                       timeout=600)
+        outs.append(torch.load(path))
+    names = ("o", "h", "ht", "dq", "dk", "dv", "db", "dg", "dh0")
+    for name, a, b in zip(names, *outs):
+        tol = 5e-3 if name in ("o", "h", "ht") else 1e-2
+        assert orc.rel_err(a.float(), b.float()) < tol, name
+
+
+def test_warmup_scan_against_host_loop():
+    from flashqla_b200 import ops
+
+    torch.manual_seed(5)
+    T, Hv = 64 * 37 + 11, 6
+    # per-token log gates chosen so that some (segment, head) pairs cross the threshold early,
+    # some late, some never
+    g = -torch.rand(1, T, Hv) * torch.tensor([0.5, 0.05, 0.005, 0.0005, 0.2, 0.0])
+    seg = [0, 64 * 5, 64 * 5, 64 * 20, 64 * 36, T]
+    seg_cu = torch.tensor(seg, dtype=torch.int32)
+    g_cum = orc.chunk_local_cumsum(g, seg_cu)
+    keep = torch.tensor([1, 1, 0, 1, 1], dtype=torch.int32)
+    for from_start in (False, True):
+        warm, fb = ops.warmup_scan(g_cum.to(DEV), seg_cu.to(DEV), -10.0, from_start, keep.to(DEV))
+        warm, fb = warm.cpu(), fb.cpu()
+        for s, (b, e) in enumerate(zip(seg[:-1], seg[1:])):
+            n_chunks = (e - b + 63) // 64
+            ends = [min(e, b + 64 * (c + 1)) - 1 for c in range(n_chunks)]
+            order = ends if from_start else ends[::-1]
+            for h in range(Hv):
+                if keep[s] == 0:
+                    assert warm[s, h] == 0 and fb[s, h] == 0
+                    continue
+                acc, n, reached = 0.0, 0, False
+                for r in order:
+                    acc += float(g_cum[0, r, h])
+                    n += 1
+                    if acc < -10.0:
+                        reached = True
+                        break
+                # summation order differs (warp prefix sum): allow the crossing chunk to move by
+                # one only when the running sum is within rounding of the threshold
+                assert abs(int(warm[s, h]) - n) <= (1 if abs(acc + 10.0) < 1e-3 else 0), (s, h)
+                if int(warm[s, h]) == n:
+                    assert int(fb[s, h]) == (0 if reached else 1)
+
+
+def test_merge_states_against_host_chain():
+    from flashqla_b200 import ops
+
+    torch.manual_seed(6)
+    n_seg, Hv, D = 7, 3, 128
+    seg_begin = torch.tensor([0, 3, 3, 7], dtype=torch.int32)  # raw sequences of 3, 0 and 4 segments
+    local = torch.randn(n_seg, Hv, D, D)
+    M = torch.randn(n_seg, Hv, D, D) * 0.05
+    use = (torch.rand(n_seg, Hv) > 0.4).int()
+    raw = torch.randn(3, Hv, D, D)
+    for reverse in (False, True):
+        out = ops.merge_states(local.to(DEV), M.to(DEV), use.to(DEV), raw.to(DEV), seg_begin.to(DEV),
+                               reverse=reverse).cpu()
+        for r in range(3):
+            s0, s1 = int(seg_begin[r]), int(seg_begin[r + 1])
+            idx = list(range(s0, s1))[::-1] if reverse else list(range(s0, s1))
+            cur = raw[r].clone()
+            for j, i in enumerate(idx):
+                assert orc.rel_err(out[i], cur) < 1e-5, (reverse, r, i)
+                m = M[i].transpose(-1, -2) if reverse else M[i]
+                cur = local[i] + use[i].view(Hv, 1, 1) * (m @ cur)

@@ -91,6 +91,7 @@ ORACLE_SHAPES = [
     ("fixed_b2", 2, 256, 2, 4, 128, None, "logsigmoid", True, False),
     ("padding", 1, 1000, 2, 4, 128, [0, 211, 985], "logsigmoid", True, True),
     ("short_seqs", 1, 300, 1, 1, 128, [0, 1, 64, 129, 192, 193, 300], "logsigmoid", True, False),
+    ("empty_seq", 1, 400, 2, 2, 128, [0, 100, 100, 400], "logsigmoid", True, False),
     ("no_h0", 1, 200, 2, 2, 128, None, "logsigmoid", False, False),
     ("d64", 1, 512, 4, 4, 64, None, "logsigmoid", True, True),  # BASELINE config 0
     ("hard_gate", 1, 320, 2, 4, 128, [0, 130, 320], "hard", True, True),

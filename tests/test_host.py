@@ -152,3 +152,22 @@ def test_drop_in_package_paths():
     import flashqla_b200
 
     assert flash_qla.chunk_gated_delta_rule is flashqla_b200.chunk_gated_delta_rule is a
+
+
+def test_kernel_chunk_table_uses_positions_of_sequences():
+    """The public chunk table keeps the reference's numbering (a zero-length sequence takes no
+    id); the table handed to the kernels carries the position in cu_seqlens instead, and is
+    the public one when no sequence is empty."""
+    import torch
+
+    from flashqla_b200 import ops
+    from flashqla_b200.utils import prepare_chunk_indices
+
+    cu = torch.tensor([0, 100, 100, 400], dtype=torch.int32)
+    assert prepare_chunk_indices(cu, 64)[:, 0].tolist() == [0, 0, 1, 1, 1, 1, 1]
+    t = ops._kernel_chunk_indices(cu)
+    assert t[:, 0].tolist() == [0, 0, 2, 2, 2, 2, 2]
+    assert t[:, 1].tolist() == [0, 1, 0, 1, 2, 3, 4]
+    assert t.dtype == cu.dtype and t.is_contiguous()
+    full = torch.tensor([0, 64, 130], dtype=torch.int64)
+    assert ops._kernel_chunk_indices(full) is prepare_chunk_indices(full, 64)
