@@ -63,9 +63,10 @@ constexpr int OFF_DS = OFF_A + 8192;        // ds, later diag(beta) dA3
 constexpr int OFF_DA = OFF_DS + 8192;       // dA, then T = A^T dA, then dA3
 constexpr int OFF_DW = OFF_DA + 8192;       // -du h^T
 // g, gamma, rho, beta (64 floats each); per-warp partial sums of dg (rows: 4 column quarters x 64,
-// columns: 4 lane quarters x 64), of db (4 x 64) and of the chunk total (16)
+// columns: 4 lane quarters x 64), of db (rows 4 x 64, two column terms 4 x 64 each) and of the
+// chunk total (16)
 constexpr int OFF_VEC = OFF_DW + ROW_TILE;
-constexpr int OFF_BAR = OFF_VEC + (4 * 64 + 3 * 256 + 16) * 4;
+constexpr int OFF_BAR = OFF_VEC + (4 * 64 + 5 * 256 + 512 + 16) * 4;
 constexpr int N_BARS = 20;
 constexpr int OFF_MISC = OFF_BAR + N_BARS * 8;
 constexpr int SMEM_BYTES = OFF_MISC + 16 + 1024;
@@ -75,12 +76,12 @@ constexpr uint32_t TX_B = 3 * ROW_TILE;                // du, q, v
 constexpr uint32_t TX_C = 8192;                        // A
 // tensor memory: (column, lane half) of every accumulator
 constexpr uint32_t HI = 16u << 16;
-constexpr uint32_t T_DQ1 = 0, T_DK1 = 128, T_DW = 256, T_T1 = 384;
-constexpr uint32_t T_DQ2 = 0 + HI, T_DK2 = 128 + HI, T_T2 = 256 + HI, T_DS = 384 + HI, T_QK = 448 + HI;
+constexpr uint32_t T_DQ1 = 0, T_DK1 = 0 + HI, T_DW = 256;   // dq1 | dk1 share columns (lane halves)
+constexpr uint32_t T_DQ2 = 128, T_DK2 = 128 + HI;        // ds K | the four-product dk sum share columns
+constexpr uint32_t T_T2 = 256 + HI, T_DS = 384 + HI, T_QK = 448 + HI;
 constexpr uint32_t T_X1 = 256, T_X2 = 320;            // after dw has been read
 constexpr uint32_t T_T = 384 + HI, T_KK = 448 + HI;    // after ds, qk have been read
 constexpr uint32_t T_D3 = 256;                         // after x1 has been read
-constexpr uint32_t T_T3 = 0, T_DK5 = 0 + HI;           // after dq1, dq2 have been read
 enum {
   L_A = 0, L_B, L_C,                                       // TMA groups landed
   C_DW, C_DSQK, C_1B, C_X, C_2B, C_T, C_D3, C_5,           // product groups complete (commit)
@@ -140,7 +141,10 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
   float* sRowDg = sBeta + 64;
   float* sColDg = sRowDg + 256;
   float* sRowDb = sColDg + 256;
-  float* sLast = sRowDb + 256;
+  float* sColC1 = sRowDb + 256;
+  float* sColC2 = sColC1 + 256;
+  float* sRowW = sColC2 + 256;  // row terms of the 128-wide steps: [column quarter x lane half][row]
+  float* sLast = sRowW + 512;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const long long total = p.n_chunks * p.Hv;
@@ -236,6 +240,7 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
       const uint32_t dumn_lo = desc_lo_mnmajor(smem + OFF_DU, 8192), dwmn_lo = desc_lo_mnmajor(smem + OFF_DW, 8192);
       const uint32_t amn_lo = desc_lo_mnmajor(smem + OFF_A, 8192), dsmn_lo = desc_lo_mnmajor(smem + OFF_DS, 8192);
       const uint32_t damn_lo = desc_lo_mnmajor(smem + OFF_DA, 8192);
+      const uint32_t a1mn_lo = desc_lo_mnmajor(smem + OFF_V, 8192), a2mn_lo = desc_lo_mnmajor(smem + OFF_V + 8192, 8192);
       // operand-tile layouts: [V rows][K or token columns], read MN-major, contraction over rows
       const uint32_t hT_lo = desc_lo_mnmajor(smem + OFF_H, 16384), dhT_lo = desc_lo_mnmajor(smem + OFF_DH, 16384);
       const uint32_t vnT_lo = desc_lo_mnmajor(smem + OFF_VN, 16384), duT_lo = desc_lo_mnmajor(smem + OFF_DU, 16384);
@@ -295,9 +300,6 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
           umma_group<8, 2, 512, 2, 1024, false>(tmem + T_DK1, vn_lo, dh_lo, ID_KK_128);
         }
         umma_commit(&bars[C_1B]);
-        umma_group<4, 128, 0, 128, 0, false>(tmem + T_T1, amn_lo, dwmn_lo, ID_MM_128);
-        if constexpr (TILED) umma_group<4, 128, 0, 2, 0, false>(tmem + T_T2, amn_lo, du_lo, ID_MK_128);
-        else umma_group<4, 128, 0, 128, 0, false>(tmem + T_T2, amn_lo, dumn_lo, ID_MM_128);
         // ---- ds is an operand now ----
         ok = WAIT(R_DS, ph);
         if (!ok) break;
@@ -305,7 +307,6 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
         umma_group<4, 2, 0, 128, 0, false>(tmem + T_DQ2, ds_lo, kmn_lo, ID_KM_128);
         umma_group<4, 128, 0, 128, 0, false>(tmem + T_DK2, dsmn_lo, qmn_lo, ID_MM_128);
         umma_group<8, 2, 512, 2, 512, false>(tmem + T_KK, k_lo, k_lo, ID_KK_64);  // qk has been read
-        umma_commit(&bars[C_2B]);
         // h, dh, dO, v_new are dead once the first products are complete and the h.dh sum is done
         if (has_next) {
           ok = WAIT(C_1B, ph) && WAIT(R_HD, ph);
@@ -318,6 +319,12 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
         tc_fence_after();
         umma_group<4, 128, 0, 128, 0, false>(tmem + T_T, amn_lo, damn_lo, ID_MM_64);
         umma_commit(&bars[C_T]);
+        // with A' = A diag(beta) and A'' = A diag(beta gamma) (written over the dead v tile):
+        // dk += A''^T dw (onto ds^T q), dv = A'^T du -- the row scalings ride on the operands
+        umma_group<4, 128, 0, 128, 0, true>(tmem + T_DK2, a2mn_lo, dwmn_lo, ID_MM_128);
+        if constexpr (TILED) umma_group<4, 128, 0, 2, 0, false>(tmem + T_T2, a1mn_lo, du_lo, ID_MK_128);
+        else umma_group<4, 128, 0, 128, 0, false>(tmem + T_T2, a1mn_lo, dumn_lo, ID_MM_128);
+        umma_commit(&bars[C_2B]);
         // ---- T -> d3 = T A^T ----
         ok = WAIT(R_T, ph);
         if (!ok) break;
@@ -333,12 +340,13 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
           if (!ok) break;
           load_c(nxt);
         }
-        // ---- dA3 -> dA3 K and (beta dA3)^T K ----
+        // ---- beta dA3 is an operand now ----
         ok = WAIT(R_D3, ph);
         if (!ok) break;
         tc_fence_after();
-        umma_group<4, 2, 0, 128, 0, false>(tmem + T_T3, da_lo, kmn_lo, ID_KM_128);
-        umma_group<4, 128, 0, 128, 0, false>(tmem + T_DK5, dsmn_lo, kmn_lo, ID_MM_128);
+        // dk += (beta dA3) K + (beta dA3)^T K, onto the same accumulator
+        umma_group<4, 2, 0, 128, 0, true>(tmem + T_DK2, ds_lo, kmn_lo, ID_KM_128);
+        umma_group<4, 128, 0, 128, 0, true>(tmem + T_DK2, dsmn_lo, kmn_lo, ID_MM_128);
         umma_commit(&bars[C_5]);
         cur = nxt;
       }
@@ -346,14 +354,21 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
     }
   } else {
     // ====================== read-out warps ======================
+    // 64-wide accumulators (ds, qk, x1, x2, T, d3, kk) are read in the 16-lane shape: lane l of
+    // warp (qd, cq) owns rows 16 qd + l/4 (+8) and column pairs 16 cq + 8 i + 2 (l%4).
+    // 128-wide accumulators are read in the 32-lane shape, which returns the accumulator at lanes
+    // +0 and the one at lanes +16 of the same columns at once: lane l owns row 16 qd + l%16 of
+    // the lower (l < 16) or upper (l >= 16) accumulator, 32 consecutive columns 32 cq ..; shared
+    // memory and global memory are then touched 16 bytes at a time.
     const int qd = warp & 3, cq = warp >> 2;
     const int row_a = 16 * qd + (lane >> 2), row_b = row_a + 8, cp = 2 * (lane & 3);
+    const int row_w = 16 * qd + (lane & 15);
+    const bool hi = lane >= 16;
     const uint32_t lanes = (uint32_t)(qd * 32) << 16;
-    const int c128 = 32 * cq, c64 = 16 * cq;  // first column of this warp in 128- / 64-wide tiles
-    // bf16 pair of a [64 x 128] row tile at (row, col), col even
-    auto tile2 = [&](int off, int row, int col) {
-      return ld_bf16x2(reinterpret_cast<const bf16*>(smem + off + (col >> 6) * 8192 + sw128_offset(row, col & 63)));
-    };
+    const int c128 = 32 * cq, c64 = 16 * cq;
+    // byte offset of this thread's 16-byte piece j (8 columns) inside a [64 x 128] row tile
+    const int piece_base = (cq >> 1) * 8192 + row_w * 128;
+    auto piece = [&](int j) { return piece_base + (((4 * (cq & 1) + j) ^ (row_w & 7)) << 4); };
     auto quad_sum = [&](float x) {
       x += __shfl_xor_sync(0xffffffffu, x, 1);
       x += __shfl_xor_sync(0xffffffffu, x, 2);
@@ -365,8 +380,11 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
       x += __shfl_xor_sync(0xffffffffu, x, 16);
       return x;
     };
-    auto st_tile64 = [&](int off, int row, int col, float lo, float hi) {
-      *reinterpret_cast<uint32_t*>(smem + off + sw128_offset(row, col)) = pack_bf16(lo, hi);
+    auto st_tile64 = [&](int off, int row, int col, float lo, float hi2) {
+      *reinterpret_cast<uint32_t*>(smem + off + sw128_offset(row, col)) = pack_bf16(lo, hi2);
+    };
+    auto pack8 = [&](const float* x) {
+      return make_uint4(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]), pack_bf16(x[4], x[5]), pack_bf16(x[6], x[7]));
     };
     // this warp's part of a tile (or of the accumulators) is done: tell the issue warp
     auto signal = [&](int bar) {
@@ -432,31 +450,35 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
       if (has_next) fetch_vectors(nxt);
       stamp();
       const float g_a = sG[row_a], g_b = sG[row_b];
-      const float gam_a = sGam[row_a], gam_b = sGam[row_b];
-      const float rho_a = sRho[row_a], rho_b = sRho[row_b];
       const float beta_a = sBeta[row_a], beta_b = sBeta[row_b];
-      const long long out_a = ((cur.row0 + row_a) * p.Hv + cur.hv) * D, out_b = ((cur.row0 + row_b) * p.Hv + cur.hv) * D;
-      const bool wr_a = row_a < valid, wr_b = row_b < valid;
-      float dq1[16], dkacc[16];
-      // this thread's share of the row sums (dg, db), column sums (dg) and of the chunk total;
-      // reduced across lanes once, at the end of the item
-      float acc_dg_a = 0.f, acc_dg_b = 0.f, acc_db_a = 0.f, acc_db_b = 0.f, acc_last = 0.f;
+      // factor and tile of the 128-wide step that reads dq1 (lower lanes) and dk1 (upper lanes)
+      const float f_w = hi ? sRho[row_w] : p.scale * sGam[row_w];
+      const bf16* out_w_base = nullptr;
+      const long long out_w = ((cur.row0 + row_w) * p.Hv + cur.hv) * D + c128;
+      const bool wr_w = row_w < valid;
+      float keep[32];  // scaled dq1 (lower lanes) / dk1 (upper lanes) until the last step
+      (void)out_w_base;
+      // this thread's share of the row sums (dg, db), column sums (dg, and the two column terms of
+      // db / dg that come from A^T dw and A^T du) and of the chunk total; reduced across lanes
+      // once, at the end of the item
+      float acc_dg_a = 0.f, acc_dg_b = 0.f, acc_db_a = 0.f, acc_db_b = 0.f, acc_last = 0.f, acc_w = 0.f;
       float acc_col[4] = {0.f, 0.f, 0.f, 0.f};
+      float acc_c1[4] = {0.f, 0.f, 0.f, 0.f}, acc_c2[4] = {0.f, 0.f, 0.f, 0.f};
 
       // ---- E1: dw = -du h^T as an operand tile ----
+      stamp();
       ok = ok && WAIT(C_DW, ph);
       stamp();
       if (ok) {
         tc_fence_after();
-        float dw[16];
-        tmem_ld_16x32(tmem + lanes + T_DW + c128, dw);
+        float x[32];
+        tmem_ld32(tmem + lanes + T_DW + c128, x);
         tmem_ld_wait();
+        if (!hi) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int col = c128 + 8 * i + cp;
-          unsigned char* base = smem + OFF_DW + (col >> 6) * 8192;
-          *reinterpret_cast<uint32_t*>(base + sw128_offset(row_a, col & 63)) = pack_bf16(-dw[4 * i], -dw[4 * i + 1]);
-          *reinterpret_cast<uint32_t*>(base + sw128_offset(row_b, col & 63)) = pack_bf16(-dw[4 * i + 2], -dw[4 * i + 3]);
+          for (int j = 0; j < 32; ++j) x[j] = -x[j];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(smem + OFF_DW + piece(j)) = pack8(x + 8 * j);
         }
       }
       signal(R_DW);
@@ -482,6 +504,7 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
       if (lane == 0) mbar_arrive(&bars[R_HD]);
 
       // ---- E2: ds = scale * G * (dO Vn^T); ds2 = ds * (Q K^T) ----
+      stamp();
       ok = ok && WAIT(C_DSQK, ph);
       stamp();
       if (ok) {
@@ -490,7 +513,6 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
         tmem_ld_16x16(tmem + lanes + T_DS + c64, ds);
         tmem_ld_16x16(tmem + lanes + T_QK + c64, qk);
         tmem_ld_wait();
-        float rs_a = 0.f, rs_b = 0.f;
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
           const int col = c64 + 8 * i + cp;
@@ -502,17 +524,16 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
           st_tile64(OFF_DS, row_a, col, a0, a1);
           st_tile64(OFF_DS, row_b, col, b0, b1);
           const float s0 = a0 * qk[4 * i], s1 = a1 * qk[4 * i + 1], s2 = b0 * qk[4 * i + 2], s3 = b1 * qk[4 * i + 3];
-          rs_a += s0 + s1;
-          rs_b += s2 + s3;
+          acc_dg_a += s0 + s1;
+          acc_dg_b += s2 + s3;
           acc_col[2 * i] += s0 + s2;
           acc_col[2 * i + 1] += s1 + s3;
         }
-        acc_dg_a += rs_a;
-        acc_dg_b += rs_b;
       }
       signal(R_DS);
 
-      // ---- E3: dA = strict_lower(beta_c (gamma_c x1 + x2)) ----
+      // ---- E3: dA = strict_lower(beta_c (gamma_c x1 + x2)); A' = A diag(beta), A'' = A diag(beta gamma) ----
+      stamp();
       ok = ok && WAIT(C_X, ph);
       stamp();
       if (ok) {
@@ -529,43 +550,51 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
                     col + 1 < row_a ? b1 * (g1 * x1[4 * i + 1] + x2[4 * i + 1]) : 0.f);
           st_tile64(OFF_DA, row_b, col, col < row_b ? b0 * (g0 * x1[4 * i + 2] + x2[4 * i + 2]) : 0.f,
                     col + 1 < row_b ? b1 * (g1 * x1[4 * i + 3] + x2[4 * i + 3]) : 0.f);
+          // rowsum((A^T dw) k)[r] = sum_s A[s][r] x1[s][r], rowsum((A^T du) v)[r] = sum_s A[s][r] x2[s][r]
+          const float2 A_a = ld_bf16x2(reinterpret_cast<const bf16*>(smem + OFF_A + sw128_offset(row_a, col)));
+          const float2 A_b = ld_bf16x2(reinterpret_cast<const bf16*>(smem + OFF_A + sw128_offset(row_b, col)));
+          acc_c1[2 * i] += A_a.x * x1[4 * i] + A_b.x * x1[4 * i + 2];
+          acc_c1[2 * i + 1] += A_a.y * x1[4 * i + 1] + A_b.y * x1[4 * i + 3];
+          acc_c2[2 * i] += A_a.x * x2[4 * i] + A_b.x * x2[4 * i + 2];
+          acc_c2[2 * i + 1] += A_a.y * x2[4 * i + 1] + A_b.y * x2[4 * i + 3];
+          // the v tile is dead (its product is part of this group): A' and A'' go there
+          st_tile64(OFF_V, row_a, col, A_a.x * b0, A_a.y * b1);
+          st_tile64(OFF_V, row_b, col, A_b.x * b0, A_b.y * b1);
+          st_tile64(OFF_V + 8192, row_a, col, A_a.x * b0 * g0, A_a.y * b1 * g1);
+          st_tile64(OFF_V + 8192, row_b, col, A_b.x * b0 * g0, A_b.y * b1 * g1);
         }
       }
       signal(R_DA);
 
-      // ---- E4: dq1 = scale * gamma * (dO h^T), dk1 = rho * (Vn dh^T) and their dg terms ----
+      // ---- E4: dq1 = scale gamma (dO h^T) on the lower lanes, dk1 = rho (Vn dh^T) on the upper ----
+      stamp();
       ok = ok && WAIT(C_1B, ph);
       stamp();
       if (ok) {
         tc_fence_after();
-        tmem_ld_16x32(tmem + lanes + T_DQ1 + c128, dq1);
-        tmem_ld_16x32(tmem + lanes + T_DK1 + c128, dkacc);
+        tmem_ld32(tmem + lanes + T_DQ1 + c128, keep);
         tmem_ld_wait();
-        float qa = 0.f, qb = 0.f, ka = 0.f, kb = 0.f;
+        const unsigned char* tile = smem + (hi ? koff : OFF_Q);
+        float s = 0.f;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int col = c128 + 8 * i + cp;
-          dq1[4 * i] *= p.scale * gam_a;
-          dq1[4 * i + 1] *= p.scale * gam_a;
-          dq1[4 * i + 2] *= p.scale * gam_b;
-          dq1[4 * i + 3] *= p.scale * gam_b;
-          dkacc[4 * i] *= rho_a;
-          dkacc[4 * i + 1] *= rho_a;
-          dkacc[4 * i + 2] *= rho_b;
-          dkacc[4 * i + 3] *= rho_b;
-          const float2 q_a = tile2(OFF_Q, row_a, col), q_b = tile2(OFF_Q, row_b, col);
-          const float2 k_a = tile2(koff, row_a, col), k_b = tile2(koff, row_b, col);
-          qa += q_a.x * dq1[4 * i] + q_a.y * dq1[4 * i + 1];
-          qb += q_b.x * dq1[4 * i + 2] + q_b.y * dq1[4 * i + 3];
-          ka += k_a.x * dkacc[4 * i] + k_a.y * dkacc[4 * i + 1];
-          kb += k_b.x * dkacc[4 * i + 2] + k_b.y * dkacc[4 * i + 3];
+        for (int j = 0; j < 4; ++j) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(tile + piece(j));
+          const uint32_t* pr = &raw.x;
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 t = __bfloat1622float2(*reinterpret_cast<const bf162*>(&pr[e]));
+            keep[8 * j + 2 * e] *= f_w;
+            keep[8 * j + 2 * e + 1] *= f_w;
+            s += t.x * keep[8 * j + 2 * e] + t.y * keep[8 * j + 2 * e + 1];
+          }
         }
-        acc_dg_a += qa - ka;
-        acc_dg_b += qb - kb;
-        acc_last += ka + kb;
+        // dg += rowsum(q dq1) - rowsum(k dk1); the chunk total gets + sum(k dk1)
+        acc_w += hi ? -s : s;
+        if (hi) acc_last += s;
       }
 
       // ---- E5: T = A^T dA as an operand tile (over dA, which the product has consumed) ----
+      stamp();
       ok = ok && WAIT(C_T, ph);
       stamp();
       if (ok) {
@@ -582,65 +611,24 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
       }
       signal(R_T);
 
-      // ---- E6: dq out; dk += ds^T Q + beta gamma (A^T dw); dv = beta (A^T du); db terms ----
+      // ---- E6: dv = A'^T du (upper lanes), already row-scaled by beta ----
+      stamp();
       ok = ok && WAIT(C_2B, ph);
       stamp();
       if (ok) {
         tc_fence_after();
-        {
-          float x[16];
-          tmem_ld_16x32(tmem + lanes + T_DQ2 + c128, x);
-          tmem_ld_wait();
+        float x[32];
+        tmem_ld32(tmem + lanes + (T_T2 & 0xFFFFu) + c128, x);
+        tmem_ld_wait();
+        if (hi && wr_w) {
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int col = c128 + 8 * i + cp;
-            if (wr_a) *reinterpret_cast<uint32_t*>(p.dq + out_a + col) = pack_bf16(dq1[4 * i] + x[4 * i], dq1[4 * i + 1] + x[4 * i + 1]);
-            if (wr_b) *reinterpret_cast<uint32_t*>(p.dq + out_b + col) = pack_bf16(dq1[4 * i + 2] + x[4 * i + 2], dq1[4 * i + 3] + x[4 * i + 3]);
-          }
-        }
-        {
-          float x[16], t1[16];
-          tmem_ld_16x32(tmem + lanes + T_DK2 + c128, x);
-          tmem_ld_16x32(tmem + lanes + T_T1 + c128, t1);
-          tmem_ld_wait();
-          float sa = 0.f, sb = 0.f;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int col = c128 + 8 * i + cp;
-            const float2 k_a = tile2(koff, row_a, col), k_b = tile2(koff, row_b, col);
-            sa += k_a.x * t1[4 * i] + k_a.y * t1[4 * i + 1];
-            sb += k_b.x * t1[4 * i + 2] + k_b.y * t1[4 * i + 3];
-            dkacc[4 * i] += x[4 * i] + beta_a * gam_a * t1[4 * i];
-            dkacc[4 * i + 1] += x[4 * i + 1] + beta_a * gam_a * t1[4 * i + 1];
-            dkacc[4 * i + 2] += x[4 * i + 2] + beta_b * gam_b * t1[4 * i + 2];
-            dkacc[4 * i + 3] += x[4 * i + 3] + beta_b * gam_b * t1[4 * i + 3];
-          }
-          acc_db_a += gam_a * sa;
-          acc_db_b += gam_b * sb;
-          acc_dg_a += beta_a * gam_a * sa;
-          acc_dg_b += beta_b * gam_b * sb;
-        }
-        {
-          float t2[16];
-          tmem_ld_16x32(tmem + lanes + T_T2 + c128, t2);
-          tmem_ld_wait();
-          float sa = 0.f, sb = 0.f;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int col = c128 + 8 * i + cp;
-            const float2 v_a = tile2(OFF_V, row_a, col), v_b = tile2(OFF_V, row_b, col);
-            sa += v_a.x * t2[4 * i] + v_a.y * t2[4 * i + 1];
-            sb += v_b.x * t2[4 * i + 2] + v_b.y * t2[4 * i + 3];
-            if (wr_a) *reinterpret_cast<uint32_t*>(p.dv + out_a + col) = pack_bf16(beta_a * t2[4 * i], beta_a * t2[4 * i + 1]);
-            if (wr_b) *reinterpret_cast<uint32_t*>(p.dv + out_b + col) = pack_bf16(beta_b * t2[4 * i + 2], beta_b * t2[4 * i + 3]);
-          }
-          acc_db_a += sa;
-          acc_db_b += sb;
+          for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(p.dv + out_w + 8 * j) = pack8(x + 8 * j);
         }
       }
       signal(R_E6);
 
-      // ---- E7: dA3 = -G * d3 (over T) and diag(beta) dA3 (over ds), both consumed by now ----
+      // ---- E7: beta dA3 = -beta G d3 (over ds) as an operand tile; its dg and db terms ----
+      stamp();
       ok = ok && WAIT(C_D3, ph);
       stamp();
       if (ok) {
@@ -649,7 +637,6 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
         tmem_ld_16x16(tmem + lanes + T_D3 + c64, d3);
         tmem_ld_16x16(tmem + lanes + T_KK + c64, kk);
         tmem_ld_wait();
-        float rs_a = 0.f, rs_b = 0.f;
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
           const int col = c64 + 8 * i + cp;
@@ -658,47 +645,37 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
           const float a1 = col + 1 < row_a ? -d3[4 * i + 1] * fast_exp(g_a - gc1) : 0.f;
           const float b0 = col < row_b ? -d3[4 * i + 2] * fast_exp(g_b - gc0) : 0.f;
           const float b1 = col + 1 < row_b ? -d3[4 * i + 3] * fast_exp(g_b - gc1) : 0.f;
-          st_tile64(OFF_DA, row_a, col, a0, a1);
-          st_tile64(OFF_DA, row_b, col, b0, b1);
           st_tile64(OFF_DS, row_a, col, beta_a * a0, beta_a * a1);
           st_tile64(OFF_DS, row_b, col, beta_b * b0, beta_b * b1);
-          const float s0 = a0 * beta_a * kk[4 * i], s1 = a1 * beta_a * kk[4 * i + 1];
-          const float s2 = b0 * beta_b * kk[4 * i + 2], s3 = b1 * beta_b * kk[4 * i + 3];
-          rs_a += s0 + s1;
-          rs_b += s2 + s3;
+          // db += rowsum((dA3 K) k) = rowsum(dA3 * (K K^T)); the dg terms carry the beta factor
+          const float u0 = a0 * kk[4 * i], u1 = a1 * kk[4 * i + 1], u2 = b0 * kk[4 * i + 2], u3 = b1 * kk[4 * i + 3];
+          acc_db_a += u0 + u1;
+          acc_db_b += u2 + u3;
+          const float s0 = u0 * beta_a, s1 = u1 * beta_a, s2 = u2 * beta_b, s3 = u3 * beta_b;
+          acc_dg_a += s0 + s1;
+          acc_dg_b += s2 + s3;
           acc_col[2 * i] += s0 + s2;
           acc_col[2 * i + 1] += s1 + s3;
         }
-        acc_dg_a += rs_a;
-        acc_dg_b += rs_b;
       }
       signal(R_D3);
 
-      // ---- E8: dk out; db += rowsum((dA3 K) k) ----
+      // ---- E8: dq = dq1 + ds K (lower lanes); dk = dk1 + [ds^T q + A''^T dw + (beta dA3) K + (beta dA3)^T K] (upper) ----
+      stamp();
       ok = ok && WAIT(C_5, ph);
       stamp();
       if (ok) {
         tc_fence_after();
-        float t3[16], x[16];
-        tmem_ld_16x32(tmem + lanes + T_T3 + c128, t3);
-        tmem_ld_16x32(tmem + lanes + T_DK5 + c128, x);
+        float x[32];
+        tmem_ld32(tmem + lanes + T_DQ2 + c128, x);
         tmem_ld_wait();
-        float sa = 0.f, sb = 0.f;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int col = c128 + 8 * i + cp;
-          const float2 k_a = tile2(koff, row_a, col), k_b = tile2(koff, row_b, col);
-          sa += k_a.x * t3[4 * i] + k_a.y * t3[4 * i + 1];
-          sb += k_b.x * t3[4 * i + 2] + k_b.y * t3[4 * i + 3];
-          if (wr_a)
-            *reinterpret_cast<uint32_t*>(p.dk + out_a + col) =
-                pack_bf16(dkacc[4 * i] + beta_a * t3[4 * i] + x[4 * i], dkacc[4 * i + 1] + beta_a * t3[4 * i + 1] + x[4 * i + 1]);
-          if (wr_b)
-            *reinterpret_cast<uint32_t*>(p.dk + out_b + col) =
-                pack_bf16(dkacc[4 * i + 2] + beta_b * t3[4 * i + 2] + x[4 * i + 2], dkacc[4 * i + 3] + beta_b * t3[4 * i + 3] + x[4 * i + 3]);
+        for (int j = 0; j < 32; ++j) x[j] += keep[j];
+        if (wr_w) {
+          bf16* out = hi ? p.dk : p.dq;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(out + out_w + 8 * j) = pack8(x + 8 * j);
         }
-        acc_db_a += sa;
-        acc_db_b += sb;
       }
       stamp();
       signal(R_END);  // accumulators and k of this item are free
@@ -713,10 +690,17 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
         sRowDb[cq * 64 + row_a] = acc_db_a;
         sRowDb[cq * 64 + row_b] = acc_db_b;
       }
+      sRowW[(2 * cq + (hi ? 1 : 0)) * 64 + row_w] = acc_w;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const float c = col_sum(acc_col[j]);
-        if (lane < 4) sColDg[qd * 64 + c64 + 8 * (j >> 1) + cp + (j & 1)] = c;
+        const float c1 = col_sum(acc_c1[j]), c2 = col_sum(acc_c2[j]);
+        if (lane < 4) {
+          const int col = c64 + 8 * (j >> 1) + cp + (j & 1);
+          sColDg[qd * 64 + col] = c;
+          sColC1[qd * 64 + col] = c1;
+          sColC2[qd * 64 + col] = c2;
+        }
       }
 #pragma unroll
       for (int d = 16; d > 0; d >>= 1) acc_last += __shfl_xor_sync(0xffffffffu, acc_last, d);
@@ -725,12 +709,16 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
       epi_barrier();  // every contribution to dg, db is in
       if (tid == 0 && *abort_flag) *stop_flag = 1;
       if (tid < valid) {
-        float dgv = 0.f, dbv = 0.f;
+        float dgv = 0.f, dbv = 0.f, c1 = 0.f, c2 = 0.f;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          dgv += sRowDg[j * 64 + tid] - sColDg[j * 64 + tid];
+          dgv += sRowDg[j * 64 + tid] - sColDg[j * 64 + tid] + sRowW[2 * j * 64 + tid] + sRowW[(2 * j + 1) * 64 + tid];
           dbv += sRowDb[j * 64 + tid];
+          c1 += sColC1[j * 64 + tid];
+          c2 += sColC2[j * 64 + tid];
         }
+        dbv += sGam[tid] * c1 + c2;
+        dgv += sBeta[tid] * sGam[tid] * c1;
         if (tid == valid - 1) {
 #pragma unroll
           for (int j = 0; j < N_EPI / 32; ++j) dgv += sLast[j];
