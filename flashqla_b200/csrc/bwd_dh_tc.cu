@@ -472,9 +472,11 @@ bwd_dh_tc_kernel(const BwdDhTcParams p, const __grid_constant__ CUtensorMap map_
     }
   } else {
     // =============================== scaling warps (2, 3) ===============================
-    // A'' = A diag(beta gamma) (columns) and q' = scale gamma .* q (rows), one thread per row;
-    // eight consecutive rows visit the 16-byte chunks of their rows in rotated order.
+    // A'' = A diag(beta gamma) (columns): thread t owns the 8 columns 8 (t%8) .. of the rows
+    // t/8 + 8 i, its scale factors stay in registers and the eight threads of a row touch one
+    // 128-byte line per access.  q' = scale gamma .* q (rows): one thread per row, rotated order.
     const int r = tid - 64;
+    const int c8 = r & 7, r0 = r >> 3, pc_a = c8 ^ r0;
     for (int it = 0; it < n_it && ok; ++it) {
       const int s = it & 1;
       ok = WAIT(FULL0 + s, (it >> 1) & 1);
@@ -482,15 +484,14 @@ bwd_dh_tc_kernel(const BwdDhTcParams p, const __grid_constant__ CUtensorMap map_
       if (!ok) break;
       const float* vs = vec + (it & 3) * VEC_SLOT_FLOATS;
       const unsigned char* stg = smem + OFF_STAGE + s * STAGE_BYTES;
-      const unsigned char* src = stg + 3 * TILE + r * 128;
-#pragma unroll 1
-      for (int q8 = 0; q8 < 8; ++q8) {
-        const int pc = (q8 + r) & 7;
-        const int col = (pc ^ (r & 7)) * 8;
-        const uint4 a = *reinterpret_cast<const uint4*>(src + pc * 16);
-        const float4 g0 = *reinterpret_cast<const float4*>(vs + V_BG * CHUNK + col);
-        const float4 g1 = *reinterpret_cast<const float4*>(vs + V_BG * CHUNK + col + 4);
-        *reinterpret_cast<uint4*>(smem + OFF_APP + r * 128 + pc * 16) =
+      const unsigned char* src = stg + 3 * TILE;
+      const float4 g0 = *reinterpret_cast<const float4*>(vs + V_BG * CHUNK + 8 * c8);
+      const float4 g1 = *reinterpret_cast<const float4*>(vs + V_BG * CHUNK + 8 * c8 + 4);
+#pragma unroll 4
+      for (int i = 0; i < 8; ++i) {
+        const int off = (r0 + 8 * i) * 128 + pc_a * 16;
+        const uint4 a = *reinterpret_cast<const uint4*>(src + off);
+        *reinterpret_cast<uint4*>(smem + OFF_APP + off) =
             make_uint4(scale2(a.x, g0.x, g0.y), scale2(a.y, g0.z, g0.w), scale2(a.z, g1.x, g1.y),
                        scale2(a.w, g1.z, g1.w));
       }

@@ -632,9 +632,11 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
     }
   } else {
     // =============================== prep (warps 2, 3) ===============================
-    // A' = A diag(beta), A'' = A diag(beta gamma), one thread per chunk row.  Eight consecutive
-    // rows visit the eight 16-byte chunks of their rows in rotated order: conflict-free.
-    const int r = tid - 64;
+    // A' = A diag(beta), A'' = A diag(beta gamma).  Thread t owns the 8 columns 8 (t%8) .. of the
+    // rows t/8 + 8 i: its 16 scale factors stay in registers, and the eight threads of a row touch
+    // the eight 16-byte pieces of that row (one 128-byte line per access, conflict-free).
+    const int t = tid - 64, c8 = t & 7, r0 = t >> 3;
+    const int pc = c8 ^ r0;  // physical piece: rows r0 + 8 i all have (row & 7) == r0
     for (int it = 0; it < n_it && ok; ++it) {
       const int s = it & 1;
       ok = WAIT(FULL0 + s, (it >> 1) & 1);
@@ -642,20 +644,19 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
       if (!ok) break;
       SEC_BEGIN();
       const float* vs = vec + (it & 3) * VEC_SLOT_FLOATS;
-      const unsigned char* src = smem + OFF_STAGE + s * STAGE_BYTES + 2 * TILE_QK + TILE_V + r * 128;
-#pragma unroll 1
-      for (int q8 = 0; q8 < 8; ++q8) {
-        const int pc = (q8 + r) & 7;            // physical chunk; holds columns 8*(pc ^ (r&7)) ..
-        const int col = (pc ^ (r & 7)) * 8;
-        const uint4 a = *reinterpret_cast<const uint4*>(src + pc * 16);
-        const float4 b0 = *reinterpret_cast<const float4*>(vs + V_BETA * CHUNK + col);
-        const float4 b1 = *reinterpret_cast<const float4*>(vs + V_BETA * CHUNK + col + 4);
-        const float4 g0 = *reinterpret_cast<const float4*>(vs + V_BG * CHUNK + col);
-        const float4 g1 = *reinterpret_cast<const float4*>(vs + V_BG * CHUNK + col + 4);
-        *reinterpret_cast<uint4*>(smem + OFF_AP + r * 128 + pc * 16) =
+      const float4 b0 = *reinterpret_cast<const float4*>(vs + V_BETA * CHUNK + 8 * c8);
+      const float4 b1 = *reinterpret_cast<const float4*>(vs + V_BETA * CHUNK + 8 * c8 + 4);
+      const float4 g0 = *reinterpret_cast<const float4*>(vs + V_BG * CHUNK + 8 * c8);
+      const float4 g1 = *reinterpret_cast<const float4*>(vs + V_BG * CHUNK + 8 * c8 + 4);
+      const unsigned char* src = smem + OFF_STAGE + s * STAGE_BYTES + 2 * TILE_QK + TILE_V;
+#pragma unroll 4
+      for (int i = 0; i < 8; ++i) {
+        const int off = (r0 + 8 * i) * 128 + pc * 16;
+        const uint4 a = *reinterpret_cast<const uint4*>(src + off);
+        *reinterpret_cast<uint4*>(smem + OFF_AP + off) =
             make_uint4(scale_bf16x2(a.x, b0.x, b0.y), scale_bf16x2(a.y, b0.z, b0.w),
                        scale_bf16x2(a.z, b1.x, b1.y), scale_bf16x2(a.w, b1.z, b1.w));
-        *reinterpret_cast<uint4*>(smem + OFF_APP + r * 128 + pc * 16) =
+        *reinterpret_cast<uint4*>(smem + OFF_APP + off) =
             make_uint4(scale_bf16x2(a.x, g0.x, g0.y), scale_bf16x2(a.y, g0.z, g0.w),
                        scale_bf16x2(a.z, g1.x, g1.y), scale_bf16x2(a.w, g1.z, g1.w));
       }

@@ -111,12 +111,14 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(
   constexpr int LDL = CHUNK + 4;  // floats; rows stay 16-byte aligned
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* sK = reinterpret_cast<bf16*>(smem_raw);
-  float* sL = reinterpret_cast<float*>(smem_raw + CHUNK * LDK * sizeof(bf16));
+  // the inverse X [64][LDL] is built over the K tile, dead once K K^T is in sL (5 CTAs per SM)
+  constexpr int REGION0 = CHUNK * LDK * 2 > CHUNK * LDL * 4 ? CHUNK * LDK * 2 : CHUNK * LDL * 4;
+  float* sX = reinterpret_cast<float*>(smem_raw);
+  float* sL = reinterpret_cast<float*>(smem_raw + REGION0);
   float* sG = sL + CHUNK * LDL;
   float* sB = sG + CHUNK;
-  float* sX = sB + CHUNK;         // [64][LDL] the inverse
-  constexpr int LDY = 40;         // partial products [32][LDY]; reuse the K tile, dead by then
-  float* sY = reinterpret_cast<float*>(smem_raw);
+  constexpr int LDY = 40;         // partial products [32][LDY]
+  float* sY = sB + CHUNK;
 
   int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   int hv = blockIdx.y, hq = hv / (Hv / Hq);
@@ -273,7 +275,8 @@ template <int D>
 static int launch_kkt(const void* k, const void* beta, int beta_is_f32, const float* g, void* A,
                       int Hq, int Hv, SeqLayout lay, IndexTable ci, long long n,
                       cudaStream_t st) {
-  constexpr int smem = CHUNK * (D + 8) * 2 + 2 * CHUNK * (CHUNK + 4) * 4 + 2 * CHUNK * 4;
+  constexpr int k_tile = CHUNK * (D + 8) * 2, x_tile = CHUNK * (CHUNK + 4) * 4;
+  constexpr int smem = (k_tile > x_tile ? k_tile : x_tile) + x_tile + 2 * CHUNK * 4 + 32 * 40 * 4;
   int rc = configure_smem((const void*)kkt_solve_kernel<D>, smem);
   if (rc != 0) return rc;
   kkt_solve_kernel<D><<<dim3((unsigned)n, Hv), 128, smem, st>>>(
