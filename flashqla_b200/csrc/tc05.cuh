@@ -60,11 +60,26 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity, ui
   return ok != 0;
 }
 
+// Non-blocking test of a phase (about 13 cycles on B200 when the phase is complete; the bounded
+// loop around the suspending form was measured at about 200 cycles even then).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(s32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Bounded wait: at most `budget` tries of up to 1 ms each.  Gives up as soon as *abort_flag
 // (shared memory) is set; on its own timeout it sets *abort_flag so that every other role of the
 // CTA leaves too.  Returns false when the wait was abandoned.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
                                           volatile int* abort_flag, uint32_t budget = 2000) {
+  if (mbar_test_wait(bar, parity)) return true;  // fast path: the phase is already complete
   for (uint32_t i = 0; i < budget; ++i) {
     if (mbar_try_wait(bar, parity, 1000000u)) return true;
     if (*abort_flag) return false;
