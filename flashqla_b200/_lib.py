@@ -16,7 +16,7 @@ P, I, LL, F = C.c_void_p, C.c_int, C.c_longlong, C.c_float
 # name -> argument types, in the order of include/fqla.h
 SIGNATURES = {
     "fqla_chunk_local_cumsum": [P, P, I, I, I, P, I, I, P, LL, I, P],
-    "fqla_kkt_solve": [P, P, I, P, P, I, I, I, I, I, P, I, P, LL, P],
+    "fqla_kkt_solve": [P, P, I, P, P, P, I, I, I, I, I, P, I, P, LL, P],
     "fqla_fwd_seq": [P, P, P, P, P, P, I, P, P, P, P, P, P, P, P, I, I, I, I, I, F, P, P, I, I, I, P],
     "fqla_bwd_dh": [P, P, P, P, P, I, P, P, P, P, P, P, I, I, I, I, I, F, P, P, I, I, I, P],
     "fqla_bwd_main": [P] * 7 + [I] + [P] * 9 + [I, I, I, I, I, F, P, P, P, I, LL, I, P],

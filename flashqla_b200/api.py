@@ -94,8 +94,7 @@ def chunk_gated_delta_rule_fwd(
     beta = _beta_in(beta).contiguous()
     B, T, Hq, D = k.shape
     tables = SeqTables(B, T, cu_seqlens)
-    g_cum = ops.chunk_local_cumsum(g, CHUNK_SIZE, cu_seqlens)
-    A = ops.kkt_solve(k, beta, g_cum, cu_seqlens)
+    g_cum, A = ops.kkt_solve(k, beta, g, cu_seqlens, raw_gate=True)  # cumsum fused into the kernel
     h0 = _state_in(initial_state, state_v_first)
 
     res, cp_cache = run_forward(q, k, v, A, g_cum, beta, scale, h0, tables, output_final_state,

@@ -57,12 +57,14 @@ constexpr int OFF_QS = OFF_APP + 8192;    // scale gamma .* q, 2 blocks of [64 x
 constexpr int OFF_VEC = OFF_QS + TILE;
 constexpr int VEC_SLOT_FLOATS = 5 * CHUNK;
 constexpr int OFF_BAR = OFF_VEC + 4 * VEC_SLOT_FLOATS * 4;
-constexpr int N_BARS = 18;
+constexpr int N_BARS = 24;
 constexpr int OFF_MISC = OFF_BAR + N_BARS * 8;
 constexpr int SMEM_BYTES = OFF_MISC + 16 + 1024;
 constexpr uint32_t TM_S = 0, TM_X1 = 128, TM_X2 = 192, TM_P = 256, TM_W = 384;
 enum { FULL0 = 0, FULL1, EMPTY0, EMPTY1, S_COPY, S_DEC, X1_DONE, X2_DONE, S_DONE, P_DONE, W_DONE,
-       DV_READY, W_READY, P_READY, AP_READY, QS_READY, PRIV };
+       DV_READY, W_READY, P_READY, AP_READY, QS_READY, PRIV,
+       // the A tile and the per-row vectors of a chunk travel one chunk ahead of q, k, dO
+       FULLA0, FULLA1, EMPTYA0, EMPTYA1, PRIVA };
 enum { V_G = 0, V_BG = 1, V_RHO = 2, V_SGAM = 3, V_GL = 4 };
 }  // namespace bdtc
 
@@ -109,6 +111,11 @@ bwd_dh_tc_kernel(const BwdDhTcParams p, const __grid_constant__ CUtensorMap map_
     mbar_init(&bars[AP_READY], 2);
     mbar_init(&bars[QS_READY], 2);
     mbar_init(&bars[PRIV], 1);
+    mbar_init(&bars[FULLA0], 1);
+    mbar_init(&bars[FULLA1], 1);
+    mbar_init(&bars[EMPTYA0], 2);  // the two scaling warps, the only readers of the raw A tile
+    mbar_init(&bars[EMPTYA1], 2);
+    mbar_init(&bars[PRIVA], 1);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&map_q);
@@ -419,16 +426,14 @@ bwd_dh_tc_kernel(const BwdDhTcParams p, const __grid_constant__ CUtensorMap map_
         b_r[z] = r < valid ? load_beta(p.beta, p.beta_is_f32, (row0 + r) * p.Hv + hv) : 0.f;
       }
     };
-    if (n_it > 0) fetch(0);
-    for (int it = 0; it < n_it && ok; ++it) {
-      const int s = it & 1, c = n_it - 1 - it;
+    // vectors and A tile of the chunk of iteration j (its stage's A buffer is free once the
+    // scaling warps have read it)
+    auto a_part = [&](int j) {
+      const int sj = j & 1, c = n_it - 1 - j;
       const long long row0 = sp.bos + (long long)c * CHUNK;
       const int valid = min(CHUNK, sp.len - c * CHUNK);
-      if (it >= 2) {
-        ok = WAIT(EMPTY0 + s, ((it >> 1) - 1) & 1);
-        if (!ok) break;
-      }
-      float* vs = vec + (it & 3) * VEC_SLOT_FLOATS;
+      if (j >= 2 && !WAIT(EMPTYA0 + sj, ((j >> 1) - 1) & 1)) return false;
+      float* vs = vec + (j & 3) * VEC_SLOT_FLOATS;
 #pragma unroll
       for (int z = 0; z < 2; ++z) {
         int r = 2 * lane + z;
@@ -440,13 +445,43 @@ bwd_dh_tc_kernel(const BwdDhTcParams p, const __grid_constant__ CUtensorMap map_
       }
       if (lane == 0) vs[V_GL * CHUNK] = fast_exp(gl_r);
       __syncwarp();
+      unsigned char* dst = smem + OFF_STAGE + sj * STAGE_BYTES + 3 * TILE;
+      const bool partial = valid < CHUNK;
+      uint64_t* bar = partial ? &bars[PRIVA] : &bars[FULLA0 + sj];
+      if (lane == 0) {
+        mbar_arrive_expect_tx(bar, TILE_A);
+        tma_load_2d(dst, &map_a, hv * CHUNK, (int)row0, bar);
+      }
+      if (partial) {
+        // only the last chunk of a sequence (the first one walked) can be partial: used once
+        if (!WAIT(PRIVA, 0)) return false;
+        for (int i = lane; i < (CHUNK - valid) * 8; i += 32)
+          *reinterpret_cast<uint4*>(dst + (valid + (i >> 3)) * 128 + ((i & 7) << 4)) = make_uint4(0, 0, 0, 0);
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars[FULLA0 + sj]);
+      }
+      return true;
+    };
+    if (n_it > 0) {
+      fetch(0);
+      ok = a_part(0);
+      if (n_it > 1) fetch(1);
+    }
+    for (int it = 0; it < n_it && ok; ++it) {
+      const int s = it & 1, c = n_it - 1 - it;
+      const long long row0 = sp.bos + (long long)c * CHUNK;
+      const int valid = min(CHUNK, sp.len - c * CHUNK);
+      if (it >= 2) {
+        ok = WAIT(EMPTY0 + s, ((it >> 1) - 1) & 1);
+        if (!ok) break;
+      }
       unsigned char* st = smem + OFF_STAGE + s * STAGE_BYTES;
       const bool partial = valid < CHUNK;
       uint64_t* bar = partial ? &bars[PRIV] : &bars[FULL0 + s];
       if (lane == 0) {
-        mbar_arrive_expect_tx(bar, STAGE_BYTES);
+        mbar_arrive_expect_tx(bar, STAGE_BYTES - TILE_A);
         const int y = (int)row0;
-        tma_load_2d(st + 3 * TILE, &map_a, hv * CHUNK, y, bar);
         tma_load_2d(st + TILE, &map_k, hq * D, y, bar);
         tma_load_2d(st + TILE + 8192, &map_k, hq * D + 64, y, bar);
         tma_load_2d(st, &map_q, hq * D, y, bar);
@@ -454,12 +489,10 @@ bwd_dh_tc_kernel(const BwdDhTcParams p, const __grid_constant__ CUtensorMap map_
         tma_load_2d(st + 2 * TILE, &map_do, hv * D, y, bar);
         tma_load_2d(st + 2 * TILE + 8192, &map_do, hv * D + 64, y, bar);
       }
-      if (it + 1 < n_it) fetch(it + 1);
       if (partial) {
-        // only the last chunk of a sequence (the first one walked) can be partial: used once
         ok = WAIT(PRIV, 0);
         if (!ok) break;
-        for (int blk = 0; blk < 7; ++blk) {
+        for (int blk = 0; blk < 6; ++blk) {
           unsigned char* base = st + blk * 8192;
           for (int i = lane; i < (CHUNK - valid) * 8; i += 32)
             *reinterpret_cast<uint4*>(base + (valid + (i >> 3)) * 128 + ((i & 7) << 4)) =
@@ -468,6 +501,13 @@ bwd_dh_tc_kernel(const BwdDhTcParams p, const __grid_constant__ CUtensorMap map_
         fence_proxy_async();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars[FULL0 + s]);
+      }
+      // the next chunk's vectors and A tile go out a whole chunk before its q, k, dO; slot
+      // (it + 1) % 4 of the vectors was last read for the chunk of iteration it - 3, which the wait
+      // on the stage of iteration it - 2 above has seen finished
+      if (it + 1 < n_it) {
+        ok = a_part(it + 1);
+        if (ok && it + 2 < n_it) fetch(it + 2);
       }
     }
   } else {
@@ -479,7 +519,7 @@ bwd_dh_tc_kernel(const BwdDhTcParams p, const __grid_constant__ CUtensorMap map_
     const int c8 = r & 7, r0 = r >> 3, pc_a = c8 ^ r0;
     for (int it = 0; it < n_it && ok; ++it) {
       const int s = it & 1;
-      ok = WAIT(FULL0 + s, (it >> 1) & 1);
+      ok = WAIT(FULLA0 + s, (it >> 1) & 1);
       if (ok && it > 0) ok = WAIT(W_DONE, (it - 1) & 1);  // w of the chunk before has been issued and is done
       if (!ok) break;
       const float* vs = vec + (it & 3) * VEC_SLOT_FLOATS;
@@ -497,9 +537,13 @@ bwd_dh_tc_kernel(const BwdDhTcParams p, const __grid_constant__ CUtensorMap map_
       }
       fence_proxy_async();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&bars[AP_READY]);
-      // q' has one buffer: the state update of the chunk before must have read it
-      if (it > 0) ok = WAIT(S_DONE, (it - 1) & 1);
+      if (lane == 0) {
+        mbar_arrive(&bars[AP_READY]);
+        mbar_arrive(&bars[EMPTYA0 + s]);  // the A tile of this stage is no longer read
+      }
+      // q' has one buffer: the state update of the chunk before must have read it; q has landed
+      ok = WAIT(FULL0 + s, (it >> 1) & 1);
+      if (ok && it > 0) ok = WAIT(S_DONE, (it - 1) & 1);
       if (!ok) break;
       const float sg = vs[V_SGAM * CHUNK + r];
       unsigned char* qs = smem + OFF_QS;

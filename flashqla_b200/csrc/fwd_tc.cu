@@ -48,6 +48,8 @@ __device__ int g_device_status = 0;
 // Diagnostics (FQLA_PROFILE=1): cycles the first CTA's role leaders spent per barrier wait and
 // per section, [role 0..5][slot 0..23], plus [6][0] = total cycles of the CTA.
 __device__ long long g_wait_profile[7 * 24];
+// Diagnostics: (1 << 24 | warp << 16 | barrier << 8 | parity) of the first wait that was given up
+__device__ int g_fwd_abort_info = 0;
 
 struct FwdTcParams {
   const float* g;
@@ -81,7 +83,7 @@ constexpr int OFF_APP = OFF_AP + 8192;           // A diag(beta gamma)
 constexpr int OFF_VEC = OFF_APP + 8192;          // 4 slots x 6 vectors x 64 floats
 constexpr int VEC_SLOT_FLOATS = 6 * CHUNK;
 constexpr int OFF_BAR = OFF_VEC + 4 * VEC_SLOT_FLOATS * 4;
-constexpr int N_BARS = 24;
+constexpr int N_BARS = 30;
 constexpr int OFF_MISC = OFF_BAR + N_BARS * 8;
 constexpr int SMEM_BYTES = OFF_MISC + 16 + 1024;  // + slack for 1024-byte alignment of the base
 // tensor-memory columns.  An M = 64 accumulator only occupies lanes 0-15 of each 32-lane
@@ -91,7 +93,9 @@ constexpr uint32_t TM_P = TM_O1 + (16u << 16), TM_W = TM_O2 + (16u << 16);
 // barrier indices
 enum { FULL0 = 0, FULL1, EMPTY0, EMPTY1, S_COPY, S_DEC, VN_DONE, S_DONE, P_DONE, O_DONE, W_DONE,
        VN_READY, W_READY, P_READY, O_FREE, AP_READY, VR_READY, PRIV,
-       SEC_A = 18, SEC_B, SEC_C, SEC_D, SEC_E, SEC_F };  // SEC_*: profiling slots only
+       SEC_A = 18, SEC_B, SEC_C, SEC_D, SEC_E, SEC_F,  // SEC_*: profiling slots only
+       // the A tile and the per-row vectors of a chunk travel one chunk ahead of q, k, v
+       FULLA0 = 24, FULLA1, EMPTYA0, EMPTYA1, PRIVA };
 // vectors inside a slot; V_GL holds gamma_last at [0]
 enum { V_G = 0, V_BETA = 1, V_BG = 2, V_RHO = 3, V_SGAM = 4, V_GL = 5 };
 }  // namespace fwdtc
@@ -104,7 +108,9 @@ __device__ __forceinline__ uint32_t scale_bf16x2(uint32_t packed, float lo, floa
 // PROFILE: wait/section cycle counters (diagnostics).  EXTRA: per-chunk state and v_new outputs.
 // Both are compiled out of the common instantiation: the six roles run six different code
 // regions at once, and the kernel is sensitive to its instruction-cache footprint.
-template <bool PROFILE, bool EXTRA>
+// NO_O: state-only walk (recomputation for the backward pass): no q, no output products, the
+// output warps stay idle.
+template <bool PROFILE, bool EXTRA, bool NO_O>
 __global__ void __launch_bounds__(512, 1)
 fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
               const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
@@ -128,8 +134,13 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
   if (tid == 0) {
     mbar_init(&bars[FULL0], 1);
     mbar_init(&bars[FULL1], 1);
-    mbar_init(&bars[EMPTY0], 1 + 2);  // MMA commit + the two prep warps (they read the A tile)
-    mbar_init(&bars[EMPTY1], 1 + 2);
+    mbar_init(&bars[EMPTY0], 1);  // MMA commit
+    mbar_init(&bars[EMPTY1], 1);
+    mbar_init(&bars[FULLA0], 1);
+    mbar_init(&bars[FULLA1], 1);
+    mbar_init(&bars[EMPTYA0], 2);  // the two prep warps, the only readers of the raw A tile
+    mbar_init(&bars[EMPTYA1], 2);
+    mbar_init(&bars[PRIVA], 1);
     mbar_init(&bars[S_COPY], 128);
     mbar_init(&bars[S_DEC], 128);
     mbar_init(&bars[VN_DONE], 1);
@@ -171,11 +182,13 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
   long long t_sec = 0;
   auto WAIT = [&](int idx, uint32_t parity) {
     if constexpr (!PROFILE) {
-      return mbar_wait(&bars[idx], parity, abort_flag);
+      const bool r = mbar_wait(&bars[idx], parity, abort_flag);
+      if (!r) atomicCAS(&g_fwd_abort_info, 0, (1 << 24) | (warp << 16) | (idx << 8) | (int)parity);
+      return r;
     } else {
       long long t0 = clock64();
       bool r = mbar_wait(&bars[idx], parity, abort_flag);
-      waited[idx] += clock64() - t0;
+      if (idx < 24) waited[idx] += clock64() - t0;
       return r;
     }
   };
@@ -362,6 +375,7 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
       if (it + 1 < n_it) ok = convert_w(it + 1);
     }
   } else if (warp >= 12) {
+    if constexpr (!NO_O) {
     // =============================== O group ===============================
     // M = 64 accumulators are read with the 16-lane shape: lane l of warp q owns rows
     // 16q + l/4 and 16q + l/4 + 8, and in every group of 8 columns the pair 2*(l%4), +1.
@@ -459,6 +473,7 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
         *reinterpret_cast<uint4*>(p.o + ((end + (i >> 4)) * p.Hv + hv) * D + (i & 15) * 8) =
             make_uint4(0, 0, 0, 0);
     }
+    }  // !NO_O
   } else if (warp == 0) {
     // =============================== MMA issuer ===============================
     if (lane == 0) {
@@ -501,7 +516,7 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
           if (!ok) break;
           tc_fence_after();
           issue_u_w(0);
-          issue_p(0);
+          if constexpr (!NO_O) issue_p(0);
         }
         ok = WAIT(S_COPY, it & 1) && WAIT(W_READY, it & 1);
         if (!ok) break;
@@ -520,15 +535,17 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
           }
         }
         SEC_END(SEC_A);
-        if (it > 0) {
-          ok = WAIT(O_FREE, (it - 1) & 1);
-          if (!ok) break;
-          tc_fence_after();
+        if constexpr (!NO_O) {
+          if (it > 0) {
+            ok = WAIT(O_FREE, (it - 1) & 1);
+            if (!ok) break;
+            tc_fence_after();
+          }
+          SEC_BEGIN();
+          // O1 = Q S      (B = S^T copy: N = v rows, K = k)
+          umma_group<8, 2, 512, 2, 1024, false>(tmem + TM_O1, q0_lo + so, st_lo, ID_O);
+          SEC_END(SEC_B);
         }
-        SEC_BEGIN();
-        // O1 = Q S      (B = S^T copy: N = v rows, K = k)
-        umma_group<8, 2, 512, 2, 1024, false>(tmem + TM_O1, q0_lo + so, st_lo, ID_O);
-        SEC_END(SEC_B);
         ok = WAIT(VR_READY, it & 1) && WAIT(S_DEC, it & 1);
         if (!ok) break;
         tc_fence_after();
@@ -537,6 +554,7 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
         umma_group<4, 2, 0, 128, 0, true>(tmem + TM_S, vrt_lo, kmn0_lo + so, ID_S);
         if constexpr (EXTRA) tma_store_wait_read();  // the S^T tile may be rewritten after this
         umma_commit(&bars[S_DONE]);
+        if constexpr (NO_O) umma_commit(&bars[EMPTY0 + s]);  // last product that reads this stage
         SEC_END(SEC_C);
         if (it + 1 < n_it) {
           ok = WAIT(FULL0 + (s ^ 1), ((it + 1) >> 1) & 1) && WAIT(AP_READY, (it + 1) & 1) &&
@@ -548,19 +566,21 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
           SEC_END(SEC_D);
           if constexpr (EXTRA) store_vn(it);
         }
-        ok = WAIT(P_READY, it & 1) && (it + 1 < n_it || WAIT(VN_READY, it & 1));
+        ok = (NO_O || WAIT(P_READY, it & 1)) && (it + 1 < n_it || WAIT(VN_READY, it & 1));
         if (!ok) break;
         tc_fence_after();
         if constexpr (EXTRA) {
           if (it + 1 >= n_it) store_vn(it);
         }
-        SEC_BEGIN();
-        // O2 = Pg Vn     (B = Vn^T copy: N = v rows, K = tok')
-        umma_group<4, 2, 0, 2, 0, false>(tmem + TM_O2, p_lo, vnt_lo, ID_O);
-        umma_commit(&bars[O_DONE]);
-        umma_commit(&bars[EMPTY0 + s]);
-        if (it + 1 < n_it) issue_p(so_next);
-        SEC_END(SEC_E);
+        if constexpr (!NO_O) {
+          SEC_BEGIN();
+          // O2 = Pg Vn     (B = Vn^T copy: N = v rows, K = tok')
+          umma_group<4, 2, 0, 2, 0, false>(tmem + TM_O2, p_lo, vnt_lo, ID_O);
+          umma_commit(&bars[O_DONE]);
+          umma_commit(&bars[EMPTY0 + s]);
+          if (it + 1 < n_it) issue_p(so_next);
+          SEC_END(SEC_E);
+        }
       }
       if constexpr (EXTRA) tma_store_wait_all();
     }
@@ -578,16 +598,13 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
         b_r[z] = r < valid ? load_beta(p.beta, p.beta_is_f32, (row0 + r) * p.Hv + hv) : 0.f;
       }
     };
-    if (n_it > 0) fetch(0);
-    for (int it = 0; it < n_it && ok; ++it) {
-      const int s = it & 1;
-      const long long row0 = sp.bos + (long long)it * CHUNK;
-      const int valid = min(CHUNK, sp.len - it * CHUNK);
-      if (it >= 2) {
-        ok = WAIT(EMPTY0 + s, ((it >> 1) - 1) & 1);
-        if (!ok) break;
-      }
-      float* vs = vec + (it & 3) * VEC_SLOT_FLOATS;
+    // vectors and A tile of chunk j (its stage's A buffer is free once the prep warps have read it)
+    auto a_part = [&](int j) {
+      const int sj = j & 1;
+      const long long row0 = sp.bos + (long long)j * CHUNK;
+      const int valid = min(CHUNK, sp.len - j * CHUNK);
+      if (j >= 2 && !WAIT(EMPTYA0 + sj, ((j >> 1) - 1) & 1)) return false;
+      float* vs = vec + (j & 3) * VEC_SLOT_FLOATS;
 #pragma unroll
       for (int z = 0; z < 2; ++z) {
         int r = 2 * lane + z;
@@ -600,26 +617,57 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
       }
       if (lane == 0) vs[V_GL * CHUNK] = fast_exp(gl_r);
       __syncwarp();
+      unsigned char* dst = smem + OFF_STAGE + sj * STAGE_BYTES + 2 * TILE_QK + TILE_V;
+      const bool partial = valid < CHUNK;
+      uint64_t* bar = partial ? &bars[PRIVA] : &bars[FULLA0 + sj];
+      if (lane == 0) {
+        mbar_arrive_expect_tx(bar, TILE_A);
+        tma_load_2d(dst, &map_a, hv * CHUNK, (int)row0, bar);
+      }
+      if (partial) {
+        // rows past the sequence end belong to the next sequence: wait for the copy, zero them
+        // (only the last chunk of a sequence can be partial: the private barrier is used once)
+        if (!WAIT(PRIVA, 0)) return false;
+        for (int i = lane; i < (CHUNK - valid) * 8; i += 32)
+          *reinterpret_cast<uint4*>(dst + (valid + (i >> 3)) * 128 + ((i & 7) << 4)) = make_uint4(0, 0, 0, 0);
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars[FULLA0 + sj]);
+      }
+      return true;
+    };
+    if (n_it > 0) {
+      fetch(0);
+      ok = a_part(0);
+      if (n_it > 1) fetch(1);
+    }
+    for (int it = 0; it < n_it && ok; ++it) {
+      const int s = it & 1;
+      const long long row0 = sp.bos + (long long)it * CHUNK;
+      const int valid = min(CHUNK, sp.len - it * CHUNK);
+      if (it >= 2) {
+        ok = WAIT(EMPTY0 + s, ((it >> 1) - 1) & 1);
+        if (!ok) break;
+      }
       unsigned char* st = smem + OFF_STAGE + s * STAGE_BYTES;
       const bool partial = valid < CHUNK;
       uint64_t* bar = partial ? &bars[PRIV] : &bars[FULL0 + s];
       if (lane == 0) {
-        mbar_arrive_expect_tx(bar, STAGE_BYTES);
+        mbar_arrive_expect_tx(bar, STAGE_BYTES - TILE_A - (NO_O ? TILE_QK : 0));
         const int y = (int)row0;
-        tma_load_2d(st + 2 * TILE_QK + TILE_V, &map_a, hv * CHUNK, y, bar);
         tma_load_2d(st + TILE_QK, &map_k, hq * D, y, bar);
         tma_load_2d(st + TILE_QK + 8192, &map_k, hq * D + 64, y, bar);
         tma_load_2d(st + 2 * TILE_QK, &map_v, hv * D, y, bar);
         tma_load_2d(st + 2 * TILE_QK + 8192, &map_v, hv * D + 64, y, bar);
-        tma_load_2d(st, &map_q, hq * D, y, bar);
-        tma_load_2d(st + 8192, &map_q, hq * D + 64, y, bar);
+        if constexpr (!NO_O) {
+          tma_load_2d(st, &map_q, hq * D, y, bar);
+          tma_load_2d(st + 8192, &map_q, hq * D + 64, y, bar);
+        }
       }
-      if (it + 1 < n_it) fetch(it + 1);  // in flight while this warp waits for the next free stage
       if (partial) {
-        // rows past the sequence end belong to the next sequence: wait for the copy, zero them
-        ok = WAIT(PRIV, 0);  // only the last chunk of a sequence can be partial: used once
+        ok = WAIT(PRIV, 0);
         if (!ok) break;
-        for (int blk = 0; blk < 7; ++blk) {
+        for (int blk = 0; blk < 6; ++blk) {
           unsigned char* base = st + blk * 8192;
           for (int i = lane; i < (CHUNK - valid) * 8; i += 32)
             *reinterpret_cast<uint4*>(base + (valid + (i >> 3)) * 128 + ((i & 7) << 4)) =
@@ -628,6 +676,14 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
         fence_proxy_async();
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars[FULL0 + s]);
+      }
+      // The next chunk's vectors and A tile go out now, a whole chunk before its q, k, v: the
+      // q, k, v stage of chunk it + 1 is still in use, but the prep warps can start on A early.
+      // (Slot (it + 1) % 4 of the vectors was last read for chunk it - 3, which the wait on the
+      // stage of chunk it - 2 above has seen finished.)
+      if (it + 1 < n_it) {
+        ok = a_part(it + 1);
+        if (ok && it + 2 < n_it) fetch(it + 2);
       }
     }
   } else {
@@ -639,7 +695,7 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
     const int pc = c8 ^ r0;  // physical piece: rows r0 + 8 i all have (row & 7) == r0
     for (int it = 0; it < n_it && ok; ++it) {
       const int s = it & 1;
-      ok = WAIT(FULL0 + s, (it >> 1) & 1);
+      ok = WAIT(FULLA0 + s, (it >> 1) & 1);
       if (ok && it > 0) ok = WAIT(W_DONE, (it - 1) & 1);  // u, w of the chunk before are done
       if (!ok) break;
       SEC_BEGIN();
@@ -664,7 +720,7 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
       __syncwarp();
       if (lane == 0) {
         mbar_arrive(&bars[AP_READY]);
-        mbar_arrive(&bars[EMPTY0 + s]);  // the A tile of this stage is no longer read here
+        mbar_arrive(&bars[EMPTYA0 + s]);  // the A tile of this stage is no longer read here
       }
       SEC_END(SEC_A);
     }
@@ -725,8 +781,8 @@ int launch_fwd_tc(const void* q, const void* k, const void* v, const void* A, co
   using namespace fwdtc;
   CUtensorMap mq, mk, mv, ma, mh, mvn;
   int rc;
-  // without q (recomputation of h and v_new for the backward pass) the output products run on
-  // k instead; their result is never stored
+  // without q (recomputation of h and v_new for the backward pass) the state-only variant runs;
+  // its q map is never used and only has to be a valid map
   if ((rc = make_map(&mq, q ? q : k, T_rows, (long long)Hq * D))) return rc;
   if ((rc = make_map(&mk, k, T_rows, (long long)Hq * D))) return rc;
   if ((rc = make_map(&mv, v, T_rows, (long long)Hv * D))) return rc;
@@ -753,12 +809,17 @@ int launch_fwd_tc(const void* q, const void* k, const void* v, const void* A, co
     kernel<<<(unsigned)(N * Hv), 512, SMEM_BYTES, st>>>(p, mq, mk, mv, ma, mh, mvn);
     return (int)cudaGetLastError();
   };
-  if (p.profile) return launch(fwd_tc_kernel<true, true>);
-  if (extra) return launch(fwd_tc_kernel<false, true>);
-  return launch(fwd_tc_kernel<false, false>);
+  if (p.profile) return launch(fwd_tc_kernel<true, true, false>);
+  if (!q && !o) return launch(fwd_tc_kernel<false, true, true>);  // recomputation of h, v_new
+  if (extra) return launch(fwd_tc_kernel<false, true, false>);
+  return launch(fwd_tc_kernel<false, false, false>);
 }
 
 }  // namespace fqla
+
+extern "C" int fqla_debug_abort_info(int* out) {
+  return (int)cudaMemcpyFromSymbol(out, fqla::g_fwd_abort_info, sizeof(int));
+}
 
 extern "C" int fqla_debug_wait_profile(long long* out168) {
   return (int)cudaMemcpyFromSymbol(out168, fqla::g_wait_profile, sizeof(long long) * 7 * 24);

@@ -105,8 +105,8 @@ __device__ __forceinline__ void store_frag(float* C, int ldc, const float (&c)[N
 template <int D>
 __global__ void __launch_bounds__(128) kkt_solve_kernel(
     const bf16* __restrict__ k, const void* __restrict__ beta, int beta_is_f32,
-    const float* __restrict__ g, bf16* __restrict__ A, int Hq, int Hv, SeqLayout lay,
-    IndexTable chunk_indices) {
+    const float* __restrict__ g, float* __restrict__ g_cum_out, bf16* __restrict__ A, int Hq,
+    int Hv, SeqLayout lay, IndexTable chunk_indices) {
   constexpr int LDK = D + 8;
   constexpr int LDL = CHUNK + 4;  // floats; rows stay 16-byte aligned
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -138,9 +138,25 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(
   load_tile_async<D, LDK, 128>(sK, k + (row0 * Hq + hq) * D, (long long)Hq * D, valid, tid);
   cp_async_commit();
   if (tid < CHUNK) {
-    int r = min(tid, valid - 1);
-    sG[tid] = g[(row0 + r) * Hv + hv];
     sB[tid] = tid < valid ? load_beta(beta, beta_is_f32, (row0 + tid) * Hv + hv) : 0.f;
+    if (g_cum_out) {
+      // g is the raw log gate: chunk-local inclusive prefix sum over the valid rows (rows past
+      // the end repeat the last value, as the clamped read below does), done by the first two warps
+      float x = tid < valid ? g[(row0 + tid) * Hv + hv] : 0.f;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const float y = __shfl_up_sync(0xffffffffu, x, d);
+        if (lane >= d) x += y;
+      }
+      if (tid == 31) sL[0] = x;
+      asm volatile("bar.sync 1, 64;" ::: "memory");
+      if (tid >= 32) x += sL[0];
+      sG[tid] = x;
+      if (tid < valid) g_cum_out[(row0 + tid) * Hv + hv] = x;
+    } else {
+      int r = min(tid, valid - 1);
+      sG[tid] = g[(row0 + r) * Hv + hv];
+    }
   }
   cp_async_wait<0>();
   __syncthreads();
@@ -272,20 +288,21 @@ extern "C" int fqla_chunk_local_cumsum(const float* g, float* out, int B, int T,
 }
 
 template <int D>
-static int launch_kkt(const void* k, const void* beta, int beta_is_f32, const float* g, void* A,
-                      int Hq, int Hv, SeqLayout lay, IndexTable ci, long long n,
-                      cudaStream_t st) {
+static int launch_kkt(const void* k, const void* beta, int beta_is_f32, const float* g,
+                      float* g_cum_out, void* A, int Hq, int Hv, SeqLayout lay, IndexTable ci,
+                      long long n, cudaStream_t st) {
   constexpr int k_tile = CHUNK * (D + 8) * 2, x_tile = CHUNK * (CHUNK + 4) * 4;
   constexpr int smem = (k_tile > x_tile ? k_tile : x_tile) + x_tile + 2 * CHUNK * 4 + 32 * 40 * 4;
   int rc = configure_smem((const void*)kkt_solve_kernel<D>, smem);
   if (rc != 0) return rc;
   kkt_solve_kernel<D><<<dim3((unsigned)n, Hv), 128, smem, st>>>(
-      (const bf16*)k, beta, beta_is_f32, g, (bf16*)A, Hq, Hv, lay, ci);
+      (const bf16*)k, beta, beta_is_f32, g, g_cum_out, (bf16*)A, Hq, Hv, lay, ci);
   return (int)cudaGetLastError();
 }
 
 extern "C" int fqla_kkt_solve(const void* k, const void* beta, int beta_is_f32,
-                              const float* g_cum, void* A, int B, int T, int Hq, int Hv, int D,
+                              const float* g_cum, float* g_cum_out, void* A, int B, int T, int Hq,
+                              int Hv, int D,
                               const void* cu_seqlens, int idx_is64, const void* chunk_indices,
                               long long num_chunks, void* stream) {
   if (!k || !beta || !g_cum || !A || Hq <= 0 || Hv % Hq) return FQLA_ERR_INVALID_ARG;
@@ -295,8 +312,8 @@ extern "C" int fqla_kkt_solve(const void* k, const void* beta, int beta_is_f32,
   long long n = cu_seqlens ? num_chunks : (long long)B * ((T + CHUNK - 1) / CHUNK);
   if (n <= 0) return FQLA_OK;
   cudaStream_t st = (cudaStream_t)stream;
-  if (D == 128) return launch_kkt<128>(k, beta, beta_is_f32, g_cum, A, Hq, Hv, lay, ci, n, st);
-  if (D == 64) return launch_kkt<64>(k, beta, beta_is_f32, g_cum, A, Hq, Hv, lay, ci, n, st);
+  if (D == 128) return launch_kkt<128>(k, beta, beta_is_f32, g_cum, g_cum_out, A, Hq, Hv, lay, ci, n, st);
+  if (D == 64) return launch_kkt<64>(k, beta, beta_is_f32, g_cum, g_cum_out, A, Hq, Hv, lay, ci, n, st);
   return FQLA_ERR_UNSUPPORTED_DIM;
 }
 

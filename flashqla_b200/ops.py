@@ -118,9 +118,11 @@ def chunk_local_cumsum(g, chunk_size: int = CHUNK_SIZE, cu_seqlens=None, reverse
     return out
 
 
-def kkt_solve(k, b, g_cum, cu_seqlens=None, chunk_size: int = CHUNK_SIZE):
+def kkt_solve(k, b, g_cum, cu_seqlens=None, chunk_size: int = CHUNK_SIZE, raw_gate: bool = False):
     """``A = (I + strict_lower(diag(b) K K^T * decay))^-1`` per (chunk, value head), bf16
-    ``[B,T,Hv,64]`` (reference: ``blackwell/kkt_solve.py:284-324``; the gate is folded in)."""
+    ``[B,T,Hv,64]`` (reference: ``blackwell/kkt_solve.py:284-324``; the gate is folded in).
+    With ``raw_gate`` the third argument is the raw per-token log gate, its chunk-local cumsum is
+    formed in the same kernel, and ``(g_cum, A)`` is returned."""
     assert chunk_size == CHUNK_SIZE
     _require_cuda(k, b, g_cum)
     _check_bf16(k=k)
@@ -128,11 +130,17 @@ def kkt_solve(k, b, g_cum, cu_seqlens=None, chunk_size: int = CHUNK_SIZE):
     Hv = b.shape[-1]
     tb = SeqTables(B, T, cu_seqlens)
     A = torch.empty(B, T, Hv, CHUNK_SIZE, dtype=k.dtype, device=k.device)
+    g_out = None
+    if raw_gate:
+        assert g_cum.dtype == torch.float32 and g_cum.is_contiguous()
+        g_out = torch.empty_like(g_cum)
+        if tb.total < B * T:  # rows past the last packed sequence: zero, as the cumsum kernel leaves them
+            g_out[:, tb.total:].zero_()
     st = _lib.load().fqla_kkt_solve(
-        _ptr(k), _ptr(b), _beta_flag(b), _ptr(g_cum), _ptr(A), B, T, Hq, Hv, D, _ptr(tb.cu),
-        tb.is64, _ptr(tb.chunk_indices), tb.num_chunks, _stream(k))
+        _ptr(k), _ptr(b), _beta_flag(b), _ptr(g_cum), _ptr(g_out), _ptr(A), B, T, Hq, Hv, D,
+        _ptr(tb.cu), tb.is64, _ptr(tb.chunk_indices), tb.num_chunks, _stream(k))
     _lib.check(st, "kkt_solve")
-    return A
+    return (g_out, A) if raw_gate else A
 
 
 def fwd_seq(q, k, v, a, g_cum, b, scale, initial_state=None, *, output_final_state=False,

@@ -50,10 +50,14 @@ int fqla_chunk_local_cumsum(const float* g, float* out, int B, int T, int H,
 /* A = (I + strict_lower(diag(beta) K K^T * exp(g_s - g_t)))^-1 per (chunk, value head); row t of
  * A holds row (t mod 64) of its chunk's matrix.
  * Replaces kkt_solve, flash_qla/ops/gated_delta_rule/chunk/blackwell/kkt_solve.py:284-324
- * (this library folds the gate into A, as the reference's tests/ref_gdr.py:77-140 does). */
-int fqla_kkt_solve(const void* k, const void* beta, int beta_is_f32, const float* g_cum, void* A,
-                   int B, int T, int Hq, int Hv, int D, const void* cu_seqlens, int idx_is64,
-                   const void* chunk_indices, long long num_chunks, void* stream);
+ * (this library folds the gate into A, as the reference's tests/ref_gdr.py:77-140 does).
+ * g_cum_out (optional): when given, g_cum is taken as the RAW per-token log gate and its
+ * chunk-local cumulative sum (what fqla_chunk_local_cumsum computes) is formed in the same
+ * kernel and written to g_cum_out on the rows that belong to sequences. */
+int fqla_kkt_solve(const void* k, const void* beta, int beta_is_f32, const float* g_cum,
+                   float* g_cum_out, void* A, int B, int T, int Hq, int Hv, int D,
+                   const void* cu_seqlens, int idx_is64, const void* chunk_indices,
+                   long long num_chunks, void* stream);
 
 /* Sequential forward recurrence.  Optional outputs (NULL to skip): o, per-chunk states h,
  * vnew (the delta-rule corrected values, needed by the backward), final state ht, and the

@@ -176,3 +176,21 @@ def test_merge_states_against_host_chain():
                 assert orc.rel_err(out[i], cur) < 1e-5, (reverse, r, i)
                 m = M[i].transpose(-1, -2) if reverse else M[i]
                 cur = local[i] + use[i].view(Hv, 1, 1) * (m @ cur)
+
+
+@pytest.mark.parametrize("cu", [None, [0, 130, 130, 777, 1000]], ids=["fixed", "varlen"])
+def test_kkt_solve_with_fused_cumsum(cu):
+    """kkt_solve fed with the raw gate forms the chunk-local cumsum itself: same g_cum as the
+    cumsum kernel (up to the order of the fp32 additions) and the same A."""
+    from flashqla_b200 import ops
+
+    T = 1024 if cu is None else 1000
+    d = _inputs(T, 2, 4, seed=41, cu=cu)
+    cu_t = d["cu_seqlens"]
+    g_ref = ops.chunk_local_cumsum(d["g"], 64, cu_t)
+    A_ref = ops.kkt_solve(d["k"], d["beta"], g_ref, cu_t)
+    g_cum, A = ops.kkt_solve(d["k"], d["beta"], d["g"], cu_t, raw_gate=True)
+    assert orc.rel_err(g_cum, g_ref) < 1e-6
+    assert orc.rel_err(A.float(), A_ref.float()) < 1e-3
+    want = orc.chunk_local_cumsum(d["g"].cpu(), None if cu_t is None else cu_t.cpu())
+    assert orc.rel_err(g_cum.cpu(), want) < 1e-6
