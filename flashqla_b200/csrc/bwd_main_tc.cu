@@ -6,14 +6,18 @@
 // tcgen05.mma with M = 64 (rows = tokens) and fp32 accumulators in tensor memory; two M = 64
 // accumulators share each column range (lanes +0 and +16 of every 32-lane quarter).
 //
-// Roles: warp 16 issues every product and every TMA load (one elected thread); warps 0-15 read the
-// accumulators (16-lane shape; 4 lane quarters x 4 column quarters), do the elementwise work and
-// write the intermediate operands (dw, ds, dA, T, dA3) back to shared memory as bf16 tiles.  The
-// two sides are coupled by one mbarrier per product group (commit -> read-out) and one per
-// operand tile (written -> may be multiplied), so that the dependent chain
-//     dw -> dA -> T = A^T dA -> dA3 -> (dA3 K, (beta dA3)^T K)
-// overlaps with the products and read-outs that do not depend on it.  Operand tiles of the next
-// item are fetched as soon as the buffers of the current one are dead (k has two buffers).
+// Roles: warp 16 issues every product and every TMA load (one elected thread).  Warps 0-7 (chain
+// group) read the 64-wide accumulators (16-lane shape) and write the intermediate operands (dw,
+// ds, dA, T, dA3) back to shared memory as bf16 tiles; warps 8-15 (bulk group) do what is off the
+// dependent chain: the h.dh sum, dq1 | dk1 (scaled in place in tensor memory), dv and the final
+// dq | dk, read in the 32-lane shape with 16-byte shared and global accesses.  The sides are
+// coupled by one mbarrier per product group (commit -> read-out) and one per operand tile
+// (written -> may be multiplied), so that the chain
+//     dw -> dA -> T = A^T dA -> dA3 -> (beta dA3) K, (beta dA3)^T K
+// never waits for the bulk work.  Row scalings ride on operands where they can (A diag(beta),
+// A diag(beta gamma) are written over the dead v tile; dk is one accumulator fed by four
+// products).  Operand tiles of the next item are fetched as soon as the buffers of the current
+// one are dead (k has two buffers).
 #include <cuda.h>
 
 #include "common.cuh"
@@ -85,7 +89,9 @@ constexpr uint32_t T_D3 = 256;                         // after x1 has been read
 enum {
   L_A = 0, L_B, L_C,                                       // TMA groups landed
   C_DW, C_DSQK, C_1B, C_X, C_2B, C_T, C_D3, C_5,           // product groups complete (commit)
-  R_ZERO, R_HD, R_DW, R_DS, R_DA, R_T, R_E6, R_D3, R_END   // read-out side -> issue warp (16 warps)
+  R_ZERO, R_END,                     // all 16 read-out warps -> issue warp
+  R_DW, R_DS, R_DA, R_T, R_D3,       // the 8 warps of the chain group -> issue warp
+  R_HD, R_E4                         // the 8 warps of the bulk group -> issue warp
 };
 }  // namespace bmtc
 
@@ -177,7 +183,9 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
 
   if (tid == 0) {
     for (int i = L_A; i <= C_5; ++i) mbar_init(&bars[i], 1);
-    for (int i = R_ZERO; i <= R_END; ++i) mbar_init(&bars[i], N_EPI / 32);
+    mbar_init(&bars[R_ZERO], N_EPI / 32);
+    mbar_init(&bars[R_END], N_EPI / 32);
+    for (int i = R_DW; i <= R_E4; ++i) mbar_init(&bars[i], N_EPI / 64);
     *abort_flag = 0;
     *stop_flag = 0;
     fence_mbar_init();
@@ -332,8 +340,8 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
         umma_group<4, 2, 0, 2, 0, false>(tmem + T_D3, da_lo, a_lo, ID_KK_64);
         umma_commit(&bars[C_D3]);
         if (has_next) {
-          // du, q, v are dead once their products are complete and the read-out has used q, v
-          ok = WAIT(C_2B, ph) && WAIT(R_E6, ph);
+          // du, q, v are dead once their products are complete and the bulk group has used q
+          ok = WAIT(C_2B, ph) && WAIT(R_E4, ph);
           if (!ok) break;
           load_b(nxt);
           ok = WAIT(C_D3, ph);  // last product that reads A
@@ -354,21 +362,26 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
     }
   } else {
     // ====================== read-out warps ======================
-    // 64-wide accumulators (ds, qk, x1, x2, T, d3, kk) are read in the 16-lane shape: lane l of
-    // warp (qd, cq) owns rows 16 qd + l/4 (+8) and column pairs 16 cq + 8 i + 2 (l%4).
-    // 128-wide accumulators are read in the 32-lane shape, which returns the accumulator at lanes
-    // +0 and the one at lanes +16 of the same columns at once: lane l owns row 16 qd + l%16 of
-    // the lower (l < 16) or upper (l >= 16) accumulator, 32 consecutive columns 32 cq ..; shared
-    // memory and global memory are then touched 16 bytes at a time.
-    const int qd = warp & 3, cq = warp >> 2;
+    // Two groups of eight warps.  The CHAIN group (warps 0-7) serves the dependent chain
+    // dw -> dA -> T -> dA3 (plus ds, which it gets for free from the same kind of tile): it reads
+    // the 64-wide accumulators in the 16-lane shape (lane l of warp (qd, half) owns rows
+    // 16 qd + l/4 (+8), column pairs 32 half + 8 i + 2 (l%4)).  The BULK group (warps 8-15) does
+    // everything that is off the chain: the h.dh sum, the scaling of dq1 | dk1 (written back to
+    // tensor memory), dv, and the final dq | dk.  It reads the 128-wide accumulators in the
+    // 32-lane shape, which returns the accumulator at lanes +0 and the one at lanes +16 of the
+    // same columns at once: lane l owns row 16 qd + l%16 of the lower (l < 16) or upper one, 32
+    // consecutive columns per pass; shared and global memory are touched 16 bytes at a time.
+    const bool chain = warp < 8;
+    const int gw = warp & 7, qd = gw & 3, half = gw >> 2;
     const int row_a = 16 * qd + (lane >> 2), row_b = row_a + 8, cp = 2 * (lane & 3);
     const int row_w = 16 * qd + (lane & 15);
     const bool hi = lane >= 16;
     const uint32_t lanes = (uint32_t)(qd * 32) << 16;
-    const int c128 = 32 * cq, c64 = 16 * cq;
-    // byte offset of this thread's 16-byte piece j (8 columns) inside a [64 x 128] row tile
-    const int piece_base = (cq >> 1) * 8192 + row_w * 128;
-    auto piece = [&](int j) { return piece_base + (((4 * (cq & 1) + j) ^ (row_w & 7)) << 4); };
+    const int c64 = 32 * half;    // first column of this warp in 64-wide tiles (chain group)
+    const int c128 = 64 * half;   // first column of this warp in 128-wide tiles
+    // byte offset of this thread's 16-byte piece (pass, j) (8 columns) inside a [64 x 128] row tile
+    const int piece_base = half * 8192 + row_w * 128;
+    auto piece = [&](int pass, int j) { return piece_base + (((4 * pass + j) ^ (row_w & 7)) << 4); };
     auto quad_sum = [&](float x) {
       x += __shfl_xor_sync(0xffffffffu, x, 1);
       x += __shfl_xor_sync(0xffffffffu, x, 2);
@@ -412,11 +425,6 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
     Item cur = decode(blockIdx.x);
     fetch_vectors(cur);
     uint32_t it = 0;
-    const bool prof = p.profile && tid == 0 && blockIdx.x == 0;
-    int stamp_i = 0;
-    auto stamp = [&]() {
-      if (prof && stamp_i < 64) g_bwd_main_profile[stamp_i++] = clock64();
-    };
 #pragma unroll 1
     for (long long w = blockIdx.x; w < total; w += gridDim.x, ++it) {
       const uint32_t ph = it & 1;
@@ -431,7 +439,6 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
         sRho[tid] = fast_exp(pre_gl - pre_g);
         sBeta[tid] = pre_beta;
       }
-      stamp();
       epi_barrier();
       if (*stop_flag) break;  // written before the barrier by one thread: uniform
       bool ok = WAIT(L_A, ph) && WAIT(L_B, ph) && WAIT(L_C, ph);
@@ -448,263 +455,266 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
       }
       signal(R_ZERO);
       if (has_next) fetch_vectors(nxt);
-      stamp();
-      const float g_a = sG[row_a], g_b = sG[row_b];
-      const float beta_a = sBeta[row_a], beta_b = sBeta[row_b];
-      // factor and tile of the 128-wide step that reads dq1 (lower lanes) and dk1 (upper lanes)
-      const float f_w = hi ? sRho[row_w] : p.scale * sGam[row_w];
-      const bf16* out_w_base = nullptr;
-      const long long out_w = ((cur.row0 + row_w) * p.Hv + cur.hv) * D + c128;
-      const bool wr_w = row_w < valid;
-      float keep[32];  // scaled dq1 (lower lanes) / dk1 (upper lanes) until the last step
-      (void)out_w_base;
-      // this thread's share of the row sums (dg, db), column sums (dg, and the two column terms of
-      // db / dg that come from A^T dw and A^T du) and of the chunk total; reduced across lanes
-      // once, at the end of the item
-      float acc_dg_a = 0.f, acc_dg_b = 0.f, acc_db_a = 0.f, acc_db_b = 0.f, acc_last = 0.f, acc_w = 0.f;
-      float acc_col[4] = {0.f, 0.f, 0.f, 0.f};
-      float acc_c1[4] = {0.f, 0.f, 0.f, 0.f}, acc_c2[4] = {0.f, 0.f, 0.f, 0.f};
+      float acc_last = 0.f;
 
-      // ---- E1: dw = -du h^T as an operand tile ----
-      stamp();
-      ok = ok && WAIT(C_DW, ph);
-      stamp();
-      if (ok) {
-        tc_fence_after();
-        float x[32];
-        tmem_ld32(tmem + lanes + T_DW + c128, x);
-        tmem_ld_wait();
-        if (!hi) {
+      if (chain) {
+        // ===================== chain group =====================
+        const float g_a = sG[row_a], g_b = sG[row_b];
+        const float beta_a = sBeta[row_a], beta_b = sBeta[row_b];
+        // row sums (dg, db) and column sums (dg; the two column terms that come from A^T dw and
+        // A^T du) of this thread; reduced across lanes once, at the end of the item
+        float acc_dg_a = 0.f, acc_dg_b = 0.f, acc_db_a = 0.f, acc_db_b = 0.f;
+        float acc_col[8], acc_c1[8], acc_c2[8];
 #pragma unroll
-          for (int j = 0; j < 32; ++j) x[j] = -x[j];
+        for (int j = 0; j < 8; ++j) acc_col[j] = acc_c1[j] = acc_c2[j] = 0.f;
+
+        // ---- E1: dw = -du h^T as an operand tile (lower lanes of the 32-lane shape) ----
+        ok = ok && WAIT(C_DW, ph);
+        if (ok) {
+          tc_fence_after();
+#pragma unroll 1
+          for (int pass = 0; pass < 2; ++pass) {
+            float x[32];
+            tmem_ld32(tmem + lanes + T_DW + c128 + 32 * pass, x);
+            tmem_ld_wait();
+            if (!hi) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(smem + OFF_DW + piece(j)) = pack8(x + 8 * j);
-        }
-      }
-      signal(R_DW);
-      // gamma_last * sum(h * dh) over the whole 128 x 128 tiles (plain shared-memory reads), while
-      // the issue warp works on the products that wait for dw
-      if (ok) {
-        float hd = 0.f;
-        for (int i = tid; i < SQ_TILE / 16; i += N_EPI) {
-          const uint4 a = *reinterpret_cast<const uint4*>(smem + OFF_H + i * 16);
-          const uint4 b = *reinterpret_cast<const uint4*>(smem + OFF_DH + i * 16);
-          const uint32_t* pa = &a.x;
-          const uint32_t* pb = &b.x;
+              for (int j = 0; j < 32; ++j) x[j] = -x[j];
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            float2 fa = __bfloat1622float2(*reinterpret_cast<const bf162*>(&pa[e]));
-            float2 fb = __bfloat1622float2(*reinterpret_cast<const bf162*>(&pb[e]));
-            hd += fa.x * fb.x + fa.y * fb.y;
+              for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(smem + OFF_DW + piece(pass, j)) = pack8(x + 8 * j);
+            }
           }
         }
-        acc_last += sGam[CHUNK - 1] * hd;
-      }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars[R_HD]);
+        signal(R_DW);
 
-      // ---- E2: ds = scale * G * (dO Vn^T); ds2 = ds * (Q K^T) ----
-      stamp();
-      ok = ok && WAIT(C_DSQK, ph);
-      stamp();
-      if (ok) {
-        tc_fence_after();
-        float ds[8], qk[8];
-        tmem_ld_16x16(tmem + lanes + T_DS + c64, ds);
-        tmem_ld_16x16(tmem + lanes + T_QK + c64, qk);
-        tmem_ld_wait();
+        // ---- E2: ds = scale * G * (dO Vn^T); ds2 = ds * (Q K^T) ----
+        ok = ok && WAIT(C_DSQK, ph);
+        if (ok) {
+          tc_fence_after();
+          float ds[16], qk[16];
+          tmem_ld_16x32(tmem + lanes + T_DS + c64, ds);
+          tmem_ld_16x32(tmem + lanes + T_QK + c64, qk);
+          tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          const int col = c64 + 8 * i + cp;
-          const float gc0 = sG[col], gc1 = sG[col + 1];
-          const float a0 = col <= row_a ? p.scale * ds[4 * i] * fast_exp(g_a - gc0) : 0.f;
-          const float a1 = col + 1 <= row_a ? p.scale * ds[4 * i + 1] * fast_exp(g_a - gc1) : 0.f;
-          const float b0 = col <= row_b ? p.scale * ds[4 * i + 2] * fast_exp(g_b - gc0) : 0.f;
-          const float b1 = col + 1 <= row_b ? p.scale * ds[4 * i + 3] * fast_exp(g_b - gc1) : 0.f;
-          st_tile64(OFF_DS, row_a, col, a0, a1);
-          st_tile64(OFF_DS, row_b, col, b0, b1);
-          const float s0 = a0 * qk[4 * i], s1 = a1 * qk[4 * i + 1], s2 = b0 * qk[4 * i + 2], s3 = b1 * qk[4 * i + 3];
-          acc_dg_a += s0 + s1;
-          acc_dg_b += s2 + s3;
-          acc_col[2 * i] += s0 + s2;
-          acc_col[2 * i + 1] += s1 + s3;
-        }
-      }
-      signal(R_DS);
-
-      // ---- E3: dA = strict_lower(beta_c (gamma_c x1 + x2)); A' = A diag(beta), A'' = A diag(beta gamma) ----
-      stamp();
-      ok = ok && WAIT(C_X, ph);
-      stamp();
-      if (ok) {
-        tc_fence_after();
-        float x1[8], x2[8];
-        tmem_ld_16x16(tmem + lanes + T_X1 + c64, x1);
-        tmem_ld_16x16(tmem + lanes + T_X2 + c64, x2);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          const int col = c64 + 8 * i + cp;
-          const float b0 = sBeta[col], b1 = sBeta[col + 1], g0 = sGam[col], g1 = sGam[col + 1];
-          st_tile64(OFF_DA, row_a, col, col < row_a ? b0 * (g0 * x1[4 * i] + x2[4 * i]) : 0.f,
-                    col + 1 < row_a ? b1 * (g1 * x1[4 * i + 1] + x2[4 * i + 1]) : 0.f);
-          st_tile64(OFF_DA, row_b, col, col < row_b ? b0 * (g0 * x1[4 * i + 2] + x2[4 * i + 2]) : 0.f,
-                    col + 1 < row_b ? b1 * (g1 * x1[4 * i + 3] + x2[4 * i + 3]) : 0.f);
-          // rowsum((A^T dw) k)[r] = sum_s A[s][r] x1[s][r], rowsum((A^T du) v)[r] = sum_s A[s][r] x2[s][r]
-          const float2 A_a = ld_bf16x2(reinterpret_cast<const bf16*>(smem + OFF_A + sw128_offset(row_a, col)));
-          const float2 A_b = ld_bf16x2(reinterpret_cast<const bf16*>(smem + OFF_A + sw128_offset(row_b, col)));
-          acc_c1[2 * i] += A_a.x * x1[4 * i] + A_b.x * x1[4 * i + 2];
-          acc_c1[2 * i + 1] += A_a.y * x1[4 * i + 1] + A_b.y * x1[4 * i + 3];
-          acc_c2[2 * i] += A_a.x * x2[4 * i] + A_b.x * x2[4 * i + 2];
-          acc_c2[2 * i + 1] += A_a.y * x2[4 * i + 1] + A_b.y * x2[4 * i + 3];
-          // the v tile is dead (its product is part of this group): A' and A'' go there
-          st_tile64(OFF_V, row_a, col, A_a.x * b0, A_a.y * b1);
-          st_tile64(OFF_V, row_b, col, A_b.x * b0, A_b.y * b1);
-          st_tile64(OFF_V + 8192, row_a, col, A_a.x * b0 * g0, A_a.y * b1 * g1);
-          st_tile64(OFF_V + 8192, row_b, col, A_b.x * b0 * g0, A_b.y * b1 * g1);
-        }
-      }
-      signal(R_DA);
-
-      // ---- E4: dq1 = scale gamma (dO h^T) on the lower lanes, dk1 = rho (Vn dh^T) on the upper ----
-      stamp();
-      ok = ok && WAIT(C_1B, ph);
-      stamp();
-      if (ok) {
-        tc_fence_after();
-        tmem_ld32(tmem + lanes + T_DQ1 + c128, keep);
-        tmem_ld_wait();
-        const unsigned char* tile = smem + (hi ? koff : OFF_Q);
-        float s = 0.f;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const uint4 raw = *reinterpret_cast<const uint4*>(tile + piece(j));
-          const uint32_t* pr = &raw.x;
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float2 t = __bfloat1622float2(*reinterpret_cast<const bf162*>(&pr[e]));
-            keep[8 * j + 2 * e] *= f_w;
-            keep[8 * j + 2 * e + 1] *= f_w;
-            s += t.x * keep[8 * j + 2 * e] + t.y * keep[8 * j + 2 * e + 1];
+          for (int i = 0; i < 4; ++i) {
+            const int col = c64 + 8 * i + cp;
+            const float gc0 = sG[col], gc1 = sG[col + 1];
+            const float a0 = col <= row_a ? p.scale * ds[4 * i] * fast_exp(g_a - gc0) : 0.f;
+            const float a1 = col + 1 <= row_a ? p.scale * ds[4 * i + 1] * fast_exp(g_a - gc1) : 0.f;
+            const float b0 = col <= row_b ? p.scale * ds[4 * i + 2] * fast_exp(g_b - gc0) : 0.f;
+            const float b1 = col + 1 <= row_b ? p.scale * ds[4 * i + 3] * fast_exp(g_b - gc1) : 0.f;
+            st_tile64(OFF_DS, row_a, col, a0, a1);
+            st_tile64(OFF_DS, row_b, col, b0, b1);
+            const float s0 = a0 * qk[4 * i], s1 = a1 * qk[4 * i + 1], s2 = b0 * qk[4 * i + 2], s3 = b1 * qk[4 * i + 3];
+            acc_dg_a += s0 + s1;
+            acc_dg_b += s2 + s3;
+            acc_col[2 * i] += s0 + s2;
+            acc_col[2 * i + 1] += s1 + s3;
           }
         }
-        // dg += rowsum(q dq1) - rowsum(k dk1); the chunk total gets + sum(k dk1)
-        acc_w += hi ? -s : s;
-        if (hi) acc_last += s;
-      }
+        signal(R_DS);
 
-      // ---- E5: T = A^T dA as an operand tile (over dA, which the product has consumed) ----
-      stamp();
-      ok = ok && WAIT(C_T, ph);
-      stamp();
-      if (ok) {
-        tc_fence_after();
-        float t[8];
-        tmem_ld_16x16(tmem + lanes + T_T + c64, t);
-        tmem_ld_wait();
+        // ---- E3: dA = strict_lower(beta_c (gamma_c x1 + x2)); A' = A diag(beta), A'' = A diag(beta gamma) ----
+        ok = ok && WAIT(C_X, ph);
+        if (ok) {
+          tc_fence_after();
+          float x1[16], x2[16];
+          tmem_ld_16x32(tmem + lanes + T_X1 + c64, x1);
+          tmem_ld_16x32(tmem + lanes + T_X2 + c64, x2);
+          tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          const int col = c64 + 8 * i + cp;
-          st_tile64(OFF_DA, row_a, col, t[4 * i], t[4 * i + 1]);
-          st_tile64(OFF_DA, row_b, col, t[4 * i + 2], t[4 * i + 3]);
+          for (int i = 0; i < 4; ++i) {
+            const int col = c64 + 8 * i + cp;
+            const float b0 = sBeta[col], b1 = sBeta[col + 1], g0 = sGam[col], g1 = sGam[col + 1];
+            st_tile64(OFF_DA, row_a, col, col < row_a ? b0 * (g0 * x1[4 * i] + x2[4 * i]) : 0.f,
+                      col + 1 < row_a ? b1 * (g1 * x1[4 * i + 1] + x2[4 * i + 1]) : 0.f);
+            st_tile64(OFF_DA, row_b, col, col < row_b ? b0 * (g0 * x1[4 * i + 2] + x2[4 * i + 2]) : 0.f,
+                      col + 1 < row_b ? b1 * (g1 * x1[4 * i + 3] + x2[4 * i + 3]) : 0.f);
+            // rowsum((A^T dw) k)[r] = sum_s A[s][r] x1[s][r], rowsum((A^T du) v)[r] = sum_s A[s][r] x2[s][r]
+            const float2 A_a = ld_bf16x2(reinterpret_cast<const bf16*>(smem + OFF_A + sw128_offset(row_a, col)));
+            const float2 A_b = ld_bf16x2(reinterpret_cast<const bf16*>(smem + OFF_A + sw128_offset(row_b, col)));
+            acc_c1[2 * i] += A_a.x * x1[4 * i] + A_b.x * x1[4 * i + 2];
+            acc_c1[2 * i + 1] += A_a.y * x1[4 * i + 1] + A_b.y * x1[4 * i + 3];
+            acc_c2[2 * i] += A_a.x * x2[4 * i] + A_b.x * x2[4 * i + 2];
+            acc_c2[2 * i + 1] += A_a.y * x2[4 * i + 1] + A_b.y * x2[4 * i + 3];
+            // the v tile is dead (its product is part of this group): A' and A'' go there
+            st_tile64(OFF_V, row_a, col, A_a.x * b0, A_a.y * b1);
+            st_tile64(OFF_V, row_b, col, A_b.x * b0, A_b.y * b1);
+            st_tile64(OFF_V + 8192, row_a, col, A_a.x * b0 * g0, A_a.y * b1 * g1);
+            st_tile64(OFF_V + 8192, row_b, col, A_b.x * b0 * g0, A_b.y * b1 * g1);
+          }
         }
-      }
-      signal(R_T);
+        signal(R_DA);
 
-      // ---- E6: dv = A'^T du (upper lanes), already row-scaled by beta ----
-      stamp();
-      ok = ok && WAIT(C_2B, ph);
-      stamp();
-      if (ok) {
-        tc_fence_after();
-        float x[32];
-        tmem_ld32(tmem + lanes + (T_T2 & 0xFFFFu) + c128, x);
-        tmem_ld_wait();
-        if (hi && wr_w) {
+        // ---- E5: T = A^T dA as an operand tile (over dA, which the product has consumed) ----
+        ok = ok && WAIT(C_T, ph);
+        if (ok) {
+          tc_fence_after();
+          float t[16];
+          tmem_ld_16x32(tmem + lanes + T_T + c64, t);
+          tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(p.dv + out_w + 8 * j) = pack8(x + 8 * j);
+          for (int i = 0; i < 4; ++i) {
+            const int col = c64 + 8 * i + cp;
+            st_tile64(OFF_DA, row_a, col, t[4 * i], t[4 * i + 1]);
+            st_tile64(OFF_DA, row_b, col, t[4 * i + 2], t[4 * i + 3]);
+          }
         }
-      }
-      signal(R_E6);
+        signal(R_T);
 
-      // ---- E7: beta dA3 = -beta G d3 (over ds) as an operand tile; its dg and db terms ----
-      stamp();
-      ok = ok && WAIT(C_D3, ph);
-      stamp();
-      if (ok) {
-        tc_fence_after();
-        float d3[8], kk[8];
-        tmem_ld_16x16(tmem + lanes + T_D3 + c64, d3);
-        tmem_ld_16x16(tmem + lanes + T_KK + c64, kk);
-        tmem_ld_wait();
+        // ---- E7: beta dA3 = -beta G d3 (over ds) as an operand tile; its dg and db terms ----
+        ok = ok && WAIT(C_D3, ph);
+        if (ok) {
+          tc_fence_after();
+          float d3[16], kk[16];
+          tmem_ld_16x32(tmem + lanes + T_D3 + c64, d3);
+          tmem_ld_16x32(tmem + lanes + T_KK + c64, kk);
+          tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          const int col = c64 + 8 * i + cp;
-          const float gc0 = sG[col], gc1 = sG[col + 1];
-          const float a0 = col < row_a ? -d3[4 * i] * fast_exp(g_a - gc0) : 0.f;
-          const float a1 = col + 1 < row_a ? -d3[4 * i + 1] * fast_exp(g_a - gc1) : 0.f;
-          const float b0 = col < row_b ? -d3[4 * i + 2] * fast_exp(g_b - gc0) : 0.f;
-          const float b1 = col + 1 < row_b ? -d3[4 * i + 3] * fast_exp(g_b - gc1) : 0.f;
-          st_tile64(OFF_DS, row_a, col, beta_a * a0, beta_a * a1);
-          st_tile64(OFF_DS, row_b, col, beta_b * b0, beta_b * b1);
-          // db += rowsum((dA3 K) k) = rowsum(dA3 * (K K^T)); the dg terms carry the beta factor
-          const float u0 = a0 * kk[4 * i], u1 = a1 * kk[4 * i + 1], u2 = b0 * kk[4 * i + 2], u3 = b1 * kk[4 * i + 3];
-          acc_db_a += u0 + u1;
-          acc_db_b += u2 + u3;
-          const float s0 = u0 * beta_a, s1 = u1 * beta_a, s2 = u2 * beta_b, s3 = u3 * beta_b;
-          acc_dg_a += s0 + s1;
-          acc_dg_b += s2 + s3;
-          acc_col[2 * i] += s0 + s2;
-          acc_col[2 * i + 1] += s1 + s3;
+          for (int i = 0; i < 4; ++i) {
+            const int col = c64 + 8 * i + cp;
+            const float gc0 = sG[col], gc1 = sG[col + 1];
+            const float a0 = col < row_a ? -d3[4 * i] * fast_exp(g_a - gc0) : 0.f;
+            const float a1 = col + 1 < row_a ? -d3[4 * i + 1] * fast_exp(g_a - gc1) : 0.f;
+            const float b0 = col < row_b ? -d3[4 * i + 2] * fast_exp(g_b - gc0) : 0.f;
+            const float b1 = col + 1 < row_b ? -d3[4 * i + 3] * fast_exp(g_b - gc1) : 0.f;
+            st_tile64(OFF_DS, row_a, col, beta_a * a0, beta_a * a1);
+            st_tile64(OFF_DS, row_b, col, beta_b * b0, beta_b * b1);
+            // db += rowsum((dA3 K) k) = rowsum(dA3 * (K K^T)); the dg terms carry the beta factor
+            const float u0 = a0 * kk[4 * i], u1 = a1 * kk[4 * i + 1], u2 = b0 * kk[4 * i + 2], u3 = b1 * kk[4 * i + 3];
+            acc_db_a += u0 + u1;
+            acc_db_b += u2 + u3;
+            const float s0 = u0 * beta_a, s1 = u1 * beta_a, s2 = u2 * beta_b, s3 = u3 * beta_b;
+            acc_dg_a += s0 + s1;
+            acc_dg_b += s2 + s3;
+            acc_col[2 * i] += s0 + s2;
+            acc_col[2 * i + 1] += s1 + s3;
+          }
         }
-      }
-      signal(R_D3);
-
-      // ---- E8: dq = dq1 + ds K (lower lanes); dk = dk1 + [ds^T q + A''^T dw + (beta dA3) K + (beta dA3)^T K] (upper) ----
-      stamp();
-      ok = ok && WAIT(C_5, ph);
-      stamp();
-      if (ok) {
-        tc_fence_after();
-        float x[32];
-        tmem_ld32(tmem + lanes + T_DQ2 + c128, x);
-        tmem_ld_wait();
+        signal(R_D3);
+        signal(R_END);  // this group no longer touches the accumulators or the tiles of the item
+        // one reduction per quantity, one plain store per (warp, row or column): no atomics
+        acc_dg_a = quad_sum(acc_dg_a);
+        acc_dg_b = quad_sum(acc_dg_b);
+        acc_db_a = quad_sum(acc_db_a);
+        acc_db_b = quad_sum(acc_db_b);
+        if ((lane & 3) == 0) {
+          sRowDg[half * 64 + row_a] = acc_dg_a;
+          sRowDg[half * 64 + row_b] = acc_dg_b;
+          sRowDb[half * 64 + row_a] = acc_db_a;
+          sRowDb[half * 64 + row_b] = acc_db_b;
+        }
 #pragma unroll
-        for (int j = 0; j < 32; ++j) x[j] += keep[j];
-        if (wr_w) {
+        for (int j = 0; j < 8; ++j) {
+          const float c = col_sum(acc_col[j]);
+          const float c1 = col_sum(acc_c1[j]), c2 = col_sum(acc_c2[j]);
+          if (lane < 4) {
+            const int col = c64 + 8 * (j >> 1) + cp + (j & 1);
+            sColDg[qd * 64 + col] = c;
+            sColC1[qd * 64 + col] = c1;
+            sColC2[qd * 64 + col] = c2;
+          }
+        }
+      } else {
+        // ===================== bulk group =====================
+        // gamma_last * sum(h * dh) over the whole 128 x 128 tiles (plain shared-memory reads)
+        if (ok) {
+          float hd = 0.f;
+          for (int i = tid - N_EPI / 2; i < SQ_TILE / 16; i += N_EPI / 2) {
+            const uint4 a = *reinterpret_cast<const uint4*>(smem + OFF_H + i * 16);
+            const uint4 b = *reinterpret_cast<const uint4*>(smem + OFF_DH + i * 16);
+            const uint32_t* pa = &a.x;
+            const uint32_t* pb = &b.x;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              float2 fa = __bfloat1622float2(*reinterpret_cast<const bf162*>(&pa[e]));
+              float2 fb = __bfloat1622float2(*reinterpret_cast<const bf162*>(&pb[e]));
+              hd += fa.x * fb.x + fa.y * fb.y;
+            }
+          }
+          acc_last += sGam[CHUNK - 1] * hd;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars[R_HD]);
+        const float f_w = hi ? sRho[row_w] : p.scale * sGam[row_w];
+        const long long out_w = ((cur.row0 + row_w) * p.Hv + cur.hv) * D + c128;
+        const bool wr_w = row_w < valid;
+        float acc_w = 0.f;
+
+        // ---- E4: dq1 = scale gamma (dO h^T) on the lower lanes, dk1 = rho (Vn dh^T) on the upper;
+        //      scaled in place (written back to tensor memory), with their dg terms ----
+        ok = ok && WAIT(C_1B, ph);
+        if (ok) {
+          tc_fence_after();
+          const unsigned char* tile = smem + (hi ? koff : OFF_Q);
+#pragma unroll 1
+          for (int pass = 0; pass < 2; ++pass) {
+            float x[32];
+            tmem_ld32(tmem + lanes + T_DQ1 + c128 + 32 * pass, x);
+            tmem_ld_wait();
+            float s = 0.f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint4 raw = *reinterpret_cast<const uint4*>(tile + piece(pass, j));
+              const uint32_t* pr = &raw.x;
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 t = __bfloat1622float2(*reinterpret_cast<const bf162*>(&pr[e]));
+                x[8 * j + 2 * e] *= f_w;
+                x[8 * j + 2 * e + 1] *= f_w;
+                s += t.x * x[8 * j + 2 * e] + t.y * x[8 * j + 2 * e + 1];
+              }
+            }
+            tmem_st32(tmem + lanes + T_DQ1 + c128 + 32 * pass, x);
+            // dg += rowsum(q dq1) - rowsum(k dk1); the chunk total gets + sum(k dk1)
+            acc_w += hi ? -s : s;
+            if (hi) acc_last += s;
+          }
+          tmem_st_wait();
+        }
+        signal(R_E4);  // q (and this item's k for this group) are no longer read from shared memory
+
+        // ---- E6: dv = A'^T du (upper lanes), already row-scaled by beta ----
+        ok = ok && WAIT(C_2B, ph);
+        if (ok) {
+          tc_fence_after();
+#pragma unroll 1
+          for (int pass = 0; pass < 2; ++pass) {
+            float x[32];
+            tmem_ld32(tmem + lanes + (T_T2 & 0xFFFFu) + c128 + 32 * pass, x);
+            tmem_ld_wait();
+            if (hi && wr_w) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(p.dv + out_w + 32 * pass + 8 * j) = pack8(x + 8 * j);
+            }
+          }
+        }
+
+        // ---- E8: dq = dq1 + ds K (lower lanes); dk = dk1 + [ds^T q + A''^T dw + (beta dA3) K + (beta dA3)^T K] ----
+        ok = ok && WAIT(C_5, ph);
+        if (ok) {
+          tc_fence_after();
           bf16* out = hi ? p.dk : p.dq;
+#pragma unroll 1
+          for (int pass = 0; pass < 2; ++pass) {
+            float x[32], y[32];
+            tmem_ld32(tmem + lanes + T_DQ1 + c128 + 32 * pass, x);
+            tmem_ld32(tmem + lanes + T_DQ2 + c128 + 32 * pass, y);
+            tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(out + out_w + 8 * j) = pack8(x + 8 * j);
+            for (int j = 0; j < 32; ++j) x[j] += y[j];
+            if (wr_w) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(out + out_w + 32 * pass + 8 * j) = pack8(x + 8 * j);
+            }
+          }
         }
-      }
-      stamp();
-      signal(R_END);  // accumulators and k of this item are free
-      // one reduction per quantity, one plain store per (warp, row or column): no atomics
-      acc_dg_a = quad_sum(acc_dg_a);
-      acc_dg_b = quad_sum(acc_dg_b);
-      acc_db_a = quad_sum(acc_db_a);
-      acc_db_b = quad_sum(acc_db_b);
-      if ((lane & 3) == 0) {
-        sRowDg[cq * 64 + row_a] = acc_dg_a;
-        sRowDg[cq * 64 + row_b] = acc_dg_b;
-        sRowDb[cq * 64 + row_a] = acc_db_a;
-        sRowDb[cq * 64 + row_b] = acc_db_b;
-      }
-      sRowW[(2 * cq + (hi ? 1 : 0)) * 64 + row_w] = acc_w;
+        signal(R_END);  // accumulators and k of this item are free
+        sRowW[(2 * half + (hi ? 1 : 0)) * 64 + row_w] = acc_w;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float c = col_sum(acc_col[j]);
-        const float c1 = col_sum(acc_c1[j]), c2 = col_sum(acc_c2[j]);
-        if (lane < 4) {
-          const int col = c64 + 8 * (j >> 1) + cp + (j & 1);
-          sColDg[qd * 64 + col] = c;
-          sColC1[qd * 64 + col] = c1;
-          sColC2[qd * 64 + col] = c2;
-        }
+        for (int d = 16; d > 0; d >>= 1) acc_last += __shfl_xor_sync(0xffffffffu, acc_last, d);
+        if (lane == 0) sLast[gw] = acc_last;
       }
-#pragma unroll
-      for (int d = 16; d > 0; d >>= 1) acc_last += __shfl_xor_sync(0xffffffffu, acc_last, d);
-      if (lane == 0) sLast[warp] = acc_last;
       if (!ok) *abort_flag = 1;
       epi_barrier();  // every contribution to dg, db is in
       if (tid == 0 && *abort_flag) *stop_flag = 1;
@@ -712,16 +722,17 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
         float dgv = 0.f, dbv = 0.f, c1 = 0.f, c2 = 0.f;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          dgv += sRowDg[j * 64 + tid] - sColDg[j * 64 + tid] + sRowW[2 * j * 64 + tid] + sRowW[(2 * j + 1) * 64 + tid];
-          dbv += sRowDb[j * 64 + tid];
+          dgv += sRowW[j * 64 + tid] - sColDg[j * 64 + tid];
           c1 += sColC1[j * 64 + tid];
           c2 += sColC2[j * 64 + tid];
         }
+        dgv += sRowDg[tid] + sRowDg[64 + tid];
+        dbv += sRowDb[tid] + sRowDb[64 + tid];
         dbv += sGam[tid] * c1 + c2;
         dgv += sBeta[tid] * sGam[tid] * c1;
         if (tid == valid - 1) {
 #pragma unroll
-          for (int j = 0; j < N_EPI / 32; ++j) dgv += sLast[j];
+          for (int j = 0; j < 8; ++j) dgv += sLast[j];
         }
         p.dg[(cur.row0 + tid) * p.Hv + cur.hv] = dgv;
         p.db[(cur.row0 + tid) * p.Hv + cur.hv] = dbv;
