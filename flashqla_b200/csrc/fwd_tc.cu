@@ -516,7 +516,6 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
           if (!ok) break;
           tc_fence_after();
           issue_u_w(0);
-          if constexpr (!NO_O) issue_p(0);
         }
         ok = WAIT(S_COPY, it & 1) && WAIT(W_READY, it & 1);
         if (!ok) break;
@@ -544,6 +543,10 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
           SEC_BEGIN();
           // O1 = Q S      (B = S^T copy: N = v rows, K = k)
           umma_group<8, 2, 512, 2, 1024, false>(tmem + TM_O1, q0_lo + so, st_lo, ID_O);
+          // P of this chunk goes here, into the time the value group needs for Vn: the output
+          // group turns it into Pg while the state update runs (it read P of the chunk before
+          // ahead of the output product issued at the end of the previous iteration)
+          issue_p(so);
           SEC_END(SEC_B);
         }
         ok = WAIT(VR_READY, it & 1) && WAIT(S_DEC, it & 1);
@@ -554,7 +557,7 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
         umma_group<4, 2, 0, 128, 0, true>(tmem + TM_S, vrt_lo, kmn0_lo + so, ID_S);
         if constexpr (EXTRA) tma_store_wait_read();  // the S^T tile may be rewritten after this
         umma_commit(&bars[S_DONE]);
-        if constexpr (NO_O) umma_commit(&bars[EMPTY0 + s]);  // last product that reads this stage
+        umma_commit(&bars[EMPTY0 + s]);  // last product that reads this stage
         SEC_END(SEC_C);
         if (it + 1 < n_it) {
           ok = WAIT(FULL0 + (s ^ 1), ((it + 1) >> 1) & 1) && WAIT(AP_READY, (it + 1) & 1) &&
@@ -577,8 +580,6 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
           // O2 = Pg Vn     (B = Vn^T copy: N = v rows, K = tok')
           umma_group<4, 2, 0, 2, 0, false>(tmem + TM_O2, p_lo, vnt_lo, ID_O);
           umma_commit(&bars[O_DONE]);
-          umma_commit(&bars[EMPTY0 + s]);
-          if (it + 1 < n_it) issue_p(so_next);
           SEC_END(SEC_E);
         }
       }
