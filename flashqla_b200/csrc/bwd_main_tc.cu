@@ -274,7 +274,12 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
         const uint32_t k_lo = k_lo0 + (ph ? KBUF_LO : 0u), kmn_lo = kmn_lo0 + (ph ? KBUF_LO : 0u);
         // the read-out warps have finished the previous item (accumulators free) and have zeroed
         // the rows past the sequence end in this item's tiles (which also means: tiles landed)
-        ok = (it == 0 || WAIT(R_END, (it - 1) & 1)) && WAIT(R_ZERO, ph);
+        // A full chunk needs no zero fill: its first products start as soon as its tiles have
+        // landed, while the bulk group still finishes the previous item (the accumulators they
+        // write were last read by the chain group, whose R_D3 this thread has seen; dq1 | dk1 come
+        // after R_DW of this item, which the read-out warps only give after the previous item).
+        if (cur.valid == CHUNK) ok = WAIT(L_A, ph) && WAIT(L_B, ph);
+        else ok = (it == 0 || WAIT(R_END, (it - 1) & 1)) && WAIT(R_ZERO, ph);
         if (!ok) break;
         tc_fence_after();
         // ---- products that need only loaded tiles ----
