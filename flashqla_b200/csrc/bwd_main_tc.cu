@@ -404,6 +404,36 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
     auto pack8 = [&](const float* x) {
       return make_uint4(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]), pack_bf16(x[4], x[5]), pack_bf16(x[6], x[7]));
     };
+    // 32 consecutive columns of this thread's output row (x, fp32) go out as bf16. A thread owns a
+    // row, so a plain 16-byte store per thread would touch 32 lines per instruction; the four
+    // lanes of a quad first exchange their 16-byte pieces (a 4 x 4 transpose, two butterfly
+    // steps), after which each store instruction writes 64 contiguous bytes of 8 rows.
+    // base = offset of the row of lane 0 of the quad (+ the 32-column block), row_q = that row.
+    auto store_rows = [&](bf16* out, long long base, int row_q, int valid_rows, const float* x) {  // whole warp
+      uint4 pc[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) pc[j] = pack8(x + 8 * j);
+      const bool b0 = lane & 1, b1 = lane & 2;
+      auto xchg = [&](uint4& keep_if0, uint4& keep_if1, bool bit, int mask) {
+        // lanes with bit clear keep keep_if0 and send keep_if1; lanes with bit set the reverse
+        uint4 snd = bit ? keep_if0 : keep_if1, rcv;
+        rcv.x = __shfl_xor_sync(0xffffffffu, snd.x, mask);
+        rcv.y = __shfl_xor_sync(0xffffffffu, snd.y, mask);
+        rcv.z = __shfl_xor_sync(0xffffffffu, snd.z, mask);
+        rcv.w = __shfl_xor_sync(0xffffffffu, snd.w, mask);
+        if (bit) keep_if0 = rcv; else keep_if1 = rcv;
+      };
+      xchg(pc[0], pc[1], b0, 1);
+      xchg(pc[2], pc[3], b0, 1);
+      xchg(pc[0], pc[2], b1, 2);
+      xchg(pc[1], pc[3], b1, 2);
+      // pc[j] now holds piece (lane & 3) of row row_q + j
+      const long long pitch = (long long)p.Hv * D;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (row_q + j < valid_rows)
+          *reinterpret_cast<uint4*>(out + base + j * pitch + 8 * (lane & 3)) = pc[j];
+    };
     // this warp's part of a tile (or of the accumulators) is done: tell the issue warp
     auto signal = [&](int bar) {
       fence_proxy_async();
@@ -469,9 +499,9 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
         // row sums (dg, db) and column sums (dg; the two column terms that come from A^T dw and
         // A^T du) of this thread; reduced across lanes once, at the end of the item
         float acc_dg_a = 0.f, acc_dg_b = 0.f, acc_db_a = 0.f, acc_db_b = 0.f;
-        float acc_col[8], acc_c1[8], acc_c2[8];
+        float acc_col[8], acc_dbc[8];  // per column: dg terms (to subtract), db terms
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc_col[j] = acc_c1[j] = acc_c2[j] = 0.f;
+        for (int j = 0; j < 8; ++j) acc_col[j] = acc_dbc[j] = 0.f;
 
         // ---- E1: dw = -du h^T as an operand tile (lower lanes of the 32-lane shape) ----
         ok = ok && WAIT(C_DW, ph);
@@ -538,10 +568,14 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
             // rowsum((A^T dw) k)[r] = sum_s A[s][r] x1[s][r], rowsum((A^T du) v)[r] = sum_s A[s][r] x2[s][r]
             const float2 A_a = ld_bf16x2(reinterpret_cast<const bf16*>(smem + OFF_A + sw128_offset(row_a, col)));
             const float2 A_b = ld_bf16x2(reinterpret_cast<const bf16*>(smem + OFF_A + sw128_offset(row_b, col)));
-            acc_c1[2 * i] += A_a.x * x1[4 * i] + A_b.x * x1[4 * i + 2];
-            acc_c1[2 * i + 1] += A_a.y * x1[4 * i + 1] + A_b.y * x1[4 * i + 3];
-            acc_c2[2 * i] += A_a.x * x2[4 * i] + A_b.x * x2[4 * i + 2];
-            acc_c2[2 * i + 1] += A_a.y * x2[4 * i + 1] + A_b.y * x2[4 * i + 3];
+            // column r: db += gamma_r c1 + c2, dg += beta_r gamma_r c1 (entered with a minus sign
+            // into the column sums, which the final step subtracts)
+            const float c1a = A_a.x * x1[4 * i] + A_b.x * x1[4 * i + 2];
+            const float c1b = A_a.y * x1[4 * i + 1] + A_b.y * x1[4 * i + 3];
+            acc_dbc[2 * i] += g0 * c1a + A_a.x * x2[4 * i] + A_b.x * x2[4 * i + 2];
+            acc_dbc[2 * i + 1] += g1 * c1b + A_a.y * x2[4 * i + 1] + A_b.y * x2[4 * i + 3];
+            acc_col[2 * i] -= b0 * g0 * c1a;
+            acc_col[2 * i + 1] -= b1 * g1 * c1b;
             // the v tile is dead (its product is part of this group): A' and A'' go there
             st_tile64(OFF_V, row_a, col, A_a.x * b0, A_a.y * b1);
             st_tile64(OFF_V, row_b, col, A_b.x * b0, A_b.y * b1);
@@ -612,12 +646,11 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const float c = col_sum(acc_col[j]);
-          const float c1 = col_sum(acc_c1[j]), c2 = col_sum(acc_c2[j]);
+          const float c1 = col_sum(acc_dbc[j]);
           if (lane < 4) {
             const int col = c64 + 8 * (j >> 1) + cp + (j & 1);
             sColDg[qd * 64 + col] = c;
             sColC1[qd * 64 + col] = c1;
-            sColC2[qd * 64 + col] = c2;
           }
         }
       } else {
@@ -642,8 +675,8 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars[R_HD]);
         const float f_w = hi ? sRho[row_w] : p.scale * sGam[row_w];
-        const long long out_w = ((cur.row0 + row_w) * p.Hv + cur.hv) * D + c128;
-        const bool wr_w = row_w < valid;
+        const int row_q = row_w - (lane & 3);  // row of lane 0 of this quad
+        const long long out_q = ((cur.row0 + row_q) * p.Hv + cur.hv) * D + c128;
         float acc_w = 0.f;
 
         // ---- E4: dq1 = scale gamma (dO h^T) on the lower lanes, dk1 = rho (Vn dh^T) on the upper;
@@ -688,10 +721,7 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
             float x[32];
             tmem_ld32(tmem + lanes + (T_T2 & 0xFFFFu) + c128 + 32 * pass, x);
             tmem_ld_wait();
-            if (hi && wr_w) {
-#pragma unroll
-              for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(p.dv + out_w + 32 * pass + 8 * j) = pack8(x + 8 * j);
-            }
+            store_rows(p.dv, out_q + 32 * pass, row_q, hi ? valid : 0, x);  // dv sits on the upper lanes
           }
         }
 
@@ -708,10 +738,7 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
             tmem_ld_wait();
 #pragma unroll
             for (int j = 0; j < 32; ++j) x[j] += y[j];
-            if (wr_w) {
-#pragma unroll
-              for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(out + out_w + 32 * pass + 8 * j) = pack8(x + 8 * j);
-            }
+            store_rows(out, out_q + 32 * pass, row_q, valid, x);
           }
         }
         signal(R_END);  // accumulators and k of this item are free
@@ -724,17 +751,14 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
       epi_barrier();  // every contribution to dg, db is in
       if (tid == 0 && *abort_flag) *stop_flag = 1;
       if (tid < valid) {
-        float dgv = 0.f, dbv = 0.f, c1 = 0.f, c2 = 0.f;
+        float dgv = 0.f, dbv = 0.f;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           dgv += sRowW[j * 64 + tid] - sColDg[j * 64 + tid];
-          c1 += sColC1[j * 64 + tid];
-          c2 += sColC2[j * 64 + tid];
+          dbv += sColC1[j * 64 + tid];
         }
         dgv += sRowDg[tid] + sRowDg[64 + tid];
         dbv += sRowDb[tid] + sRowDb[64 + tid];
-        dbv += sGam[tid] * c1 + c2;
-        dgv += sBeta[tid] * sGam[tid] * c1;
         if (tid == valid - 1) {
 #pragma unroll
           for (int j = 0; j < 8; ++j) dgv += sLast[j];

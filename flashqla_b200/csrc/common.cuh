@@ -107,6 +107,22 @@ __device__ __forceinline__ float2 ld_bf16x2(const bf16* p) {
   return __bfloat1622float2(*reinterpret_cast<const bf162*>(p));
 }
 
+// 4 x 4 transpose of 32-bit words across the four lanes of a quad (lanes 4n .. 4n+3): on return
+// w[m] of lane j holds what w[j] of lane m held.  Two butterfly steps, four shuffles; the whole
+// warp must call it.
+__device__ __forceinline__ void quad_transpose(uint32_t* w, int lane) {
+  const bool b0 = lane & 1, b1 = lane & 2;
+  uint32_t r;
+  r = __shfl_xor_sync(0xffffffffu, b0 ? w[0] : w[1], 1);
+  if (b0) w[0] = r; else w[1] = r;
+  r = __shfl_xor_sync(0xffffffffu, b0 ? w[2] : w[3], 1);
+  if (b0) w[2] = r; else w[3] = r;
+  r = __shfl_xor_sync(0xffffffffu, b1 ? w[0] : w[2], 2);
+  if (b1) w[0] = r; else w[2] = r;
+  r = __shfl_xor_sync(0xffffffffu, b1 ? w[1] : w[3], 2);
+  if (b1) w[1] = r; else w[3] = r;
+}
+
 // ---- warp-level tile GEMM on shared-memory operands -----------------------------------------
 // acc[mt][nt] (+)= op(A) * op(B) for a warp tile of (MT*16) x (NT*8), reduction length KT*16.
 //   A_TRANS = false: A is stored [m][k] (row stride lda), `As` points at (m0, 0).

@@ -401,14 +401,25 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
           tc_fence_before();
           mbar_arrive(&bars[O_FREE]);
         }
+        // A lane holds one column pair of every group of 8 columns; the four lanes of a quad
+        // (same rows) exchange words (4 x 4 transposes, two butterfly steps each) so that each
+        // lane ends up with 8 consecutive columns: a store instruction then writes 64 contiguous
+        // bytes of 8 rows instead of 16 bytes of 8 rows.
+        uint32_t wa[8], wb[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
+          wa[i] = pack_bf16(sg_a * a[4 * i] + b[4 * i], sg_a * a[4 * i + 1] + b[4 * i + 1]);
+          wb[i] = pack_bf16(sg_b * a[4 * i + 2] + b[4 * i + 2], sg_b * a[4 * i + 3] + b[4 * i + 3]);
+        }
+#pragma unroll
+        for (int h4 = 0; h4 < 8; h4 += 4) {
+          quad_transpose(wa + h4, lane);
+          quad_transpose(wb + h4, lane);
+          // lane j of the quad now holds columns c0 + 8 h4 + 8 j .. + 7 (o_a, o_b include 2 j)
           if (wr_a)
-            *reinterpret_cast<uint32_t*>(o_a + c0 + 8 * i) =
-                pack_bf16(sg_a * a[4 * i] + b[4 * i], sg_a * a[4 * i + 1] + b[4 * i + 1]);
+            *reinterpret_cast<uint4*>(o_a + c0 + 8 * h4 + 3 * cp) = make_uint4(wa[h4], wa[h4 + 1], wa[h4 + 2], wa[h4 + 3]);
           if (wr_b)
-            *reinterpret_cast<uint32_t*>(o_b + c0 + 8 * i) =
-                pack_bf16(sg_b * a[4 * i + 2] + b[4 * i + 2], sg_b * a[4 * i + 3] + b[4 * i + 3]);
+            *reinterpret_cast<uint4*>(o_b + c0 + 8 * h4 + 3 * cp) = make_uint4(wb[h4], wb[h4 + 1], wb[h4 + 2], wb[h4 + 3]);
         }
       }
     };
