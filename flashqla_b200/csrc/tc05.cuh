@@ -80,6 +80,8 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
                                           volatile int* abort_flag, uint32_t budget = 2000) {
   if (mbar_test_wait(bar, parity)) return true;  // fast path: the phase is already complete
+  // not unrolled: a kernel has dozens of wait sites and is larger than the instruction cache
+#pragma unroll 1
   for (uint32_t i = 0; i < budget; ++i) {
     if (mbar_try_wait(bar, parity, 1000000u)) return true;
     if (*abort_flag) return false;
