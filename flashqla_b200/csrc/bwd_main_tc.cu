@@ -139,17 +139,16 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + OFF_MISC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + OFF_MISC + 4);
-  volatile int* stop_flag = reinterpret_cast<volatile int*>(smem + OFF_MISC + 8);
-  float* sG = reinterpret_cast<float*>(smem + OFF_VEC);
-  float* sGam = sG + 64;
-  float* sRho = sGam + 64;
-  float* sBeta = sRho + 64;
-  float* sRowDg = sBeta + 64;
+  volatile int* stop_flag = reinterpret_cast<volatile int*>(smem + OFF_MISC + 8);  // [2], by item parity
+  // per-row vectors g, gamma, rho, beta of an item: two buffers (item parity), the second one
+  // behind the column sums
+  float* sVec0 = reinterpret_cast<float*>(smem + OFF_VEC);
+  float* sRowDg = sVec0 + 256;
   float* sColDg = sRowDg + 256;
   float* sRowDb = sColDg + 256;
   float* sColC1 = sRowDb + 256;
-  float* sColC2 = sColC1 + 256;
-  float* sRowW = sColC2 + 256;  // row terms of the 128-wide steps: [column quarter x lane half][row]
+  float* sVec1 = sColC1 + 256;
+  float* sRowW = sVec1 + 256;  // row terms of the 128-wide steps: [column quarter x lane half][row]
   float* sLast = sRowW + 512;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -187,7 +186,8 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
     mbar_init(&bars[R_END], N_EPI / 32);
     for (int i = R_DW; i <= R_E4; ++i) mbar_init(&bars[i], N_EPI / 64);
     *abort_flag = 0;
-    *stop_flag = 0;
+    stop_flag[0] = 0;
+    stop_flag[1] = 0;
     fence_mbar_init();
   }
   if (warp == 0) tmem_alloc(tmem_slot, 512);
@@ -344,9 +344,14 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
         tc_fence_after();
         umma_group<4, 2, 0, 2, 0, false>(tmem + T_D3, da_lo, a_lo, ID_KK_64);
         umma_commit(&bars[C_D3]);
+        // The bulk group is past its first read-out (always waited for: its threads combine the
+        // partial sums of the previous item before that, and the last products of this item let
+        // the group overwrite those sums).
+        ok = WAIT(R_E4, ph);
+        if (!ok) break;
         if (has_next) {
           // du, q, v are dead once their products are complete and the bulk group has used q
-          ok = WAIT(C_2B, ph) && WAIT(R_E4, ph);
+          ok = WAIT(C_2B, ph);
           if (!ok) break;
           load_b(nxt);
           ok = WAIT(C_D3, ph);  // last product that reads A
@@ -448,18 +453,59 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
           *reinterpret_cast<uint4*>(base + (valid + (i >> 3)) * 128 + ((i & 7) << 4)) = make_uint4(0, 0, 0, 0);
       }
     };
-    float pre_g = 0.f, pre_gl = 0.f, pre_beta = 0.f;
+    // The vectors of the next item are fetched a whole item ahead.  beta stays in its raw form
+    // until it is used: a conversion right behind the load would make the thread wait for it.
+    float pre_g = 0.f, pre_gl = 0.f;
+    uint32_t pre_beta_raw = 0;
     auto fetch_vectors = [&](const Item& t) {
       if (tid < CHUNK) {
         const int r = min(tid, t.valid - 1);
-        pre_g = p.g[(t.row0 + r) * p.Hv + t.hv];
+        const long long i = (t.row0 + r) * p.Hv + t.hv;
+        pre_g = p.g[i];
         pre_gl = p.g[(t.row0 + t.valid - 1) * p.Hv + t.hv];
-        pre_beta = tid < t.valid ? load_beta(p.beta, p.beta_is_f32, (t.row0 + tid) * p.Hv + t.hv) : 0.f;
+        pre_beta_raw = p.beta_is_f32 ? reinterpret_cast<const uint32_t*>(p.beta)[i]
+                                     : (uint32_t)reinterpret_cast<const unsigned short*>(p.beta)[i];
+      }
+    };
+    // the fetched vectors of item t go to buffer `buf` (threads 0..63; published by a barrier)
+    auto write_vectors = [&](const Item& t, float* buf) {
+      if (tid < CHUNK) {
+        buf[tid] = pre_g;
+        buf[64 + tid] = fast_exp(pre_g);
+        buf[128 + tid] = fast_exp(pre_gl - pre_g);
+        buf[192 + tid] =
+            tid < t.valid ? __uint_as_float(p.beta_is_f32 ? pre_beta_raw : pre_beta_raw << 16) : 0.f;
+      }
+    };
+    // dg, db of a finished item from the partial sums in shared memory (threads 256..319, which
+    // would otherwise idle until the first wide products are complete)
+    auto combine = [&](long long first, int n_rows) {  // first = row0 * Hv + hv of the item
+      const int r = tid - N_EPI / 2;
+      if (r >= 0 && r < n_rows) {
+        float dgv = 0.f, dbv = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          dgv += sRowW[j * 64 + r] - sColDg[j * 64 + r];
+          dbv += sColC1[j * 64 + r];
+        }
+        dgv += sRowDg[r] + sRowDg[64 + r];
+        dbv += sRowDb[r] + sRowDb[64 + r];
+        if (r == n_rows - 1) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) dgv += sLast[j];
+        }
+        p.dg[first + (long long)r * p.Hv] = dgv;
+        p.db[first + (long long)r * p.Hv] = dbv;
       }
     };
     Item cur = decode(blockIdx.x);
+    long long prev_first = 0;
+    int prev_rows = 0;
     fetch_vectors(cur);
+    write_vectors(cur, sVec0);
+    epi_barrier();
     uint32_t it = 0;
+    bool stopped = false;
 #pragma unroll 1
     for (long long w = blockIdx.x; w < total; w += gridDim.x, ++it) {
       const uint32_t ph = it & 1;
@@ -468,14 +514,8 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
       if (has_next) nxt = decode(w + gridDim.x);
       const int valid = cur.valid;
       const int koff = OFF_K + (int)ph * ROW_TILE;
-      if (tid < CHUNK) {
-        sG[tid] = pre_g;
-        sGam[tid] = fast_exp(pre_g);
-        sRho[tid] = fast_exp(pre_gl - pre_g);
-        sBeta[tid] = pre_beta;
-      }
-      epi_barrier();
-      if (*stop_flag) break;  // written before the barrier by one thread: uniform
+      const float* sG = ph ? sVec1 : sVec0;
+      const float *sGam = sG + 64, *sRho = sG + 128, *sBeta = sG + 192;
       bool ok = WAIT(L_A, ph) && WAIT(L_B, ph) && WAIT(L_C, ph);
       if (ok && valid < CHUNK) {
         zero_rows(OFF_Q, 2, valid);
@@ -632,6 +672,9 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
         }
         signal(R_D3);
         signal(R_END);  // this group no longer touches the accumulators or the tiles of the item
+        // The partial-sum slots were read for the previous item by threads of the bulk group, which
+        // arrive on R_E4 of this item only after that: long complete by now.
+        ok = ok && WAIT(R_E4, ph);
         // one reduction per quantity, one plain store per (warp, row or column): no atomics
         acc_dg_a = quad_sum(acc_dg_a);
         acc_dg_b = quad_sum(acc_dg_b);
@@ -674,6 +717,7 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars[R_HD]);
+        if (it > 0) combine(prev_first, prev_rows);  // fits into the wait for the first wide products
         const float f_w = hi ? sRho[row_w] : p.scale * sGam[row_w];
         const int row_q = row_w - (lane & 3);  // row of lane 0 of this quad
         const long long out_q = ((cur.row0 + row_q) * p.Hv + cur.hv) * D + c128;
@@ -747,27 +791,22 @@ bwd_main_tc_kernel(const BwdMainTcParams p, const __grid_constant__ CUtensorMap 
         for (int d = 16; d > 0; d >>= 1) acc_last += __shfl_xor_sync(0xffffffffu, acc_last, d);
         if (lane == 0) sLast[gw] = acc_last;
       }
+      // One barrier per item: every contribution to dg, db of this item is in, and the vectors of
+      // the next item are in place (other buffer).  The stop flag alternates as well, so that it
+      // is read by all before it can be written again.
+      if (has_next) write_vectors(nxt, ph ? sVec0 : sVec1);
       if (!ok) *abort_flag = 1;
-      epi_barrier();  // every contribution to dg, db is in
-      if (tid == 0 && *abort_flag) *stop_flag = 1;
-      if (tid < valid) {
-        float dgv = 0.f, dbv = 0.f;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          dgv += sRowW[j * 64 + tid] - sColDg[j * 64 + tid];
-          dbv += sColC1[j * 64 + tid];
-        }
-        dgv += sRowDg[tid] + sRowDg[64 + tid];
-        dbv += sRowDb[tid] + sRowDb[64 + tid];
-        if (tid == valid - 1) {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) dgv += sLast[j];
-        }
-        p.dg[(cur.row0 + tid) * p.Hv + cur.hv] = dgv;
-        p.db[(cur.row0 + tid) * p.Hv + cur.hv] = dbv;
-      }
+      if (tid == 0) stop_flag[ph] = *abort_flag;
+      epi_barrier();
+      prev_first = cur.row0 * p.Hv + cur.hv;
+      prev_rows = cur.valid;
       cur = nxt;
+      if (stop_flag[ph]) {  // written before the barrier by one thread: uniform
+        stopped = true;
+        break;
+      }
     }
+    if (it > 0 && !stopped) combine(prev_first, prev_rows);
   }
   tc_fence_before();
   __syncthreads();
