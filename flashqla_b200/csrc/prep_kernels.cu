@@ -4,6 +4,7 @@
 //   * sum of per-value-head dq/dk over each grouped-value-attention group
 // These replace the reference's ops/utils/cumsum.py:14-134, blackwell/kkt_solve.py:19-281 and
 // ops/utils/group_reduce.py:12-57.
+#include <type_traits>
 #include "common.cuh"
 #include "fqla_internal.h"
 
@@ -161,20 +162,34 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(
   cp_async_wait<0>();
   __syncthreads();
 
-  // warp w: rows 16w..16w+15, all 64 columns
-  float acc[1][8][4];
-  zero_acc(acc);
-  warp_gemm<1, 8, D / 16, false, false>(acc, sK + warp * 16 * LDK, LDK, sK, LDK, lane);
+  // Only the 16 x 16 blocks on and below the diagonal of K K^T are needed (10 of 16); they are
+  // dealt to the four warps 3, 3, 2, 2.  rb = row block, [u0, u0 + NU) = 16-column blocks.
+  auto kkt_blocks = [&](auto nu_tag, int rb, int u0) {
+    constexpr int NU = decltype(nu_tag)::value;
+    float acc[1][2 * NU][4];
+    zero_acc(acc);
+    warp_gemm<1, 2 * NU, D / 16, false, false>(acc, sK + rb * 16 * LDK, LDK, sK + u0 * 16 * LDK, LDK, lane);
 #pragma unroll
-  for (int nt = 0; nt < 8; ++nt)
+    for (int nt = 0; nt < 2 * NU; ++nt)
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      int r = warp * 16 + (lane >> 2) + (e >> 1) * 8;
-      int c = nt * 8 + (lane & 3) * 2 + (e & 1);
-      float v = 0.f;
-      if (r > c) v = sB[r] * acc[0][nt][e] * fast_exp(sG[r] - sG[c]);
-      sL[r * LDL + c] = v;
-    }
+      for (int e = 0; e < 4; ++e) {
+        int r = rb * 16 + (lane >> 2) + (e >> 1) * 8;
+        int c = u0 * 16 + nt * 8 + (lane & 3) * 2 + (e & 1);
+        float v = 0.f;
+        if (r > c) v = sB[r] * acc[0][nt][e] * fast_exp(sG[r] - sG[c]);
+        sL[r * LDL + c] = v;
+      }
+  };
+  if (warp == 0) {
+    kkt_blocks(std::integral_constant<int, 3>{}, 3, 0);
+  } else if (warp == 1) {
+    kkt_blocks(std::integral_constant<int, 3>{}, 2, 0);
+  } else if (warp == 2) {
+    kkt_blocks(std::integral_constant<int, 1>{}, 3, 3);
+    kkt_blocks(std::integral_constant<int, 1>{}, 0, 0);
+  } else {
+    kkt_blocks(std::integral_constant<int, 2>{}, 1, 0);
+  }
   __syncthreads();
 
   // Inverse of the unit lower-triangular (I + L) by recursive halving:
