@@ -347,7 +347,7 @@ def run_ours(args):
     # DRAM bytes per (token, value head) of one launch, from the ncu capture of the quarter-size
     # workload (profiles/kernels__c1_quarter.md: read + write counters / 131072 pairs); traffic
     # grows in proportion to the pairs processed
-    traffic_per_th = {"fwd_tc_kernel": 141.5e6 / 131072, "bwd_main_tc_kernel": 431.1e6 / 131072}
+    traffic_per_th = {"fwd_tc_kernel": 143.4e6 / 131072, "bwd_main_tc_kernel": 432.7e6 / 131072}
     traffic = traffic_per_th[kernel_name] * tokens * x["Hv"] if G == 1 else None
     alg_bytes = tokens * x["Hv"] * bytes_per_th
     peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
