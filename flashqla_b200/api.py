@@ -47,25 +47,40 @@ def _beta_in(beta):
     return beta if beta.dtype in (torch.float32, torch.bfloat16) else beta.float()
 
 
+# With the forward cache on (the training path), the forward also keeps what the backward would
+# otherwise recompute with a second pass of the recurrence: the state entering every chunk and
+# v_new, as the operand tiles the chunk-parallel backward reads (768 bytes per token and value
+# head).  Set to False to trade that memory for the recomputation.
+SAVE_STATE_TILES = True
+
+
+def _tiles_ok(D: int) -> bool:
+    return D == 128 and os.environ.get("FQLA_FORCE_MMA_SYNC") is None
+
+
 def run_forward(q, k, v, A, g_cum, beta, scale, h0, tables, output_final_state=True,
                 output_h=False, auto_cp=True, enable_fwd_cp_cache=False):
     """The part of the forward after cumsum and kkt+solve: optional split into segments with
-    state hand-off, then the sequential recurrence.  Returns ``(outputs dict, cp_cache)``."""
+    state hand-off, then the sequential recurrence.  Returns ``(outputs dict, cp_cache)``;
+    ``cp_cache`` is ``(segment initial states or None, h tiles or None, v_new tiles or None)``."""
     plan = cp.plan_segments(tables, v.shape[2], is_bwd=False, device=k.device) if auto_cp else None
+    keep = enable_fwd_cp_cache and SAVE_STATE_TILES and not output_h and _tiles_ok(k.shape[-1])
+    extra = dict(output_h=True, output_vnew=True, operand_tiles=True) if keep else dict(output_h=output_h)
     cp_cache = None
     if plan is not None:
         seg_h0 = cp.forward_segment_states(plan, k, v, A, g_cum, beta, scale, h0)
         res = ops.fwd_seq(q, k, v, A, g_cum, beta, scale, seg_h0,
-                          output_final_state=output_final_state, output_h=output_h,
-                          tables=plan.seg_tables)
+                          output_final_state=output_final_state, tables=plan.seg_tables, **extra)
         if output_final_state:
             res["ht"] = res["ht"][plan.last_seg_of_raw]
-        if enable_fwd_cp_cache:
-            cp_cache = (seg_h0,)
     else:
+        seg_h0 = None
         res = ops.fwd_seq(q, k, v, A, g_cum, beta, scale, h0,
-                          output_final_state=output_final_state, output_h=output_h,
-                          tables=tables)
+                          output_final_state=output_final_state, tables=tables, **extra)
+    if keep:
+        cp_cache = (seg_h0, res.pop("h"), res.pop("vnew"))
+    elif enable_fwd_cp_cache and seg_h0 is not None:
+        cp_cache = (seg_h0, None, None)
     return res, cp_cache
 
 
@@ -137,10 +152,11 @@ def chunk_gated_delta_rule_bwd(
     h0 = _state_in(initial_state, state_v_first)
     dht_k = _state_in(dht, state_v_first)
 
+    cached = tuple(cp_cache) + (None, None, None) if cp_cache is not None else (None, None, None)
     plan = cp.plan_segments(tables, Hv, is_bwd=True, device=k.device) if auto_cp else None
     if plan is not None:
-        if cp_cache is not None:
-            seg_h0 = cp_cache[0]
+        if cached[0] is not None:
+            seg_h0 = cached[0]
         else:
             seg_h0 = cp.forward_segment_states(plan, k, v, A, g, beta_k, scale, h0)
         seg_dht = cp.backward_segment_states(plan, q, k, v, A, g, beta_k, do, scale, dht_k)
@@ -150,9 +166,12 @@ def chunk_gated_delta_rule_bwd(
 
     # K = V = 128: the sequential kernels hand h, v_new, dh, du to the chunk-parallel kernel as
     # ready-made operand tiles (written by TMA), not as row-major tensors
-    tiles = D == 128 and os.environ.get("FQLA_FORCE_MMA_SYNC") is None
-    fw = ops.fwd_seq(None, k, v, A, g, beta_k, scale, run_h0, output_o=False, output_h=True,
-                     output_vnew=True, tables=run_tables, operand_tiles=tiles)
+    tiles = _tiles_ok(D)
+    if tiles and cached[1] is not None and cached[2] is not None:
+        fw = {"h": cached[1], "vnew": cached[2]}  # kept by the forward: no recomputation
+    else:
+        fw = ops.fwd_seq(None, k, v, A, g, beta_k, scale, run_h0, output_o=False, output_h=True,
+                         output_vnew=True, tables=run_tables, operand_tiles=tiles)
     bw = ops.bwd_dh(q, k, A, g, beta_k, do, scale, run_dht, tables=run_tables,
                     operand_tiles=tiles)
     dq, dk, dv, db, dg = ops.bwd_main(q, k, v, fw["vnew"], A, g, beta_k, do, bw["du"], fw["h"],

@@ -194,3 +194,40 @@ def test_kkt_solve_with_fused_cumsum(cu):
     assert orc.rel_err(A.float(), A_ref.float()) < 1e-3
     want = orc.chunk_local_cumsum(d["g"].cpu(), None if cu_t is None else cu_t.cpu())
     assert orc.rel_err(g_cum.cpu(), want) < 1e-6
+
+
+@pytest.mark.parametrize("cu,T", [(None, 1024), ([0, 130, 130, 777, 1000], 1000), (None, 16384)],
+                         ids=["fixed", "varlen", "segmented"])
+def test_forward_cache_tiles_replace_the_recomputation(cu, T):
+    """With the forward cache on, the forward keeps the state entering every chunk and v_new as
+    operand tiles; they equal what the backward's own state-only pass produces, and the backward
+    returns the same gradients with or without them."""
+    import flashqla_b200 as fq
+    from flashqla_b200 import api, ops
+
+    d = _inputs(T, 2, 4, seed=47, cu=cu)
+    cu_t = d["cu_seqlens"]
+    g_cum, A, o, _, ht, cache = fq.chunk_gated_delta_rule_fwd(
+        d["q"], d["k"], d["v"], d["g"], d["beta"], None, d["h0"], cu_t, output_final_state=True,
+        enable_fwd_cp_cache=True)
+    assert cache is not None and cache[1] is not None and cache[2] is not None
+    if T >= 16384:
+        assert cache[0] is not None  # long sequence: split into segments, initial states kept too
+    _, _, o2, _, ht2, none = fq.chunk_gated_delta_rule_fwd(
+        d["q"], d["k"], d["v"], d["g"], d["beta"], None, d["h0"], cu_t, output_final_state=True)
+    assert none is None
+    assert torch.equal(o, o2) and torch.equal(ht, ht2)
+    args = (d["q"], d["k"], d["v"], g_cum, d["beta"], A, d["do"], d["dht"], None, d["h0"], cu_t)
+    with_tiles = fq.chunk_gated_delta_rule_bwd(*args, cp_cache=cache)
+    recomputed = fq.chunk_gated_delta_rule_bwd(*args, cp_cache=(cache[0], None, None))
+    for x, y, name in zip(with_tiles, recomputed, ("dq", "dk", "dv", "db", "dg", "dh0")):
+        assert torch.equal(x, y), name
+    # the switch turns the tiles off again
+    api.SAVE_STATE_TILES = False
+    try:
+        cache_off = fq.chunk_gated_delta_rule_fwd(
+            d["q"], d["k"], d["v"], d["g"], d["beta"], None, d["h0"], cu_t,
+            enable_fwd_cp_cache=True)[5]
+    finally:
+        api.SAVE_STATE_TILES = True
+    assert cache_off is None or cache_off[1] is None
