@@ -170,15 +170,19 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(
     zero_acc(acc);
     warp_gemm<1, 2 * NU, D / 16, false, false>(acc, sK + rb * 16 * LDK, LDK, sK + u0 * 16 * LDK, LDK, lane);
 #pragma unroll
-    for (int nt = 0; nt < 2 * NU; ++nt)
+    for (int hh = 0; hh < 2; ++hh) {
+      const int r = rb * 16 + (lane >> 2) + hh * 8;
+      const float br = sB[r], gr = sG[r];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        int r = rb * 16 + (lane >> 2) + (e >> 1) * 8;
-        int c = u0 * 16 + nt * 8 + (lane & 3) * 2 + (e & 1);
-        float v = 0.f;
-        if (r > c) v = sB[r] * acc[0][nt][e] * fast_exp(sG[r] - sG[c]);
-        sL[r * LDL + c] = v;
+      for (int nt = 0; nt < 2 * NU; ++nt) {
+        const int c = u0 * 16 + nt * 8 + (lane & 3) * 2;  // columns c, c + 1: one 8-byte store
+        const float2 gc = *reinterpret_cast<const float2*>(sG + c);
+        float2 v;
+        v.x = r > c ? br * acc[0][nt][2 * hh] * fast_exp(gr - gc.x) : 0.f;
+        v.y = r > c + 1 ? br * acc[0][nt][2 * hh + 1] * fast_exp(gr - gc.y) : 0.f;
+        *reinterpret_cast<float2*>(sL + r * LDL + c) = v;
       }
+    }
   };
   if (warp == 0) {
     kkt_blocks(std::integral_constant<int, 3>{}, 3, 0);
