@@ -99,12 +99,13 @@ __device__ __forceinline__ void store_frag(float* C, int ldc, const float (&c)[N
 }
 
 // ------------------------------------------------------------------------------------------
-// kkt + solve.  One CTA (128 threads) per (chunk, value head).
+// kkt + solve.  One CTA (128 threads) per (chunk, q head): K K^T is computed once and kept in
+// registers, then scaled and inverted for each of the Hv / Hq value heads of the group in turn.
 //   1. K K^T (64x64xD) on tensor cores, 2. L = strict_lower(beta_s * KK^T * exp(g_s-g_t)) in fp32,
 //   3. X = (I+L)^-1 by blocked forward substitution in fp32, 4. bf16 rows out.
 // ------------------------------------------------------------------------------------------
 template <int D>
-__global__ void __launch_bounds__(128) kkt_solve_kernel(
+__global__ void __launch_bounds__(128, 5) kkt_solve_kernel(
     const bf16* __restrict__ k, const void* __restrict__ beta, int beta_is_f32,
     const float* __restrict__ g, float* __restrict__ g_cum_out, bf16* __restrict__ A, int Hq,
     int Hv, SeqLayout lay, IndexTable chunk_indices) {
@@ -122,7 +123,7 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(
   float* sY = sB + CHUNK;
 
   int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  int hv = blockIdx.y, hq = hv / (Hv / Hq);
+  const int hq = blockIdx.y, G = Hv / Hq;
   int seq, ci;
   if (lay.cu.ptr) {
     seq = (int)chunk_indices[2 * blockIdx.x];
@@ -138,6 +139,11 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(
 
   load_tile_async<D, LDK, 128>(sK, k + (row0 * Hq + hq) * D, (long long)Hq * D, valid, tid);
   cp_async_commit();
+  float kkt[24];  // this thread's part of the lower blocks of K K^T
+#pragma unroll 1
+  for (int gi = 0; gi < G; ++gi) {
+  const int hv = hq * G + gi;
+  if (gi > 0) __syncthreads();  // the inverse of the head before has been written out
   if (tid < CHUNK) {
     sB[tid] = tid < valid ? load_beta(beta, beta_is_f32, (row0 + tid) * Hv + hv) : 0.f;
     if (g_cum_out) {
@@ -159,16 +165,18 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(
       sG[tid] = g[(row0 + r) * Hv + hv];
     }
   }
-  cp_async_wait<0>();
+  if (gi == 0) cp_async_wait<0>();
   __syncthreads();
 
   // Only the 16 x 16 blocks on and below the diagonal of K K^T are needed (10 of 16); they are
   // dealt to the four warps 3, 3, 2, 2.  rb = row block, [u0, u0 + NU) = 16-column blocks.
-  auto kkt_blocks = [&](auto nu_tag, int rb, int u0) {
+  auto kkt_blocks = [&](auto nu_tag, auto off_tag, int rb, int u0) {
     constexpr int NU = decltype(nu_tag)::value;
-    float acc[1][2 * NU][4];
-    zero_acc(acc);
-    warp_gemm<1, 2 * NU, D / 16, false, false>(acc, sK + rb * 16 * LDK, LDK, sK + u0 * 16 * LDK, LDK, lane);
+    float (&acc)[1][2 * NU][4] = *reinterpret_cast<float (*)[1][2 * NU][4]>(kkt + decltype(off_tag)::value);
+    if (gi == 0) {  // the K tile is gone (the inverse is built over it) once the first head is done
+      zero_acc(acc);
+      warp_gemm<1, 2 * NU, D / 16, false, false>(acc, sK + rb * 16 * LDK, LDK, sK + u0 * 16 * LDK, LDK, lane);
+    }
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
       const int r = rb * 16 + (lane >> 2) + hh * 8;
@@ -185,14 +193,14 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(
     }
   };
   if (warp == 0) {
-    kkt_blocks(std::integral_constant<int, 3>{}, 3, 0);
+    kkt_blocks(std::integral_constant<int, 3>{}, std::integral_constant<int, 0>{}, 3, 0);
   } else if (warp == 1) {
-    kkt_blocks(std::integral_constant<int, 3>{}, 2, 0);
+    kkt_blocks(std::integral_constant<int, 3>{}, std::integral_constant<int, 0>{}, 2, 0);
   } else if (warp == 2) {
-    kkt_blocks(std::integral_constant<int, 1>{}, 3, 3);
-    kkt_blocks(std::integral_constant<int, 1>{}, 0, 0);
+    kkt_blocks(std::integral_constant<int, 1>{}, std::integral_constant<int, 0>{}, 3, 3);
+    kkt_blocks(std::integral_constant<int, 1>{}, std::integral_constant<int, 8>{}, 0, 0);
   } else {
-    kkt_blocks(std::integral_constant<int, 2>{}, 1, 0);
+    kkt_blocks(std::integral_constant<int, 2>{}, std::integral_constant<int, 0>{}, 1, 0);
   }
   __syncthreads();
 
@@ -257,6 +265,7 @@ __global__ void __launch_bounds__(128) kkt_solve_kernel(
       *reinterpret_cast<uint4*>(A + ((row0 + r) * Hv + hv) * CHUNK + c0) = pk;
     }
   }
+  }  // value heads of the group
 }
 
 // ------------------------------------------------------------------------------------------
@@ -314,7 +323,7 @@ static int launch_kkt(const void* k, const void* beta, int beta_is_f32, const fl
   constexpr int smem = (k_tile > x_tile ? k_tile : x_tile) + x_tile + 2 * CHUNK * 4 + 32 * 40 * 4;
   int rc = configure_smem((const void*)kkt_solve_kernel<D>, smem);
   if (rc != 0) return rc;
-  kkt_solve_kernel<D><<<dim3((unsigned)n, Hv), 128, smem, st>>>(
+  kkt_solve_kernel<D><<<dim3((unsigned)n, Hq), 128, smem, st>>>(
       (const bf16*)k, beta, beta_is_f32, g, g_cum_out, (bf16*)A, Hq, Hv, lay, ci);
   return (int)cudaGetLastError();
 }
