@@ -417,8 +417,16 @@ def cpu_run(w, x):
                           x["h0"])
 
 
+def _use_all_host_threads():
+    """The CPU implementation gets every core the process may run on.  (torchrun exports
+    OMP_NUM_THREADS=1 to its workers, which would otherwise leave it with one thread.)"""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    torch.set_num_threads(max(1, n))
+    return torch.get_num_threads()
+
+
 def cpu_baseline(w, seconds):
-    threads = torch.get_num_threads()
+    threads = _use_all_host_threads()
     x, T = cpu_sample(w)
     cpu_run(w, x)
     times, t_end = [], time.time() + seconds
@@ -437,7 +445,7 @@ def run_reference(args):
     if rank != 0:
         return
     w = WORKLOADS[args.workload]
-    threads = torch.get_num_threads()
+    threads = _use_all_host_threads()
     x, T = cpu_sample(w)
     for _ in range(max(args.warmup, 1)):
         cpu_run(w, x)
