@@ -1,8 +1,8 @@
-"""Drop-in import path: ``flash_qla`` resolves to the B200-native implementation in
-``flashqla_b200`` (same public names as the reference's ``flash_qla/__init__.py:6-16``)."""
+"""Drop-in import path: ``flash_qla`` resolves to the B200-native implementation
+(same public names as the reference's ``flash_qla/__init__.py:6-16``)."""
 
 from flashqla_b200 import __version__  # noqa: F401
-from flashqla_b200.api import (
+from flash_qla.ops.gated_delta_rule.chunk import (
     chunk_gated_delta_rule,
     chunk_gated_delta_rule_bwd,
     chunk_gated_delta_rule_fwd,

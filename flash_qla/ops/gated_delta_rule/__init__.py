@@ -1,4 +1,4 @@
-from flashqla_b200.api import (
+from .chunk import (
     chunk_gated_delta_rule,
     chunk_gated_delta_rule_bwd,
     chunk_gated_delta_rule_fwd,

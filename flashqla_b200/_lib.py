@@ -24,6 +24,7 @@ SIGNATURES = {
     "fqla_warmup_scan": [P, I, I, P, I, I, F, I, P, P, P, P],
     "fqla_merge_states": [P, P, P, P, P, P, I, I, I, I, P],
     "fqla_device_status": [P, I],
+    "fqla_selftest_wait_timeout": [I, P],
 }
 
 _lib = None

@@ -22,6 +22,8 @@
 
 #include "common.cuh"
 #include "fqla_internal.h"
+#include <mutex>
+
 #include "tc05.cuh"
 
 namespace fqla {
@@ -31,8 +33,6 @@ using namespace tc;
 // set to 1 when a CTA of this file's kernel abandoned a bounded wait; read through
 // fqla_device_status together with the forward kernel's word
 __device__ int g_bwd_main_status = 0;
-// Diagnostics (FQLA_PROFILE=1): clock of thread 0 of CTA 0 after every wait and every read-out step
-__device__ long long g_bwd_main_profile[64];
 
 struct BwdMainTcParams {
   const float* g;
@@ -48,7 +48,6 @@ struct BwdMainTcParams {
   SeqLayout lay;
   IndexTable chunk_indices;
   long long n_chunks;
-  int profile;
 };
 
 namespace bmtc {
@@ -826,11 +825,6 @@ int bwd_main_tc_status(int* out, int reset) {
   return (int)e;
 }
 
-}  // namespace fqla
-extern "C" int fqla_debug_bwd_main_profile(long long* out64) {
-  return (int)cudaMemcpyFromSymbol(out64, fqla::g_bwd_main_profile, sizeof(long long) * 64);
-}
-namespace fqla {
 
 // ---- host side --------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn2)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -838,7 +832,12 @@ typedef CUresult (*EncodeTiledFn2)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
                                    const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-// 2-D bf16 tensor map, rows x cols (row-major), box = 64 columns x box_rows rows, 128-byte swizzle
+// 2-D bf16 tensor map, rows x cols (row-major), box = 64 columns x box_rows rows, 128-byte swizzle.
+// Encoding a map costs about a microsecond on the host and a launch needs four to nine of them, so
+// the last maps are kept in a small table keyed by (pointer, shape, box): a steady-state step that
+// reuses its buffers (a framework's caching allocator, a CUDA graph's private pool) encodes nothing.
+// A map only describes addresses and extents, so an entry stays valid when the buffer is freed and
+// an equal allocation returns at the same address.
 int make_tile_map(CUtensorMap* m, const void* ptr, long long rows, long long cols, int box_rows) {
   static EncodeTiledFn2 fn = [] {
     void* f = nullptr;
@@ -848,6 +847,26 @@ int make_tile_map(CUtensorMap* m, const void* ptr, long long rows, long long col
     return (EncodeTiledFn2)f;
   }();
   if (!fn) return FQLA_ERR_INVALID_ARG;
+  struct Entry {
+    const void* ptr;
+    long long rows, cols;
+    int box_rows, used;
+    CUtensorMap map;
+  };
+  constexpr int N_ENTRIES = 128;
+  static Entry table[N_ENTRIES] = {};
+  static std::mutex lock;
+  const uint64_t hsh = ((uint64_t)(uintptr_t)ptr >> 8) * 0x9E3779B97F4A7C15ull ^
+                       ((uint64_t)rows * 0xC2B2AE3D27D4EB4Full) ^ ((uint64_t)cols << 17) ^
+                       (uint64_t)box_rows;
+  Entry& e = table[(hsh >> 32) % N_ENTRIES];
+  {
+    std::lock_guard<std::mutex> hold(lock);
+    if (e.used && e.ptr == ptr && e.rows == rows && e.cols == cols && e.box_rows == box_rows) {
+      *m = e.map;
+      return 0;
+    }
+  }
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
   cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
@@ -855,7 +874,10 @@ int make_tile_map(CUtensorMap* m, const void* ptr, long long rows, long long col
   CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides,
                   box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : FQLA_ERR_INVALID_ARG;
+  if (r != CUDA_SUCCESS) return FQLA_ERR_INVALID_ARG;
+  std::lock_guard<std::mutex> hold(lock);
+  e.ptr = ptr; e.rows = rows; e.cols = cols; e.box_rows = box_rows; e.map = *m; e.used = 1;
+  return 0;
 }
 
 int launch_bwd_main_tc(const void* q, const void* k, const void* v, const void* vnew, const void* A,
@@ -885,17 +907,13 @@ int launch_bwd_main_tc(const void* q, const void* k, const void* v, const void* 
   p.dq = (bf16*)dq; p.dk = (bf16*)dk; p.dv = (bf16*)dv; p.db = db; p.dg = dg;
   p.Hq = Hq; p.Hv = Hv; p.scale = scale; p.lay = lay; p.chunk_indices = chunk_indices;
   p.n_chunks = n_chunks;
-  static const bool profile = getenv("FQLA_PROFILE") != nullptr;
-  p.profile = profile;
   rc = configure_smem(tiled ? (const void*)bwd_main_tc_kernel<true> : (const void*)bwd_main_tc_kernel<false>,
                       SMEM_BYTES);
   if (rc != 0) return rc;
-  static const int n_sm = [] {
-    int dev = 0, n = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    return n > 0 ? n : 148;
-  }();
+  int dev = 0, n_sm = 0;  // per launch: the current device may differ from call to call
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+  if (n_sm <= 0) n_sm = 148;
   const long long total = n_chunks * Hv;
   const unsigned grid = (unsigned)(total < n_sm ? total : n_sm);
   if (tiled)

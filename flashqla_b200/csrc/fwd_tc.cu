@@ -754,36 +754,12 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
 }
 
 // ---- host side --------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = [] {
-    void* f = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess)
-      f = nullptr;
-    return (EncodeTiledFn)f;
-  }();
-  return fn;
-}
-
-// 2-D bf16 tensor [rows][cols] (row pitch = cols), box = 64 columns x 64 rows, 128-byte swizzle.
+// 2-D bf16 tensor [rows][cols] (row pitch = cols), box = 64 columns x box_rows rows, 128-byte
+// swizzle; recently used maps are served from a small host-side table (bwd_main_tc.cu).
 int make_tile_map(CUtensorMap* m, const void* ptr, long long rows, long long cols, int box_rows);
 
 static int make_map(CUtensorMap* m, const void* ptr, long long rows, long long cols) {
-  EncodeTiledFn fn = encode_fn();
-  if (!fn) return FQLA_ERR_INVALID_ARG;
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-  cuuint32_t box[2] = {64, 64};
-  cuuint32_t es[2] = {1, 1};
-  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides,
-                  box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : FQLA_ERR_INVALID_ARG;
+  return make_tile_map(m, ptr, rows, cols, 64);
 }
 
 int launch_fwd_tc(const void* q, const void* k, const void* v, const void* A, const float* g,
@@ -812,8 +788,7 @@ int launch_fwd_tc(const void* q, const void* k, const void* v, const void* A, co
   p.g = g; p.beta = beta; p.beta_is_f32 = beta_is_f32; p.h0 = h0; p.ht = ht;
   p.o = (bf16*)o; p.h = (bf16*)h; p.vnew = (bf16*)vnew;
   p.N = N; p.Hq = Hq; p.Hv = Hv; p.T_rows = T_rows; p.scale = scale; p.lay = lay;
-  static const bool profile = getenv("FQLA_PROFILE") != nullptr;
-  p.profile = profile ? 1 : 0;
+  p.profile = 0;
   const bool extra = h != nullptr || vnew != nullptr;
   auto launch = [&](auto kernel) {
     int err = configure_smem((const void*)kernel, SMEM_BYTES);
@@ -821,7 +796,11 @@ int launch_fwd_tc(const void* q, const void* k, const void* v, const void* A, co
     kernel<<<(unsigned)(N * Hv), 512, SMEM_BYTES, st>>>(p, mq, mk, mv, ma, mh, mvn);
     return (int)cudaGetLastError();
   };
+#ifdef FQLA_DIAGNOSTICS  // wait/section cycle counters of the first CTA (development builds only)
+  static const bool profile = getenv("FQLA_PROFILE") != nullptr;
+  p.profile = profile ? 1 : 0;
   if (p.profile) return launch(fwd_tc_kernel<true, true, false>);
+#endif
   if (!q && !o) return launch(fwd_tc_kernel<false, true, true>);  // recomputation of h, v_new
   if (extra) return launch(fwd_tc_kernel<false, true, false>);
   return launch(fwd_tc_kernel<false, false, false>);
@@ -829,12 +808,40 @@ int launch_fwd_tc(const void* q, const void* k, const void* v, const void* A, co
 
 }  // namespace fqla
 
+#ifdef FQLA_DIAGNOSTICS
 extern "C" int fqla_debug_abort_info(int* out) {
   return (int)cudaMemcpyFromSymbol(out, fqla::g_fwd_abort_info, sizeof(int));
 }
 
 extern "C" int fqla_debug_wait_profile(long long* out168) {
   return (int)cudaMemcpyFromSymbol(out168, fqla::g_wait_profile, sizeof(long long) * 7 * 24);
+}
+#endif
+
+namespace fqla {
+// Self-test of the bounded-wait path: one thread waits on an mbarrier that nobody ever arrives
+// at, with a budget of `tries` suspended tries of at most 1 ms each.  The wait gives up, the
+// kernel sets the device status word exactly as a product kernel does, and returns.
+__global__ void wait_timeout_selftest_kernel(uint32_t tries) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    abort_flag = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  bool ok = true;
+  if (threadIdx.x == 0) ok = mbar_wait(&bar, 0, &abort_flag, tries);
+  __syncthreads();
+  if (threadIdx.x == 0 && (!ok || abort_flag)) atomicCAS(&g_device_status, 0, 1);
+}
+}  // namespace fqla
+
+extern "C" int fqla_selftest_wait_timeout(int tries, void* stream) {
+  if (tries < 1 || tries > 100) return FQLA_ERR_INVALID_ARG;
+  fqla::wait_timeout_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((uint32_t)tries);
+  return (int)cudaGetLastError();
 }
 
 namespace fqla {

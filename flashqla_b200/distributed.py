@@ -10,7 +10,8 @@ benchmark rows only emulate the head count one tensor-parallel shard would see):
   rank first computes, from a zero state, the end state of its own tokens and (only where the
   gates do not let the past die out inside the shard) the exact transition matrix ``M`` of its
   shard; one all-gather hands every rank all boundary summaries (``[Hv,K,V]`` + ``[Hv,K,K]`` fp32
-  per rank, about 1 MiB at Hv = 8), every rank chains them locally
+  per rank, packed with the optional edge state into one record of about 1.5 MiB at Hv = 8 and
+  moved by ONE collective per direction), every rank chains them locally
   (``start[r+1] = local[r] + M[r] start[r]``) and then runs the ordinary forward on its tokens
   with its start state.  The backward pass mirrors this for the state gradient with ``M^T`` in
   the other direction.  The payload always lands in the receiving GPU's own memory (the
@@ -54,6 +55,18 @@ def shard_heads(q, k, v, g, beta, rank: int, world: int, initial_state=None):
 
 # ---- T sharding -----------------------------------------------------------------------------
 
+_const_cache: dict = {}
+
+
+def _const_i32(values: tuple, device) -> torch.Tensor:
+    """Small constant index tensors, made once per (values, device): steady-state steps then do
+    no host-to-device copy, and the memo caches keyed by tensor identity keep hitting."""
+    key = (values, str(device))
+    if key not in _const_cache:
+        _const_cache[key] = torch.tensor(values, dtype=torch.int32, device=device)
+    return _const_cache[key]
+
+
 def chain_boundary_states(local, M, use_m, first, rank: int, reverse: bool = False,
                           merge_fn=None):
     """Start state (or, reversed, end gradient) of ``rank`` from the gathered per-rank
@@ -62,49 +75,59 @@ def chain_boundary_states(local, M, use_m, first, rank: int, reverse: bool = Fal
     ``merge_fn`` defaults to the CUDA merge kernel; the CPU tests pass a torch stand-in."""
     merge_fn = merge_fn or ops.merge_states
     R = local.shape[0]
-    seg_begin = torch.tensor([0, R], dtype=torch.int32, device=local.device)
+    seg_begin = _const_i32((0, R), local.device)
     chained = merge_fn(local, M, use_m, first, seg_begin, reverse)
     return chained[rank:rank + 1].contiguous()
 
 
-def _gather(x, group):
-    world = dist.get_world_size(group)
-    parts = [torch.empty_like(x) for _ in range(world)]
-    dist.all_gather(parts, x.contiguous(), group=group)
-    return torch.stack(parts)
+def _exchange(local, M, use_m, edge_state, edge_rank: int, reverse: bool, group, merge_fn):
+    """One all-gather per direction, the same on every rank whatever its local arguments.
+
+    Every rank contributes one record ``[local | M | edge state | use_m]``; the edge state (the
+    sequence's initial state for the forward direction, the gradient of its final state for the
+    reverse one) is read from the record of ``edge_rank`` only, and an owner that was given none
+    sends zeros, which chain exactly like "no state".  So a caller may pass the state on the
+    owning rank only, on every rank, or nowhere: the collective sequence is identical in all
+    three cases."""
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    Hv, D = local.shape[1], local.shape[2]
+    n_state = Hv * D * D
+    rec = torch.zeros(3 * n_state + Hv, dtype=local.dtype, device=local.device)
+    rec[:n_state] = local.reshape(-1)
+    rec[n_state:2 * n_state] = M.reshape(-1)
+    if edge_state is not None and rank == edge_rank:
+        rec[2 * n_state:3 * n_state] = edge_state.reshape(-1)
+    rec[3 * n_state:] = use_m.reshape(-1).to(local.dtype)
+    flat = torch.empty(world * rec.numel(), dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(flat, rec, group=group)
+    everything = flat.view(world, rec.numel())
+    all_local = everything[:, :n_state].reshape(world, Hv, D, D)
+    all_m = everything[:, n_state:2 * n_state].reshape(world, Hv, D, D)
+    edge = everything[edge_rank, 2 * n_state:3 * n_state].reshape(1, Hv, D, D)
+    all_use = everything[:, 3 * n_state:].to(torch.int32)
+    return chain_boundary_states(all_local.contiguous(), all_m.contiguous(), all_use.contiguous(),
+                                 edge.contiguous(), rank, reverse, merge_fn)
 
 
 def exchange_forward(local, M, use_m, initial_state, group=None, merge_fn=None):
     """All-gather the forward summaries of every rank and return this rank's start state
     ``[1, Hv, D, D]``.  ``local``/``M``: ``[1, Hv, D, D]``; ``use_m``: ``[1, Hv]`` int32;
-    ``initial_state`` is the sequence's initial state (used from rank 0 only) or None."""
-    rank = dist.get_rank(group)
-    first = None
-    if initial_state is not None:
-        first = initial_state.clone()
-        dist.broadcast(first, src=dist.get_global_rank(group, 0) if group else 0, group=group)
-    all_local, all_m, all_use = _gather(local[0], group), _gather(M[0], group), _gather(use_m[0], group)
-    return chain_boundary_states(all_local, all_m, all_use, first, rank, False, merge_fn)
+    ``initial_state`` is the sequence's initial state: it is taken from rank 0, other ranks may
+    pass it too or pass None."""
+    return _exchange(local, M, use_m, initial_state, 0, False, group, merge_fn)
 
 
 def exchange_backward(local, M, use_m, dht, group=None, merge_fn=None):
     """Mirror of ``exchange_forward`` for the state gradient: returns the gradient of the state
-    leaving this rank's tokens.  ``dht`` is the gradient of the sequence's final state (used from
-    the last rank only) or None."""
-    rank, world = dist.get_rank(group), dist.get_world_size(group)
-    last = None
-    if dht is not None:
-        last = dht.clone()
-        src = world - 1
-        dist.broadcast(last, src=dist.get_global_rank(group, src) if group else src, group=group)
-    all_local, all_m, all_use = _gather(local[0], group), _gather(M[0], group), _gather(use_m[0], group)
-    return chain_boundary_states(all_local, all_m, all_use, last, rank, True, merge_fn)
+    leaving this rank's tokens.  ``dht`` is the gradient of the sequence's final state: it is
+    taken from the last rank, other ranks may pass it too or pass None."""
+    return _exchange(local, M, use_m, dht, dist.get_world_size(group) - 1, True, group, merge_fn)
 
 
 def _local_summary_fwd(k, v, A, g_cum, beta, scale):
     """(end state from zero, M, fallback flag) of this rank's whole shard, shapes [1,Hv,D,D]."""
     T = k.shape[1]
-    seg_cu = torch.tensor([0, T], dtype=torch.int32, device=k.device)
+    seg_cu = _const_i32((0, T), k.device)
     warm, fallback = ops.warmup_scan(g_cum, seg_cu, cp.THRESHOLD, from_start=False)
     tables = ops.SeqTables(1, T, seg_cu)
     res = ops.fwd_seq(None, k, v, A, g_cum, beta, scale, None, output_o=False,
@@ -114,23 +137,26 @@ def _local_summary_fwd(k, v, A, g_cum, beta, scale):
 
 
 def fwd_tsharded(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=True,
-                 group=None):
+                 group=None, for_backward=False):
     """Forward of ONE sequence whose tokens are split evenly over the ranks of ``group``
     (this rank passes its own ``[1, T/R, ...]`` slice, a multiple of 64 tokens).  Returns
     ``(g_cum, A, o, final_state, saved)``; ``final_state`` is the sequence's final state on every
-    rank, ``saved`` carries what ``bwd_tsharded`` needs."""
+    rank, ``saved`` carries what ``bwd_tsharded`` needs.  ``initial_state`` is read on rank 0 only
+    (other ranks may pass None); ``output_final_state`` and ``for_backward`` must be the same on
+    every rank.  With ``for_backward`` the forward keeps the per-chunk state and v_new tiles so
+    that ``bwd_tsharded`` skips its recomputation pass."""
     assert q.shape[0] == 1 and q.shape[1] % CHUNK_SIZE == 0, "T shard must be a chunk multiple"
     if scale is None:
         scale = k.shape[-1] ** -0.5
     world = dist.get_world_size(group)
     g32 = g if g.dtype == torch.float32 else g.float()
-    g_cum = ops.chunk_local_cumsum(g32.contiguous(), CHUNK_SIZE, None)
-    A = ops.kkt_solve(k, beta, g_cum, None)
+    g_cum, A = ops.kkt_solve(k, beta, g32.contiguous(), None, raw_gate=True)
     local, M, fallback = _local_summary_fwd(k, v, A, g_cum, beta, scale)
     h0 = None if initial_state is None else initial_state.float().contiguous()
     start = exchange_forward(local, M, fallback, h0, group)
-    res, _ = run_forward(q, k, v, A, g_cum, beta, scale, start, ops.SeqTables(1, q.shape[1], None),
-                         output_final_state=True)
+    res, cache = run_forward(q, k, v, A, g_cum, beta, scale, start,
+                             ops.SeqTables(1, q.shape[1], None), output_final_state=True,
+                             enable_fwd_cp_cache=for_backward)
     o, ht = res["o"], res["ht"]
     final_state = None
     if output_final_state:
@@ -138,18 +164,18 @@ def fwd_tsharded(q, k, v, g, beta, scale=None, initial_state=None, output_final_
         src = world - 1
         dist.broadcast(final_state, src=dist.get_global_rank(group, src) if group else src,
                        group=group)
-    return g_cum, A, o, final_state, (start, M)
+    return g_cum, A, o, final_state, (start, M, cache)
 
 
 def bwd_tsharded(q, k, v, g_cum, beta, A, do, dht=None, scale=None, saved=None, group=None):
     """Backward of a T-sharded sequence.  ``saved`` is the tuple returned by ``fwd_tsharded``.
     Returns ``(dq, dk, dv, db, dg, dh0)`` for this rank's tokens; ``dh0`` (gradient of the
-    sequence's initial state) is valid on every rank."""
+    sequence's initial state) is valid on every rank.  ``dht`` is read on the last rank only."""
     if scale is None:
         scale = k.shape[-1] ** -0.5
-    start, M_fwd = saved
+    start, _, cache = saved
     T = k.shape[1]
-    seg_cu = torch.tensor([0, T], dtype=torch.int32, device=k.device)
+    seg_cu = _const_i32((0, T), k.device)
     tables = ops.SeqTables(1, T, seg_cu)
     warm, fallback = ops.warmup_scan(g_cum, seg_cu, cp.THRESHOLD, from_start=True)
     local = ops.bwd_dh(q, k, A, g_cum, beta, do, scale, None, output_dh=False, output_du=False,
@@ -160,7 +186,7 @@ def bwd_tsharded(q, k, v, g_cum, beta, A, do, dht=None, scale=None, saved=None, 
     dht32 = None if dht is None else dht.float().contiguous()
     end = exchange_backward(local, M, fallback, dht32, group)
     dq, dk, dv, db, dg, dh0 = chunk_gated_delta_rule_bwd(q, k, v, g_cum, beta, A, do, end, scale,
-                                                         start, None)
+                                                         start, None, cp_cache=cache)
     dh0 = dh0.clone()
     dist.broadcast(dh0, src=dist.get_global_rank(group, 0) if group else 0, group=group)
     return dq, dk, dv, db, dg, dh0

@@ -9,6 +9,8 @@ the reference's kernel wrappers (``chunk_local_cumsum``, ``kkt_solve``, ``fused_
 
 from __future__ import annotations
 
+import functools
+
 import torch
 
 from . import _lib
@@ -31,6 +33,23 @@ def _require_cuda(*tensors):
             raise _lib.FqlaError(
                 "flashqla_b200 kernels need CUDA tensors; there is no CPU fallback"
             )
+
+
+def on_tensor_device(fn):
+    """Run ``fn`` with the device of its first CUDA tensor argument current.  The C entry points
+    launch on the current device (kernel attributes, the SM count and the status word are per
+    device), while callers may hold tensors of another one."""
+
+    @functools.wraps(fn)
+    def wrapper(*args, **kwargs):
+        t = next((a for a in (*args, *kwargs.values())
+                  if isinstance(a, torch.Tensor) and a.is_cuda), None)
+        if t is None or t.device.index == torch.cuda.current_device():
+            return fn(*args, **kwargs)
+        with torch.cuda.device(t.device):
+            return fn(*args, **kwargs)
+
+    return wrapper
 
 
 class SeqTables:
@@ -102,6 +121,7 @@ def _check_bf16(**named):
             )
 
 
+@on_tensor_device
 def chunk_local_cumsum(g, chunk_size: int = CHUNK_SIZE, cu_seqlens=None, reverse: bool = False):
     """Chunk-local prefix (or suffix) sum of ``g [B,T,H]`` fp32
     (reference: ``ops/utils/cumsum.py:137-171``)."""
@@ -111,6 +131,8 @@ def chunk_local_cumsum(g, chunk_size: int = CHUNK_SIZE, cu_seqlens=None, reverse
     B, T, H = g.shape
     tb = SeqTables(B, T, cu_seqlens)
     out = torch.empty_like(g)
+    if tb.total < B * T:  # rows past the last packed sequence come out zero
+        out[:, tb.total:].zero_()
     st = _lib.load().fqla_chunk_local_cumsum(
         _ptr(g), _ptr(out), B, T, H, _ptr(tb.cu), tb.is64, tb.N, _ptr(tb.chunk_indices),
         tb.num_chunks, int(reverse), _stream(g))
@@ -118,6 +140,7 @@ def chunk_local_cumsum(g, chunk_size: int = CHUNK_SIZE, cu_seqlens=None, reverse
     return out
 
 
+@on_tensor_device
 def kkt_solve(k, b, g_cum, cu_seqlens=None, chunk_size: int = CHUNK_SIZE, raw_gate: bool = False):
     """``A = (I + strict_lower(diag(b) K K^T * decay))^-1`` per (chunk, value head), bf16
     ``[B,T,Hv,64]`` (reference: ``blackwell/kkt_solve.py:284-324``; the gate is folded in).
@@ -143,6 +166,7 @@ def kkt_solve(k, b, g_cum, cu_seqlens=None, chunk_size: int = CHUNK_SIZE, raw_ga
     return (g_out, A) if raw_gate else A
 
 
+@on_tensor_device
 def fwd_seq(q, k, v, a, g_cum, b, scale, initial_state=None, *, output_final_state=False,
             output_o=True, output_h=False, output_vnew=False, output_m=False,
             warm_chunks=None, m_mask=None, cu_seqlens=None, tables: SeqTables | None = None,
@@ -186,6 +210,7 @@ def fwd_seq(q, k, v, a, g_cum, b, scale, initial_state=None, *, output_final_sta
     return out
 
 
+@on_tensor_device
 def bwd_dh(q, k, a, g_cum, b, do, scale, dht=None, *, output_dh=True, output_du=True,
            output_dh0=True, warm_chunks=None, cu_seqlens=None, tables: SeqTables | None = None,
            operand_tiles: bool = False):
@@ -218,6 +243,7 @@ def bwd_dh(q, k, a, g_cum, b, do, scale, dht=None, *, output_dh=True, output_du=
     return out
 
 
+@on_tensor_device
 def bwd_main(q, k, v, vnew, a, g_cum, b, do, du, h, dh, scale, cu_seqlens=None,
              tables: SeqTables | None = None, operand_tiles: bool = False):
     """Chunk-parallel backward.  Returns ``(dq_v, dk_v, dv, db, dg)`` with dq_v/dk_v per value
@@ -246,6 +272,7 @@ def bwd_main(q, k, v, vnew, a, g_cum, b, do, du, h, dh, scale, cu_seqlens=None,
     return dq, dk, dv, db, dg
 
 
+@on_tensor_device
 def group_reduce_vector(x, num_groups: int):
     """``[B,T,Hv,D] -> [B,T,num_groups,D]`` summing each run of ``Hv/num_groups`` heads
     (reference: ``ops/utils/group_reduce.py:60-79``)."""
@@ -262,6 +289,7 @@ def group_reduce_vector(x, num_groups: int):
     return out
 
 
+@on_tensor_device
 def warmup_scan(g_cum, seg_cu_seqlens, threshold: float = -10.0, from_start: bool = False,
                 keep=None):
     """Per (segment, head) warm-up chunk count and fallback flag, both int32 ``[n_seg, Hv]``
@@ -280,6 +308,7 @@ def warmup_scan(g_cum, seg_cu_seqlens, threshold: float = -10.0, from_start: boo
     return warm, fallback
 
 
+@on_tensor_device
 def merge_states(local, M, use_m, raw, seg_begin, reverse: bool = False):
     """Chain the segment states of every raw sequence; returns the per-segment start states
     (or, reversed, end gradients) fp32 ``[n_seg, Hv, D, D]``

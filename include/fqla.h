@@ -132,6 +132,13 @@ int fqla_merge_states(const float* local, const float* M, const int* use_m, cons
  * reference (its kernels wait without bound). */
 int fqla_device_status(int* out, int reset);
 
+/* Self-test of the failure path every tensor-core kernel of this library shares: launches one
+ * tiny kernel whose single waiter gives up on a barrier that nothing arrives at, after `tries`
+ * (1..100) bounded tries of at most 1 ms each.  The kernel returns by itself and leaves the
+ * device status word set, so fqla_device_status then reports 1 until it is reset.  Nothing
+ * faults, traps or hangs.  No counterpart in the reference (its kernels wait without bound). */
+int fqla_selftest_wait_timeout(int tries, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -65,7 +65,8 @@ def _worker_tshard(rank, world, port, out):
     eye = torch.eye(D, dtype=torch.float64).expand(1, H, D, D)
     M = orc.chunk_gdr_fwd(q, k, torch.zeros_like(v), g, b, None, eye)[4]
     use_m = torch.ones(1, H, dtype=torch.int32)
-    start = fd.exchange_forward(local, M, use_m, x["h0"], merge_fn=cpu_merge)
+    # only the owning rank passes the edge state: the collective sequence must not depend on it
+    start = fd.exchange_forward(local, M, use_m, x["h0"] if rank == 0 else None, merge_fn=cpu_merge)
     want = h_full[0, rank * per // 64].unsqueeze(0)
     err_state = float((start - want).norm() / want.norm())
     # running the shard from the exchanged state reproduces the unsplit outputs
@@ -76,7 +77,8 @@ def _worker_tshard(rank, world, port, out):
     gen = torch.Generator().manual_seed(100 + rank)
     loc_b = torch.randn(1, H, D, D, generator=gen, dtype=torch.float64)
     dht = torch.randn(1, H, D, D, generator=torch.Generator().manual_seed(7), dtype=torch.float64)
-    end = fd.exchange_backward(loc_b, M, use_m, dht, merge_fn=cpu_merge)
+    end = fd.exchange_backward(loc_b, M, use_m, dht if rank == world - 1 else None,
+                               merge_fn=cpu_merge)
     locs = [torch.randn(1, H, D, D, generator=torch.Generator().manual_seed(100 + r),
                         dtype=torch.float64) for r in range(world)]
     Ms = [torch.empty_like(M) for _ in range(world)]

@@ -203,7 +203,8 @@ def test_forward_cache_tiles_replace_the_recomputation(cu, T):
     operand tiles; they equal what the backward's own state-only pass produces, and the backward
     returns the same gradients with or without them."""
     import flashqla_b200 as fq
-    from flashqla_b200 import api, ops
+    import flash_qla.ops.gated_delta_rule.chunk as api
+    from flashqla_b200 import ops
 
     d = _inputs(T, 2, 4, seed=47, cu=cu)
     cu_t = d["cu_seqlens"]
@@ -231,3 +232,44 @@ def test_forward_cache_tiles_replace_the_recomputation(cu, T):
     finally:
         api.SAVE_STATE_TILES = True
     assert cache_off is None or cache_off[1] is None
+
+
+def test_bounded_wait_runs_out_and_reports_through_the_status_word():
+    """The failure path every tcgen05 kernel shares: a wait whose barrier nobody arrives at gives
+    up after its budget, the kernel returns by itself, the device status word reads 1 until it is
+    reset, and the launches that follow are unaffected (bit-identical to the ones before)."""
+    import ctypes
+
+    from flashqla_b200 import _lib, ops
+
+    lib = _lib.load()
+    d = _inputs(256, 1, 2, seed=61)
+    scale = 128 ** -0.5
+    g_cum, A = ops.kkt_solve(d["k"], d["beta"], d["g"], None, raw_gate=True)
+    run = lambda: ops.fwd_seq(d["q"], d["k"], d["v"], A, g_cum, d["beta"], scale, d["h0"],  # noqa: E731
+                              output_final_state=True)
+    before = run()
+    torch.cuda.synchronize()
+    status = ctypes.c_int(-1)
+    assert lib.fqla_device_status(ctypes.byref(status), 0) == 0 and status.value == 0
+    assert lib.fqla_selftest_wait_timeout(3, torch.cuda.current_stream().cuda_stream) == 0
+    torch.cuda.synchronize()  # the kernel comes back by itself after about 3 ms
+    assert lib.fqla_device_status(ctypes.byref(status), 1) == 0 and status.value == 1
+    assert lib.fqla_device_status(ctypes.byref(status), 0) == 0 and status.value == 0
+    after = run()
+    torch.cuda.synchronize()
+    assert torch.equal(before["o"], after["o"]) and torch.equal(before["ht"], after["ht"])
+    assert lib.fqla_selftest_wait_timeout(0, None) == -1
+
+
+def test_float16_inputs_are_accepted_and_computed_in_bfloat16():
+    import flashqla_b200 as fq
+
+    d = _inputs(320, 2, 4, seed=62)
+    o_bf, ht_bf = fq.chunk_gated_delta_rule(d["q"], d["k"], d["v"], d["g"], d["beta"],
+                                            initial_state=d["h0"], output_final_state=True)
+    h = {n: d[n].to(torch.float16) for n in ("q", "k", "v")}  # bf16 values are exact in fp16 here
+    o_h, ht_h = fq.chunk_gated_delta_rule(h["q"], h["k"], h["v"], d["g"], d["beta"],
+                                          initial_state=d["h0"], output_final_state=True)
+    assert o_h.dtype == torch.float16
+    assert orc.rel_err(o_h.float(), o_bf.float()) < 2e-3 and orc.rel_err(ht_h, ht_bf) < 1e-6

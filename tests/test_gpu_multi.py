@@ -1,5 +1,7 @@
-"""T sharding and head sharding on two real GPUs (NCCL), against the single-GPU result of the
-same operator.  Skipped when fewer than two GPUs are visible."""
+"""T sharding and head sharding on two real GPUs (NCCL), against the fp32 CPU oracle (the
+parity bar: 5e-3 forward, 1e-2 gradients) and against the single-GPU result of the same operator.
+The edge states are passed on their owning rank only.  Skipped when fewer than two GPUs are
+visible."""
 
 import datetime
 import os
@@ -50,19 +52,33 @@ def _worker(rank, world, port, gate, out):
         bf["q"], bf["k"], bf["v"], d["g"], bf["beta"], None, d["h0"], auto_cp=False)
     ref = fq.chunk_gated_delta_rule_bwd(bf["q"], bf["k"], bf["v"], g_cum, bf["beta"], A, bf["do"],
                                         d["dht"], None, d["h0"], auto_cp=False)
+    # the oracle over the whole sequence, on the host
+    o_ref, ht_ref = orc.chunk_gdr_fwd(x["q"], x["k"], x["v"], x["g"], x["beta"], None, x["h0"])[2::2]
+    g_ref = orc.chunk_gdr_bwd(x["q"], x["k"], x["v"], x["g"], x["beta"], x["do"], x["dht"], None,
+                              x["h0"])
     # T-sharded
     per = T // world
     sl = slice(rank * per, (rank + 1) * per)
     loc = {n: bf[n][:, sl].contiguous() for n in bf}
     g_loc = d["g"][:, sl].contiguous()
-    g_cum_l, A_l, o_l, ht_l, saved = fd.fwd_tsharded(loc["q"], loc["k"], loc["v"], g_loc,
-                                                     loc["beta"], None, d["h0"])
+    g_cum_l, A_l, o_l, ht_l, saved = fd.fwd_tsharded(
+        loc["q"], loc["k"], loc["v"], g_loc, loc["beta"], None, d["h0"] if rank == 0 else None,
+        for_backward=True)
     grads = fd.bwd_tsharded(loc["q"], loc["k"], loc["v"], g_cum_l, loc["beta"], A_l, loc["do"],
-                            d["dht"], None, saved)
+                            d["dht"] if rank == world - 1 else None, None, saved)
     errs = {"o": _rel(o_l, o[:, sl]), "ht": _rel(ht_l, ht)}
     for name, got, want in zip(("dq", "dk", "dv", "db", "dg"), grads[:5], ref[:5]):
         errs[name] = _rel(got.float(), want[:, sl].float())
     errs["dh0"] = _rel(grads[5], ref[5])
+    errs["oracle_o"], errs["oracle_ht"] = _rel(o_l, o_ref[:, sl]), _rel(ht_l, ht_ref)
+    for name, got, want in zip(("dq", "dk", "dv", "db", "dg"), grads[:5], g_ref[:5]):
+        errs["oracle_" + name] = _rel(got.float(), want[:, sl])
+    errs["oracle_dh0"] = _rel(grads[5], g_ref[5])
+    # without the forward's tiles the backward recomputes them: same gradients, bit for bit
+    again = fd.bwd_tsharded(loc["q"], loc["k"], loc["v"], g_cum_l, loc["beta"], A_l, loc["do"],
+                            d["dht"] if rank == world - 1 else None, None,
+                            (saved[0], saved[1], None))
+    errs["recompute_differs"] = float(any(not torch.equal(a, b) for a, b in zip(grads, again)))
     # head sharding: this rank's heads of the full problem equal the slice of the full result
     qs, ks, vs, gs, bs, hs = fd.shard_heads(bf["q"], bf["k"], bf["v"], d["g"], bf["beta"], rank,
                                             world, d["h0"])
@@ -90,3 +106,6 @@ def test_two_gpu_sharding_matches_single_gpu(gate):
             assert max(errs[n] for n in ("o", "ht")) < 8e-3, errs
             assert max(errs[n] for n in ("dq", "dk", "dv", "db", "dg", "dh0")) < 1.5e-2, errs
             assert errs["o_heads"] < 1e-6 and errs["ht_heads"] < 1e-6, errs
+            assert max(errs[n] for n in ("oracle_o", "oracle_ht")) <= 5e-3, errs
+            assert max(errs["oracle_" + n] for n in ("dq", "dk", "dv", "db", "dg", "dh0")) <= 1e-2, errs
+            assert errs["recompute_differs"] == 0.0, errs

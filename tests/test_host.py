@@ -131,14 +131,20 @@ def test_pack_helpers_round_trip():
 
 
 def test_backward_returns_one_gradient_per_forward_input():
-    """Same check as the reference's tests/test_function_signature.py:43-66, on this package."""
-    tree = ast.parse(open(os.path.join(ROOT, "flashqla_b200", "api.py")).read())
-    cls = next(n for n in ast.walk(tree)
+    """The check of the reference's tests/test_function_signature.py:43-66 with its own lookup
+    rules: the class is a top-level definition of flash_qla/ops/gated_delta_rule/chunk/__init__.py,
+    ``forward`` starts with ``ctx``, ``backward`` has exactly one ``return`` and it is a tuple
+    literal with one element per non-ctx input."""
+    path = os.path.join(ROOT, "flash_qla", "ops", "gated_delta_rule", "chunk", "__init__.py")
+    tree = ast.parse(open(path).read())
+    cls = next(n for n in tree.body
                if isinstance(n, ast.ClassDef) and n.name == "ChunkGatedDeltaRuleFunction")
     fns = {n.name: n for n in cls.body if isinstance(n, ast.FunctionDef)}
-    n_inputs = len(fns["forward"].args.args) - 1  # minus ctx
-    ret = next(n for n in ast.walk(fns["backward"]) if isinstance(n, ast.Return))
-    assert isinstance(ret.value, ast.Tuple) and len(ret.value.elts) == n_inputs
+    assert fns["forward"].args.args[0].arg == "ctx"
+    n_inputs = len(fns["forward"].args.args) - 1
+    returns = [n for n in ast.walk(fns["backward"]) if isinstance(n, ast.Return)]
+    assert len(returns) == 1 and isinstance(returns[0].value, ast.Tuple)
+    assert len(returns[0].value.elts) == n_inputs == 13
 
 
 def test_drop_in_package_paths():

@@ -93,3 +93,24 @@ def test_index_tables_match_reference_golden():
             assert total == int(z[name + "_total"])
     assert prepare_chunk_indices(torch.tensor([0, 100, 356, 512]), 64).tolist() == [
         [0, 0], [0, 1], [1, 0], [1, 1], [1, 2], [1, 3], [2, 0], [2, 1], [2, 2]]
+
+
+def test_reference_copy_reproduces_its_golden_vectors_when_present():
+    """Where ``oracle/_ref`` holds the reference's own ``tests/ref_gdr.py`` (the file the CPU
+    baseline of the benchmark times), it must reproduce the committed golden vectors, which were
+    generated from that same file."""
+    from oracle import ref_loader
+
+    if not ref_loader.available():
+        pytest.skip("oracle/_ref is not populated on this machine")
+    ref = ref_loader.load()
+    for name in CASES:
+        x, want = load_case(name)
+        d = {n: x[n].double() for n in ("q", "k", "v", "g", "beta", "h0", "do", "dht")}
+        g, o, A, h, ht = ref.chunk_gated_delta_rule_fwd(d["q"], d["k"], d["v"], d["g"], d["beta"],
+                                                        x["cu_seqlens"], d["h0"], x["scale"])
+        assert orc.rel_err(o, want["o"]) < TIGHT and orc.rel_err(ht, want["ht"]) < TIGHT
+        grads = ref.chunk_gated_delta_rule_bwd(d["q"], d["k"], d["v"], g, d["beta"], A, x["scale"],
+                                               d["h0"], d["do"], d["dht"], x["cu_seqlens"])
+        for got, n in zip(grads, ("dq", "dk", "dv", "db", "dg", "dh0")):
+            assert orc.rel_err(got, want[n]) < TIGHT, (name, n)
