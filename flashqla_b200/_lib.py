@@ -25,6 +25,7 @@ SIGNATURES = {
     "fqla_merge_states": [P, P, P, P, P, P, I, I, I, I, P],
     "fqla_device_status": [P, I],
     "fqla_selftest_wait_timeout": [I, P],
+    "fqla_fwd_noalloc": [P, P, P, P, P, I, P, P, P, I, I, I, I, I, F, P, P, P, I, I, LL, P],
 }
 
 _lib = None
@@ -49,6 +50,8 @@ def load():
     lib.fqla_version.argtypes = []
     lib.fqla_status_string.restype = C.c_char_p
     lib.fqla_status_string.argtypes = [I]
+    lib.fqla_fwd_noalloc_max_pairs.restype = LL
+    lib.fqla_fwd_noalloc_max_pairs.argtypes = []
     for name, argtypes in SIGNATURES.items():
         fn = getattr(lib, name)
         fn.restype = I

@@ -10,6 +10,7 @@ extern "C" const char* fqla_status_string(int status) {
     case FQLA_OK: return "ok";
     case FQLA_ERR_INVALID_ARG: return "invalid argument";
     case FQLA_ERR_UNSUPPORTED_DIM: return "unsupported head dimension (64 or 128 only)";
+    case FQLA_ERR_TOO_LARGE: return "problem larger than the fixed scratch array of this entry point";
     default: break;
   }
   if (status > 0) return cudaGetErrorString((cudaError_t)status);

@@ -34,6 +34,7 @@ extern "C" {
 #define FQLA_OK 0
 #define FQLA_ERR_INVALID_ARG (-1)
 #define FQLA_ERR_UNSUPPORTED_DIM (-2)
+#define FQLA_ERR_TOO_LARGE (-3)
 
 /* ABI version, bumped on any signature change. */
 int fqla_version(void);
@@ -125,6 +126,34 @@ int fqla_warmup_scan(const float* g_cum, int T, int Hv, const void* seg_cu_seqle
 int fqla_merge_states(const float* local, const float* M, const int* use_m, const float* raw,
                       const int* seg_begin, float* out, int n_raw, int Hv, int D, int reverse,
                       void* stream);
+
+/* Forward (o and, optionally, the final state ht) for hosts that cannot allocate device memory
+ * where they call this library: an inference engine that gave all device memory to its own arena
+ * at start-up, so that a later cudaMalloc stalls the device or simply fails, or a plugin that
+ * only receives pointers and a stream from its framework.  No counterpart in the reference (its
+ * wrappers allocate with torch on every call).
+ *
+ * The two intermediates of the forward (the chunk-local cumulative gate and the matrix A, which
+ * fqla_kkt_solve otherwise writes into caller buffers) live in a fixed array inside the library
+ * image, 4.125 MiB that every GPU loading the library holds until the process exits.  The call
+ * runs the same kernels as fqla_kkt_solve (raw gate form) followed by fqla_fwd_seq and performs
+ * no cudaMalloc, cudaFree or other allocating call.
+ *   - g is the RAW per-token log gate [B,T,Hv] fp32; q, k, v, beta, h0, ht, o and the index
+ *     tables are as for fqla_fwd_seq / fqla_kkt_solve; ht may be NULL.
+ *   - Limit: B * T * Hv <= fqla_fwd_noalloc_max_pairs() (32768, e.g. 2048 tokens x 16 value
+ *     heads); larger calls return FQLA_ERR_TOO_LARGE and launch nothing.
+ *   - The first call on each device looks the array's device address up (with that device
+ *     current); make that first call outside any stream capture.
+ *   - All calls on one device share the array and it keeps the previous call's contents (what
+ *     must be clean is cleared by the call itself).  Two calls that may run at the same time on
+ *     the GPU, from different streams or threads, race on it: order them on one stream or with
+ *     events. */
+int fqla_fwd_noalloc(const void* q, const void* k, const void* v, const float* g,
+                     const void* beta, int beta_is_f32, const float* h0, float* ht, void* o,
+                     int B, int T, int Hq, int Hv, int D, float scale, const void* cu_seqlens,
+                     const void* chunk_offsets, const void* chunk_indices, int idx_is64, int N,
+                     long long num_chunks, void* stream);
+long long fqla_fwd_noalloc_max_pairs(void);
 
 /* Host call: reads (and with reset != 0 clears) the device-side status word of the current
  * device.  It is non-zero after a kernel abandoned a bounded wait on one of its barriers; the

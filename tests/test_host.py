@@ -29,7 +29,8 @@ def test_library_exports_every_declared_symbol(lib):
         assert hasattr(raw, name), f"{name} declared in include/fqla.h but not exported"
     from flashqla_b200._lib import SIGNATURES
 
-    assert set(SIGNATURES) | {"fqla_version", "fqla_status_string"} == declared
+    assert set(SIGNATURES) | {"fqla_version", "fqla_status_string",
+                              "fqla_fwd_noalloc_max_pairs"} == declared
     assert lib.fqla_version() >= 1
     assert lib.fqla_status_string(0) == b"ok"
     assert b"invalid" in lib.fqla_status_string(-1)
