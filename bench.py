@@ -340,10 +340,10 @@ def dominant_kernel_roofline(timer, x, bwd, steps):
     B_, T_ = x["q"].shape[:2]
     tables = ops.SeqTables(B_, T_, x["cu"])
     plan = cp.plan_segments(tables, x["Hv"], device=x["q"].device)
-    run_tables, run_h0 = tables, x["h0"]
+    run_tables, run_h0, lead = tables, x["h0"], None
     if plan is not None:
         run_tables = plan.seg_tables
-        run_h0 = cp.forward_segment_states(plan, x["k"], x["v"], A, g_cum, x["beta"], scale, x["h0"])
+        run_h0, lead = cp.forward_start(plan, x["k"], x["v"], A, g_cum, x["beta"], scale, x["h0"])
     G = x["Hv"] // x["Hq"]
     pairs = x["tokens"] * x["Hv"]
     if not bwd:
@@ -351,13 +351,14 @@ def dominant_kernel_roofline(timer, x, bwd, steps):
 
         def dominant():
             ops.fwd_seq(x["q"], x["k"], x["v"], A, g_cum, x["beta"], scale, run_h0,
-                        output_final_state=True, tables=run_tables)
+                        output_final_state=True, tables=run_tables, lead_chunks=lead)
 
         min_bytes, kernel_bytes, flop_per_pair = fwd_min_bytes(G), fwd_kernel_bytes(G), 147_456
     else:
         kernel_name = "bwd_main_tc_kernel"
         fw = ops.fwd_seq(None, x["k"], x["v"], A, g_cum, x["beta"], scale, run_h0, output_o=False,
-                         output_h=True, output_vnew=True, tables=run_tables, operand_tiles=True)
+                         output_h=True, output_vnew=True, tables=run_tables, operand_tiles=True,
+                         lead_chunks=lead)
         bw = ops.bwd_dh(x["q"], x["k"], A, g_cum, x["beta"], x["do"], scale, None,
                         tables=run_tables, operand_tiles=True)
 

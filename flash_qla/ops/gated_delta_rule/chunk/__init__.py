@@ -67,19 +67,31 @@ def _tiles_ok(D: int) -> bool:
     return D == 128 and os.environ.get("FQLA_FORCE_MMA_SYNC") is None
 
 
+def _segment_starts(plan, k, v, A, g_cum, beta, scale, h0):
+    """``(segment start states, lead-in chunk counts or None)`` of a split plan.  The tcgen05
+    recurrence kernel (K = V = 128) leads in by itself; the mma.sync kernels take explicit start
+    states for every segment."""
+    if cp.LEAD_IN and _tiles_ok(k.shape[-1]):
+        return cp.forward_start(plan, k, v, A, g_cum, beta, scale, h0)
+    return cp.forward_segment_states(plan, k, v, A, g_cum, beta, scale, h0), None
+
+
 def run_forward(q, k, v, A, g_cum, beta, scale, h0, tables, output_final_state=True,
                 output_h=False, auto_cp=True, enable_fwd_cp_cache=False):
     """The part of the forward after cumsum and kkt+solve: optional split into segments with
     state hand-off, then the sequential recurrence.  Returns ``(outputs dict, cp_cache)``;
-    ``cp_cache`` is ``(segment initial states or None, h tiles or None, v_new tiles or None)``."""
+    ``cp_cache`` is ``(segment initial states or None, h tiles or None, v_new tiles or None,
+    lead-in chunk counts or None)``."""
     plan = cp.plan_segments(tables, v.shape[2], is_bwd=False, device=k.device) if auto_cp else None
     keep = enable_fwd_cp_cache and SAVE_STATE_TILES and not output_h and _tiles_ok(k.shape[-1])
     extra = dict(output_h=True, output_vnew=True, operand_tiles=True) if keep else dict(output_h=output_h)
     cp_cache = None
+    lead = None
     if plan is not None:
-        seg_h0 = cp.forward_segment_states(plan, k, v, A, g_cum, beta, scale, h0)
+        seg_h0, lead = _segment_starts(plan, k, v, A, g_cum, beta, scale, h0)
         res = ops.fwd_seq(q, k, v, A, g_cum, beta, scale, seg_h0,
-                          output_final_state=output_final_state, tables=plan.seg_tables, **extra)
+                          output_final_state=output_final_state, tables=plan.seg_tables,
+                          lead_chunks=lead, **extra)
         if output_final_state:
             res["ht"] = res["ht"][plan.last_seg_of_raw]
     else:
@@ -87,9 +99,9 @@ def run_forward(q, k, v, A, g_cum, beta, scale, h0, tables, output_final_state=T
         res = ops.fwd_seq(q, k, v, A, g_cum, beta, scale, h0,
                           output_final_state=output_final_state, tables=tables, **extra)
     if keep:
-        cp_cache = (seg_h0, res.pop("h"), res.pop("vnew"))
+        cp_cache = (seg_h0, res.pop("h"), res.pop("vnew"), lead)
     elif enable_fwd_cp_cache and seg_h0 is not None:
-        cp_cache = (seg_h0, None, None)
+        cp_cache = (seg_h0, None, None, lead)
     return res, cp_cache
 
 
@@ -165,13 +177,14 @@ def chunk_gated_delta_rule_bwd(
     h0 = _state_in(initial_state, state_v_first)
     dht_k = _state_in(dht, state_v_first)
 
-    cached = tuple(cp_cache) + (None, None, None) if cp_cache is not None else (None, None, None)
+    cached = (tuple(cp_cache) if cp_cache is not None else ()) + (None, None, None, None)
     plan = cp.plan_segments(tables, Hv, is_bwd=True, device=k.device) if auto_cp else None
+    lead = None
     if plan is not None:
         if cached[0] is not None:
-            seg_h0 = cached[0]
+            seg_h0, lead = cached[0], cached[3]
         else:
-            seg_h0 = cp.forward_segment_states(plan, k, v, A, g, beta_k, scale, h0)
+            seg_h0, lead = _segment_starts(plan, k, v, A, g, beta_k, scale, h0)
         seg_dht = cp.backward_segment_states(plan, q, k, v, A, g, beta_k, do, scale, dht_k)
         run_tables, run_h0, run_dht = plan.seg_tables, seg_h0, seg_dht
     else:
@@ -184,7 +197,8 @@ def chunk_gated_delta_rule_bwd(
         fw = {"h": cached[1], "vnew": cached[2]}  # kept by the forward: no recomputation
     else:
         fw = ops.fwd_seq(None, k, v, A, g, beta_k, scale, run_h0, output_o=False, output_h=True,
-                         output_vnew=True, tables=run_tables, operand_tiles=tiles)
+                         output_vnew=True, tables=run_tables, operand_tiles=tiles,
+                         lead_chunks=lead if tiles else None)
     bw = ops.bwd_dh(q, k, A, g, beta_k, do, scale, run_dht, tables=run_tables,
                     operand_tiles=tiles)
     dq, dk, dv, db, dg = ops.bwd_main(q, k, v, fw["vnew"], A, g, beta_k, do, bw["du"], fw["h"],

@@ -33,7 +33,11 @@ THRESHOLD = -10.0
 MIN_SEGMENT_CHUNKS = 8
 FILL_FRACTION = 0.75  # split only when the raw streams fill less than this share of the SMs
 VALUE_SLICES = 1  # CTAs per (segment, head) of the tcgen05 forward kernel
-SEGMENT_OVERHEAD_CHUNKS = 3  # cost of a hand-off, in chunk steps of the main kernel
+SEGMENT_OVERHEAD_CHUNKS = 2  # cost of a hand-off, in chunk steps of the main kernel
+# True: the tcgen05 recurrence kernel starts a segment a few chunks early from a zero state
+# (``forward_start``); False: every segment's start state comes from the separate state-only pass
+# and the merge chain (``forward_segment_states``), as the mma.sync kernels always do.
+LEAD_IN = True
 
 
 def sm_count(device) -> int:
@@ -162,6 +166,25 @@ def forward_segment_states(plan: SegmentPlan, k, v, A, g_cum, beta, scale, h0):
                       output_final_state=True, output_m=True, warm_chunks=warm,
                       m_mask=fallback, tables=seg)
     return ops.merge_states(res["ht"], res["M"], fallback, h0, plan.seg_begin, reverse=False)
+
+
+def forward_start(plan: SegmentPlan, k, v, A, g_cum, beta, scale, h0):
+    """How every segment of a split plan gets its start state, for the tcgen05 recurrence kernel:
+    returns ``(seg_h0, lead)``.  Where no segment of a (sequence, head) falls back, segment ``i``
+    just starts ``lead[i]`` chunks early from a zero state inside the recurrence kernel itself,
+    and the three launches below find nothing to do for it (the scan is the only one that costs
+    more than a launch); ``seg_h0`` then only carries the sequence's own initial state.  Where
+    some segment falls back (gates too weak for the past to die out inside a segment) the exact
+    chain of ``forward_segment_states`` runs for that (sequence, head) and ``lead`` is 0."""
+    seg = plan.seg_tables
+    _, fallback, lead, exact_warm, any_fb = ops.segment_scan(g_cum, seg.cu, plan.seg_begin,
+                                                             THRESHOLD, from_start=False)
+    res = ops.fwd_seq(None, k, v, A, g_cum, beta, scale, None, output_o=False,
+                      output_final_state=True, output_m=True, warm_chunks=exact_warm,
+                      m_mask=fallback, tables=seg)
+    seg_h0 = ops.merge_states(res["ht"], res["M"], fallback, h0, plan.seg_begin, reverse=False,
+                              any_fallback=any_fb)
+    return seg_h0, lead
 
 
 def backward_segment_states(plan: SegmentPlan, q, k, v, A, g_cum, beta, do, scale, dht):

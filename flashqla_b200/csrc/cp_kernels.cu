@@ -13,23 +13,14 @@
 
 namespace fqla {
 
-// One warp per (segment, head).  Walks the chunk totals (the cumsum value on each chunk's last
-// row) from the segment end backwards (forward pass) or from its start forwards (backward pass),
-// 32 chunks per step: the lanes load in parallel, a warp prefix sum finds the first crossing.
-// keep (optional, [n_seg]): segments with keep == 0 hand nothing on; they get warm = fallback = 0.
-__global__ void __launch_bounds__(128)
-warmup_scan_kernel(const float* __restrict__ g_cum, int Hv, SeqLayout lay, int n_seg,
-                   float threshold, int from_start, const int* __restrict__ keep,
-                   int* __restrict__ warm, int* __restrict__ fallback) {
-  const int lane = threadIdx.x & 31;
-  const int item = blockIdx.x * 4 + (threadIdx.x >> 5);
-  if (item >= n_seg * Hv) return;
-  const int seg = item / Hv, hv = item % Hv;
-  if (keep && keep[seg] == 0) {
-    if (lane == 0) warm[item] = fallback[item] = 0;
-    return;
-  }
-  const SeqSpan sp = lay.span(seg);
+// Whole-warp scan of one (segment, head).  Walks the chunk totals (the cumsum value on each
+// chunk's last row) from the segment end backwards (forward pass) or from its start forwards
+// (backward pass), 32 chunks per step: the lanes load in parallel, a warp prefix sum finds the
+// first crossing.  Returns the chunk count in every lane; `reached` tells whether the threshold
+// was crossed inside the segment.
+__device__ __forceinline__ int scan_segment(const float* __restrict__ g_cum, int Hv, int hv,
+                                            const SeqSpan sp, float threshold, int from_start,
+                                            int lane, bool& reached_out) {
   float carry = 0.f;
   int n = sp.n_chunks;
   bool reached = false;
@@ -54,9 +45,69 @@ warmup_scan_kernel(const float* __restrict__ g_cum, int Hv, SeqLayout lay, int n
     }
     carry += __shfl_sync(0xffffffffu, x, 31);
   }
+  reached_out = reached;
+  return n;
+}
+
+// One warp per (segment, head).  keep (optional, [n_seg]): segments with keep == 0 hand nothing
+// on; they get warm = fallback = 0.
+__global__ void __launch_bounds__(128)
+warmup_scan_kernel(const float* __restrict__ g_cum, int Hv, SeqLayout lay, int n_seg,
+                   float threshold, int from_start, const int* __restrict__ keep,
+                   int* __restrict__ warm, int* __restrict__ fallback) {
+  const int lane = threadIdx.x & 31;
+  const int item = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (item >= n_seg * Hv) return;
+  const int seg = item / Hv, hv = item % Hv;
+  if (keep && keep[seg] == 0) {
+    if (lane == 0) warm[item] = fallback[item] = 0;
+    return;
+  }
+  bool reached;
+  const int n = scan_segment(g_cum, Hv, hv, lay.span(seg), threshold, from_start, lane, reached);
   if (lane == 0) {
     warm[item] = n;
     fallback[item] = reached ? 0 : 1;
+  }
+}
+
+// The scan for a whole split plan in one launch: one CTA per (raw sequence, head), its warps take
+// the segments of that sequence in turn.  Besides warm / fallback per (segment, head) (same
+// meaning as above; the segment that hands nothing on, last of its sequence forward or first
+// backward, gets 0 / 0) it decides HOW each segment gets its start state:
+//   * no segment of this (sequence, head) fell back (any_fb = 0): the recurrence kernel of segment
+//     i simply starts lead[i] chunks early from a zero state (lead-in, forward: lead[i] =
+//     warm[i - 1]; backward: lead[i] = warm[i + 1]); no local states, no merge chain;
+//     exact_warm = -1 tells the separate state-only pass to skip the segment;
+//   * otherwise (any_fb = 1) lead = 0 everywhere and exact_warm = warm: the state-only pass,
+//     the transition matrices and the merge chain produce the exact start states.
+__global__ void __launch_bounds__(256)
+segment_scan_kernel(const float* __restrict__ g_cum, int Hv, SeqLayout lay,
+                    const int* __restrict__ seg_begin, float threshold, int from_start,
+                    int* __restrict__ warm, int* __restrict__ fallback, int* __restrict__ lead,
+                    int* __restrict__ exact_warm, int* __restrict__ any_fb) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int r = blockIdx.x / Hv, hv = blockIdx.x % Hv;
+  const int s0 = seg_begin[r], s1 = seg_begin[r + 1];
+  int fb_any = 0;
+  for (int seg = s0 + warp; seg < s1; seg += 8) {
+    const bool hands_on = from_start ? seg > s0 : seg + 1 < s1;
+    int n = 0;
+    bool reached = true;
+    if (hands_on) n = scan_segment(g_cum, Hv, hv, lay.span(seg), threshold, from_start, lane, reached);
+    if (lane == 0) {
+      warm[seg * Hv + hv] = n;
+      fallback[seg * Hv + hv] = reached ? 0 : 1;
+    }
+    fb_any |= reached ? 0 : 1;
+  }
+  const int any = __syncthreads_or(fb_any);  // also orders the writes above for the reads below
+  if (threadIdx.x == 0) any_fb[r * Hv + hv] = any;
+  for (int seg = s0 + threadIdx.x; seg < s1; seg += blockDim.x) {
+    const int giver = from_start ? seg + 1 : seg - 1;  // the segment whose tail/head leads in
+    const bool has = from_start ? giver < s1 : giver >= s0;
+    lead[seg * Hv + hv] = (!any && has) ? warm[giver * Hv + hv] : 0;
+    exact_warm[seg * Hv + hv] = any ? warm[seg * Hv + hv] : -1;
   }
 }
 
@@ -70,6 +121,7 @@ __global__ void __launch_bounds__(D) merge_kernel(const float* __restrict__ loca
                                                   const int* __restrict__ use_m,
                                                   const float* __restrict__ raw,
                                                   const int* __restrict__ seg_begin,
+                                                  const int* __restrict__ any_fb,
                                                   float* __restrict__ out, int Hv, int reverse) {
   constexpr int BV = 32, BK = 32, LDC = BV + 1;
   // all global traffic is one 128-byte row segment per warp instruction; the padded row stride
@@ -85,6 +137,15 @@ __global__ void __launch_bounds__(D) merge_kernel(const float* __restrict__ loca
   auto state = [&](const float* base, int seg) {
     return base + (((long long)seg * Hv + hv) * D) * D;
   };
+  if (any_fb && any_fb[r * Hv + hv] == 0) {
+    // no chain for this (sequence, head): the recurrence kernel leads in by itself; only the
+    // edge segment needs a state (the sequence's own initial state or final-state gradient)
+    const float* src = raw ? state(raw, r) : nullptr;
+    float* dst = const_cast<float*>(state(out, reverse ? s1 - 1 : s0));
+    for (int row = warp; row < D; row += D / 32)
+      dst[(long long)row * D + v0 + lane] = src ? src[(long long)row * D + v0 + lane] : 0.f;
+    return;
+  }
   // initial value
   {
     const float* src = raw ? state(raw, r) : nullptr;
@@ -163,18 +224,32 @@ extern "C" int fqla_warmup_scan(const float* g_cum, int T, int Hv, const void* s
   return (int)cudaGetLastError();
 }
 
+extern "C" int fqla_segment_scan(const float* g_cum, int T, int Hv, const void* seg_cu_seqlens,
+                                 int idx_is64, const int* seg_begin, int n_raw, float threshold,
+                                 int from_start, int* warm, int* fallback, int* lead,
+                                 int* exact_warm, int* any_fb, void* stream) {
+  if (!g_cum || !seg_cu_seqlens || !seg_begin || !warm || !fallback || !lead || !exact_warm ||
+      !any_fb || Hv <= 0)
+    return FQLA_ERR_INVALID_ARG;
+  if (n_raw <= 0) return FQLA_OK;
+  SeqLayout lay{{seg_cu_seqlens, idx_is64}, {seg_cu_seqlens, idx_is64}, T};
+  segment_scan_kernel<<<(unsigned)(n_raw * Hv), 256, 0, (cudaStream_t)stream>>>(
+      g_cum, Hv, lay, seg_begin, threshold, from_start, warm, fallback, lead, exact_warm, any_fb);
+  return (int)cudaGetLastError();
+}
+
 extern "C" int fqla_merge_states(const float* local, const float* M, const int* use_m,
-                                 const float* raw, const int* seg_begin, float* out, int n_raw,
-                                 int Hv, int D, int reverse, void* stream) {
+                                 const float* raw, const int* seg_begin, const int* any_fb,
+                                 float* out, int n_raw, int Hv, int D, int reverse, void* stream) {
   if (!local || !M || !seg_begin || !out || Hv <= 0) return FQLA_ERR_INVALID_ARG;
   if (n_raw <= 0) return FQLA_OK;
   cudaStream_t st = (cudaStream_t)stream;
   if (D == 128) {
     merge_kernel<128><<<dim3(128 / 32, Hv, n_raw), 128, 0, st>>>(local, M, use_m, raw, seg_begin,
-                                                                  out, Hv, reverse);
+                                                                  any_fb, out, Hv, reverse);
   } else if (D == 64) {
     merge_kernel<64><<<dim3(64 / 32, Hv, n_raw), 64, 0, st>>>(local, M, use_m, raw, seg_begin,
-                                                                out, Hv, reverse);
+                                                                any_fb, out, Hv, reverse);
   } else {
     return FQLA_ERR_UNSUPPORTED_DIM;
   }

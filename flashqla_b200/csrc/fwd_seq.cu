@@ -26,8 +26,8 @@ namespace fqla {
 // tcgen05 implementation of the full forward (fwd_tc.cu)
 int launch_fwd_tc(const void* q, const void* k, const void* v, const void* A, const float* g,
                   const void* beta, int beta_is_f32, const float* h0, float* ht, void* o, void* h,
-                  void* vnew, int tiled, int N, int Hq, int Hv, long long T_rows, float scale,
-                  SeqLayout lay, cudaStream_t st);
+                  void* vnew, int tiled, const int* lead, int N, int Hq, int Hv, long long T_rows,
+                  float scale, SeqLayout lay, cudaStream_t st);
 
 struct FwdSeqParams {
   const bf16* q;      // may be null (state-only pass)
@@ -106,7 +106,11 @@ __global__ void __launch_bounds__(256, 1) fwd_seq_kernel(const FwdSeqParams p) {
   if (!m_slice && !p.ht && !p.o && !p.h && !p.vnew) return;          // nothing asked of this slice
 
   int c_begin = 0;
-  if (p.warm) c_begin = max(0, sp.n_chunks - p.warm[n * p.Hv + hv]);
+  if (p.warm) {
+    const int w = p.warm[n * p.Hv + hv];
+    if (w < 0) return;  // nothing is wanted of this (sequence, head): no output is written
+    c_begin = max(0, sp.n_chunks - w);
+  }
 
   // ---- state in registers: rows 32*wm + mt*16 + ..., cols (BV/2)*wn + nt*8 + ...
   float S[MTS][NTV][4];
@@ -344,14 +348,15 @@ using namespace fqla;
 extern "C" int fqla_fwd_seq(const void* q, const void* k, const void* v, const void* A,
                             const float* g_cum, const void* beta, int beta_is_f32,
                             const float* h0, float* ht, void* o, void* h, void* vnew, float* M,
-                            const int* warm_chunks, const int* m_mask, int B, int T, int Hq,
-                            int Hv, int D, float scale, const void* cu_seqlens,
+                            const int* warm_chunks, const int* m_mask, const int* lead_chunks,
+                            int B, int T, int Hq, int Hv, int D, float scale, const void* cu_seqlens,
                             const void* chunk_offsets, int idx_is64, int N, int operand_tiles,
                             void* stream) {
   if (!k || !v || !A || !g_cum || !beta || Hq <= 0 || Hv % Hq) return FQLA_ERR_INVALID_ARG;
   if (cu_seqlens && (!chunk_offsets || B != 1)) return FQLA_ERR_INVALID_ARG;
   if (o && !q) return FQLA_ERR_INVALID_ARG;
   if (warm_chunks && (q || h || vnew)) return FQLA_ERR_INVALID_ARG;
+  if (lead_chunks && (warm_chunks || M || m_mask)) return FQLA_ERR_INVALID_ARG;
   FwdSeqParams p;
   p.q = (const bf16*)q; p.k = (const bf16*)k; p.v = (const bf16*)v; p.A = (const bf16*)A;
   p.g = g_cum; p.beta = beta; p.beta_is_f32 = beta_is_f32;
@@ -371,8 +376,8 @@ extern "C" int fqla_fwd_seq(const void* q, const void* k, const void* v, const v
   const bool full = q && o, recompute = !q && !o && (h || vnew);
   if (D == 128 && (full || recompute) && !M && !warm_chunks && !m_mask && !force_legacy)
     return launch_fwd_tc(q, k, v, A, g_cum, beta, beta_is_f32, h0, ht, o, h, vnew, operand_tiles,
-                         p.N, Hq, Hv, p.T_rows, scale, p.lay, st);
-  if (operand_tiles) return FQLA_ERR_UNSUPPORTED_DIM;  // only the tcgen05 kernel writes tiles
+                         lead_chunks, p.N, Hq, Hv, p.T_rows, scale, p.lay, st);
+  if (operand_tiles || lead_chunks) return FQLA_ERR_UNSUPPORTED_DIM;  // tcgen05 kernel only
   if (D == 128) return launch_fwd_seq<128>(p, st);
   if (D == 64) return launch_fwd_seq<64>(p, st);
   return FQLA_ERR_UNSUPPORTED_DIM;

@@ -66,6 +66,11 @@ struct FwdTcParams {
   SeqLayout lay;
   int profile;
   int tiled;  // h and vnew are written as operand tiles (h^T per chunk, v_new^T per chunk) by TMA
+  // [N, Hv] or null: lead-in.  A CTA with lead > 0 starts from a ZERO state `lead` chunks before
+  // its sequence (segment) and walks those chunks state-only (no q, no output, nothing stored):
+  // the rows just before a segment are the tail of the segment before it, whose influence dies
+  // out within `lead` chunks.  h0 is ignored for such a CTA.
+  const int* lead;
 };
 
 namespace fwdtc {
@@ -129,7 +134,9 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
   const int n = blockIdx.x / p.Hv, hv = blockIdx.x % p.Hv;
   const int hq = hv / (p.Hv / p.Hq);
   const SeqSpan sp = p.lay.span(n);
-  const int n_it = sp.n_chunks;
+  // iteration j handles chunk c = j - lead of the sequence; c < 0 are the lead-in chunks
+  const int lead = p.lead ? p.lead[n * p.Hv + hv] : 0;
+  const int n_it = sp.n_chunks == 0 ? 0 : sp.n_chunks + lead;
 
   if (tid == 0) {
     mbar_init(&bars[FULL0], 1);
@@ -207,7 +214,7 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
       float x[32];
 #pragma unroll
       for (int j = 0; j < 32; ++j)
-        x[j] = p.h0 ? p.h0[state_off + (long long)(k0 + j) * D + v] : 0.f;
+        x[j] = (p.h0 && lead == 0) ? p.h0[state_off + (long long)(k0 + j) * D + v] : 0.f;
       tmem_st32(tmem + lane_sel + TM_S + k0, x);
     }
     tmem_st_wait();
@@ -217,7 +224,8 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
       if (!ok) break;
       tc_fence_after();
       SEC_BEGIN();
-      bf16* hdst = (EXTRA && p.h) ? p.h + ((sp.chunk_base + it) * p.Hv + hv) * (long long)D * D : nullptr;
+      bf16* hdst = (EXTRA && p.h && it >= lead)
+                       ? p.h + ((sp.chunk_base + (it - lead)) * p.Hv + hv) * (long long)D * D : nullptr;
       // on the chain: the bf16 operand copy of S^T
 #pragma unroll 1
       for (int kb = 0; kb < 2; ++kb) {  // 64 columns (one operand block) per round
@@ -315,8 +323,9 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
     };
     if (n_it > 0) ok = convert_w(0);
     for (int it = 0; it < n_it && ok; ++it) {
-      const long long row0 = sp.bos + (long long)it * CHUNK;
-      const int valid = min(CHUNK, sp.len - it * CHUNK);
+      const int c = it - lead;
+      const long long row0 = sp.bos + (long long)c * CHUNK;
+      const int valid = c < 0 ? 0 : min(CHUNK, sp.len - c * CHUNK);  // 0: nothing is stored
       ok = WAIT(FULL0 + (it & 1), (it >> 1) & 1) && WAIT(VN_DONE, it & 1);
       if (!ok) break;
       tc_fence_after();
@@ -383,10 +392,13 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
     const int row_a = 16 * wq + (lane >> 2), row_b = row_a + 8, cp = 2 * (lane & 3);
     const uint32_t lanes_o = (uint32_t)(wq * 32) << 16;        // O1 / O2: lanes 0-15 of the quarter
     const uint32_t lanes_p = (uint32_t)(wq * 32 + 16) << 16;   // P: lanes 16-31
-    auto epilogue = [&](int it) {
-      const float* vs = vec + (it & 3) * VEC_SLOT_FLOATS;
-      const long long row0 = sp.bos + (long long)it * CHUNK;
-      const int valid = min(CHUNK, sp.len - it * CHUNK);
+    // c counts the chunks of the sequence itself; the lead-in chunks (iterations j < lead) have no
+    // output products, so the barriers of this group's products are phased by c, while stages and
+    // vector slots follow the iteration j = c + lead
+    auto epilogue = [&](int c) {
+      const float* vs = vec + ((c + lead) & 3) * VEC_SLOT_FLOATS;
+      const long long row0 = sp.bos + (long long)c * CHUNK;
+      const int valid = min(CHUNK, sp.len - c * CHUNK);
       const float sg_a = vs[V_SGAM * CHUNK + row_a], sg_b = vs[V_SGAM * CHUNK + row_b];
       bf16* o_a = p.o + ((row0 + row_a) * p.Hv + hv) * D + cp;
       bf16* o_b = p.o + ((row0 + row_b) * p.Hv + hv) * D + cp;
@@ -424,10 +436,13 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
       }
     };
     const float log2_scale = log2f(p.scale);
-    for (int it = 0; it < n_it && ok; ++it) {
-      const int s = it & 1;
-      const float* vs = vec + (it & 3) * VEC_SLOT_FLOATS;
-      ok = WAIT(FULL0 + s, (it >> 1) & 1);
+    const int n_out = n_it - lead;  // chunks with output
+    for (int it = 0; it < n_out && ok; ++it) {
+      const int j = it + lead;
+      const float* vs = vec + (j & 3) * VEC_SLOT_FLOATS;
+      // (after a lead-in of four or more chunks the first of these waits may see an older phase of
+      // the same parity; the wait for this chunk's P below is what orders the reads)
+      ok = WAIT(FULL0 + (j & 1), (j >> 1) & 1);
       if (!ok) break;
       if (it > 0) {
         ok = WAIT(O_DONE, (it - 1) & 1);
@@ -470,11 +485,11 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
       mbar_arrive(&bars[P_READY]);
       SEC_END(SEC_B);
     }
-    if (ok && n_it > 0) {
-      ok = WAIT(O_DONE, (n_it - 1) & 1);
+    if (ok && n_out > 0) {
+      ok = WAIT(O_DONE, (n_out - 1) & 1);
       if (ok) {
         tc_fence_after();
-        epilogue(n_it - 1);
+        epilogue(n_out - 1);
       }
     }
     // rows of o past the end of the last packed sequence come out zero
@@ -514,8 +529,8 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
         umma_commit(&bars[P_DONE]);
       };
       auto store_vn = [&](int it) {  // after VN_READY: the v_new^T tile is complete
-        if (p.tiled && p.vnew) {
-          tma_store_2d(&map_vn, 0, (int)(((sp.chunk_base + it) * p.Hv + hv) * D), smem + OFF_VNT);
+        if (p.tiled && p.vnew && it >= lead) {
+          tma_store_2d(&map_vn, 0, (int)(((sp.chunk_base + (it - lead)) * p.Hv + hv) * D), smem + OFF_VNT);
           tma_store_commit();
         }
       };
@@ -537,17 +552,18 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
         if constexpr (EXTRA) tma_store_wait_read();  // v_new^T of the chunk before has left its tile
         umma_commit(&bars[VN_DONE]);
         if constexpr (EXTRA) {
-          if (p.tiled && p.h) {  // the operand copy of S^T is the state entering this chunk
-            const int y = (int)(((sp.chunk_base + it) * p.Hv + hv) * D);
+          if (p.tiled && p.h && it >= lead) {  // the operand copy of S^T is the state entering this chunk
+            const int y = (int)(((sp.chunk_base + (it - lead)) * p.Hv + hv) * D);
             tma_store_2d(&map_h, 0, y, smem + OFF_ST);
             tma_store_2d(&map_h, 64, y, smem + OFF_ST + 16384);
             tma_store_commit();
           }
         }
         SEC_END(SEC_A);
-        if constexpr (!NO_O) {
-          if (it > 0) {
-            ok = WAIT(O_FREE, (it - 1) & 1);
+        const int c = it - lead;  // < 0: lead-in chunk, no output products
+        if (!NO_O && c >= 0) {
+          if (c > 0) {
+            ok = WAIT(O_FREE, (c - 1) & 1);
             if (!ok) break;
             tc_fence_after();
           }
@@ -580,13 +596,13 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
           SEC_END(SEC_D);
           if constexpr (EXTRA) store_vn(it);
         }
-        ok = (NO_O || WAIT(P_READY, it & 1)) && (it + 1 < n_it || WAIT(VN_READY, it & 1));
+        ok = (NO_O || c < 0 || WAIT(P_READY, c & 1)) && (it + 1 < n_it || WAIT(VN_READY, it & 1));
         if (!ok) break;
         tc_fence_after();
         if constexpr (EXTRA) {
           if (it + 1 >= n_it) store_vn(it);
         }
-        if constexpr (!NO_O) {
+        if (!NO_O && c >= 0) {
           SEC_BEGIN();
           // O2 = Pg Vn     (B = Vn^T copy: N = v rows, K = tok')
           umma_group<4, 2, 0, 2, 0, false>(tmem + TM_O2, p_lo, vnt_lo, ID_O);
@@ -599,9 +615,11 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
   } else if (warp == 1) {
     // =============================== producer ===============================
     float g_r[2] = {0.f, 0.f}, b_r[2] = {0.f, 0.f}, gl_r = 0.f;
+    // (lead-in chunks, c < 0, are whole chunks of the rows before the sequence)
     auto fetch = [&](int it) {
-      const long long row0 = sp.bos + (long long)it * CHUNK;
-      const int valid = min(CHUNK, sp.len - it * CHUNK);
+      const int c = it - lead;
+      const long long row0 = sp.bos + (long long)c * CHUNK;
+      const int valid = c < 0 ? CHUNK : min(CHUNK, sp.len - c * CHUNK);
       gl_r = p.g[(row0 + valid - 1) * p.Hv + hv];
 #pragma unroll
       for (int z = 0; z < 2; ++z) {
@@ -612,9 +630,9 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
     };
     // vectors and A tile of chunk j (its stage's A buffer is free once the prep warps have read it)
     auto a_part = [&](int j) {
-      const int sj = j & 1;
-      const long long row0 = sp.bos + (long long)j * CHUNK;
-      const int valid = min(CHUNK, sp.len - j * CHUNK);
+      const int sj = j & 1, c = j - lead;
+      const long long row0 = sp.bos + (long long)c * CHUNK;
+      const int valid = c < 0 ? CHUNK : min(CHUNK, sp.len - c * CHUNK);
       if (j >= 2 && !WAIT(EMPTYA0 + sj, ((j >> 1) - 1) & 1)) return false;
       float* vs = vec + (j & 3) * VEC_SLOT_FLOATS;
 #pragma unroll
@@ -654,9 +672,10 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
       if (n_it > 1) fetch(1);
     }
     for (int it = 0; it < n_it && ok; ++it) {
-      const int s = it & 1;
-      const long long row0 = sp.bos + (long long)it * CHUNK;
-      const int valid = min(CHUNK, sp.len - it * CHUNK);
+      const int s = it & 1, c = it - lead;
+      const long long row0 = sp.bos + (long long)c * CHUNK;
+      const int valid = c < 0 ? CHUNK : min(CHUNK, sp.len - c * CHUNK);
+      const bool with_q = !NO_O && c >= 0;
       if (it >= 2) {
         ok = WAIT(EMPTY0 + s, ((it >> 1) - 1) & 1);
         if (!ok) break;
@@ -665,13 +684,13 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
       const bool partial = valid < CHUNK;
       uint64_t* bar = partial ? &bars[PRIV] : &bars[FULL0 + s];
       if (lane == 0) {
-        mbar_arrive_expect_tx(bar, STAGE_BYTES - TILE_A - (NO_O ? TILE_QK : 0));
+        mbar_arrive_expect_tx(bar, STAGE_BYTES - TILE_A - (with_q ? 0 : TILE_QK));
         const int y = (int)row0;
         tma_load_2d(st + TILE_QK, &map_k, hq * D, y, bar);
         tma_load_2d(st + TILE_QK + 8192, &map_k, hq * D + 64, y, bar);
         tma_load_2d(st + 2 * TILE_QK, &map_v, hv * D, y, bar);
         tma_load_2d(st + 2 * TILE_QK + 8192, &map_v, hv * D + 64, y, bar);
-        if constexpr (!NO_O) {
+        if (with_q) {
           tma_load_2d(st, &map_q, hq * D, y, bar);
           tma_load_2d(st + 8192, &map_q, hq * D + 64, y, bar);
         }
@@ -764,8 +783,8 @@ static int make_map(CUtensorMap* m, const void* ptr, long long rows, long long c
 
 int launch_fwd_tc(const void* q, const void* k, const void* v, const void* A, const float* g,
                   const void* beta, int beta_is_f32, const float* h0, float* ht, void* o, void* h,
-                  void* vnew, int tiled, int N, int Hq, int Hv, long long T_rows, float scale,
-                  SeqLayout lay, cudaStream_t st) {
+                  void* vnew, int tiled, const int* lead, int N, int Hq, int Hv, long long T_rows,
+                  float scale, SeqLayout lay, cudaStream_t st) {
   using namespace fwdtc;
   CUtensorMap mq, mk, mv, ma, mh, mvn;
   int rc;
@@ -785,6 +804,7 @@ int launch_fwd_tc(const void* q, const void* k, const void* v, const void* A, co
   }
   FwdTcParams p;
   p.tiled = tiled;
+  p.lead = lead;
   p.g = g; p.beta = beta; p.beta_is_f32 = beta_is_f32; p.h0 = h0; p.ht = ht;
   p.o = (bf16*)o; p.h = (bf16*)h; p.vnew = (bf16*)vnew;
   p.N = N; p.Hq = Hq; p.Hv = Hv; p.T_rows = T_rows; p.scale = scale; p.lay = lay;

@@ -170,12 +170,14 @@ def kkt_solve(k, b, g_cum, cu_seqlens=None, chunk_size: int = CHUNK_SIZE, raw_ga
 def fwd_seq(q, k, v, a, g_cum, b, scale, initial_state=None, *, output_final_state=False,
             output_o=True, output_h=False, output_vnew=False, output_m=False,
             warm_chunks=None, m_mask=None, cu_seqlens=None, tables: SeqTables | None = None,
-            operand_tiles: bool = False):
+            operand_tiles: bool = False, lead_chunks=None):
     """Sequential forward recurrence.  Returns a dict with the requested outputs among
     ``o, h, vnew, ht, M`` (reference: ``blackwell/fused_fwd.py:775-915`` and
     ``blackwell/prepare_h.py:669-784``).  With ``operand_tiles`` (K = V = 128 only) ``h`` comes
     out as ``[chunks, Hv, V, K]`` and ``vnew`` as ``[chunks, Hv, V, 64]``: the layouts
-    ``bwd_main(..., operand_tiles=True)`` reads as tensor-core operands."""
+    ``bwd_main(..., operand_tiles=True)`` reads as tensor-core operands.  ``lead_chunks``
+    (int32 ``[N, Hv]``, K = V = 128): per (segment, head) the number of chunks before the segment
+    to walk first, state-only, from a zero state (see ``segment_scan``)."""
     _require_cuda(k, v, a, g_cum, b)
     _check_bf16(q=q, k=k, v=v, a=a)
     B, T, Hq, D = k.shape
@@ -204,8 +206,8 @@ def fwd_seq(q, k, v, a, g_cum, b, scale, initial_state=None, *, output_final_sta
         _ptr(q) if output_o else None, _ptr(k), _ptr(v), _ptr(a), _ptr(g_cum), _ptr(b),
         _beta_flag(b), _ptr(initial_state), _ptr(out.get("ht")), _ptr(out.get("o")),
         _ptr(out.get("h")), _ptr(out.get("vnew")), _ptr(out.get("M")), _ptr(warm_chunks),
-        _ptr(m_mask), tb.B, tb.T, Hq, Hv, D, float(scale), cu, offs, is64, N, int(operand_tiles),
-        _stream(k))
+        _ptr(m_mask), _ptr(lead_chunks), tb.B, tb.T, Hq, Hv, D, float(scale), cu, offs, is64, N,
+        int(operand_tiles), _stream(k))
     _lib.check(st, "fwd_seq")
     return out
 
@@ -309,17 +311,40 @@ def warmup_scan(g_cum, seg_cu_seqlens, threshold: float = -10.0, from_start: boo
 
 
 @on_tensor_device
-def merge_states(local, M, use_m, raw, seg_begin, reverse: bool = False):
+def segment_scan(g_cum, seg_cu_seqlens, seg_begin, threshold: float = -10.0,
+                 from_start: bool = False):
+    """The warm-up scan of a whole split plan plus the decision how each segment gets its start
+    state; returns int32 tensors ``(warm, fallback, lead, exact_warm)`` of shape ``[n_seg, Hv]``
+    and ``any_fallback [n_raw, Hv]`` (``include/fqla.h``: ``fqla_segment_scan``; reference:
+    ``blackwell/cp_fwd.py:81-115``, ``:224-264`` and ``chunk/cp_context.py:148-227``)."""
+    _require_cuda(g_cum, seg_cu_seqlens, seg_begin)
+    B, T, Hv = g_cum.shape
+    n_seg, n_raw = seg_cu_seqlens.numel() - 1, seg_begin.numel() - 1
+    assert seg_begin.dtype == torch.int32
+    tables = torch.empty(4, n_seg, Hv, dtype=torch.int32, device=g_cum.device)
+    any_fb = torch.empty(n_raw, Hv, dtype=torch.int32, device=g_cum.device)
+    st = _lib.load().fqla_segment_scan(
+        _ptr(g_cum), T, Hv, _ptr(seg_cu_seqlens), int(seg_cu_seqlens.dtype == torch.int64),
+        _ptr(seg_begin), n_raw, float(threshold), int(from_start), _ptr(tables[0]),
+        _ptr(tables[1]), _ptr(tables[2]), _ptr(tables[3]), _ptr(any_fb), _stream(g_cum))
+    _lib.check(st, "segment_scan")
+    return tables[0], tables[1], tables[2], tables[3], any_fb
+
+
+@on_tensor_device
+def merge_states(local, M, use_m, raw, seg_begin, reverse: bool = False, any_fallback=None):
     """Chain the segment states of every raw sequence; returns the per-segment start states
     (or, reversed, end gradients) fp32 ``[n_seg, Hv, D, D]``
-    (reference: ``blackwell/cp_fwd.py:483-610``)."""
+    (reference: ``blackwell/cp_fwd.py:483-610``).  With ``any_fallback`` (from ``segment_scan``)
+    sequences without a chain only get their edge entry written; the other entries of the result
+    are then undefined (their segments lead in by themselves)."""
     _require_cuda(local, M, seg_begin)
     n_seg, Hv, D, _ = local.shape
     n_raw = seg_begin.numel() - 1
     assert seg_begin.dtype == torch.int32
     out = torch.empty_like(local)
     st = _lib.load().fqla_merge_states(
-        _ptr(local), _ptr(M), _ptr(use_m), _ptr(raw), _ptr(seg_begin), _ptr(out), n_raw, Hv, D,
-        int(reverse), _stream(local))
+        _ptr(local), _ptr(M), _ptr(use_m), _ptr(raw), _ptr(seg_begin), _ptr(any_fallback),
+        _ptr(out), n_raw, Hv, D, int(reverse), _stream(local))
     _lib.check(st, "merge_states")
     return out

@@ -69,14 +69,20 @@ int fqla_kkt_solve(const void* k, const void* beta, int beta_is_f32, const float
  * warm_chunks): h and vnew are written in the layout the backward kernels consume as tensor-core
  * operands, h as [chunks, Hv, V, K] (each state transposed) and vnew as [chunks, Hv, V, 64]
  * (each chunk transposed, rows past the sequence end zero); FQLA_ERR_UNSUPPORTED_DIM otherwise.
+ * warm_chunks < 0 for a (sequence, head): nothing is computed or written for it.
+ * lead_chunks [N,Hv] (int32, optional, K = V = 128, not together with warm_chunks, M, m_mask):
+ * lead-in of a segment of a longer sequence.  Where lead_chunks[n,hv] > 0 the walk starts that
+ * many chunks BEFORE the segment (those rows are the tail of the segment before it) from a zero
+ * state, state-only, and only then enters the segment: the start state needs no separate pass.
+ * h0 is ignored for such a (segment, head); outputs cover the segment's own rows only.
  * Replaces fused_gdr_fwd (blackwell/fused_fwd.py:775-915) and fused_gdr_h
  * (blackwell/prepare_h.py:669-784). */
 int fqla_fwd_seq(const void* q, const void* k, const void* v, const void* A, const float* g_cum,
                  const void* beta, int beta_is_f32, const float* h0, float* ht, void* o, void* h,
-                 void* vnew, float* M, const int* warm_chunks, const int* m_mask, int B, int T,
-                 int Hq, int Hv, int D, float scale, const void* cu_seqlens,
-                 const void* chunk_offsets, int idx_is64, int N, int operand_tiles,
-                 void* stream);
+                 void* vnew, float* M, const int* warm_chunks, const int* m_mask,
+                 const int* lead_chunks, int B, int T, int Hq, int Hv, int D, float scale,
+                 const void* cu_seqlens, const void* chunk_offsets, int idx_is64, int N,
+                 int operand_tiles, void* stream);
 
 /* Sequential reverse recurrence of the state gradient.  Optional outputs: per-chunk dh, du (the
  * gradient of vnew), dh0.  warm_chunks (optional, dh0-only calls): walk only the first
@@ -122,10 +128,28 @@ int fqla_warmup_scan(const float* g_cum, int T, int Hv, const void* seg_cu_seqle
  * reverse == 0: out[first] = raw[r] (or 0); out[i+1] = local[i] + use_m[i,hv] * M[i]   out[i]
  * reverse != 0: out[last]  = raw[r] (or 0); out[i-1] = local[i] + use_m[i,hv] * M[i]^T out[i]
  * All states fp32 [*, Hv, D, D]; use_m int32 [n_seg, Hv] or NULL (always apply M).
+ * any_fallback (int32 [n_raw, Hv] or NULL, from fqla_segment_scan): where 0, only the edge
+ * segment's entry of out is written (raw[r] or 0) and the chain is skipped.
  * Replaces correct_initial_states / correct_terminal_states, blackwell/cp_fwd.py:483-610. */
 int fqla_merge_states(const float* local, const float* M, const int* use_m, const float* raw,
-                      const int* seg_begin, float* out, int n_raw, int Hv, int D, int reverse,
-                      void* stream);
+                      const int* seg_begin, const int* any_fallback, float* out, int n_raw, int Hv,
+                      int D, int reverse, void* stream);
+
+/* The scan of fqla_warmup_scan for a whole split plan in one launch, plus the decision how each
+ * segment gets its start state.  seg_begin [n_raw+1] (int32): first segment of every raw
+ * sequence.  Outputs, all int32: warm, fallback [n_seg,Hv] as for fqla_warmup_scan (the segment
+ * that hands nothing on gets 0 / 0); any_fallback [n_raw,Hv]: some segment of this (sequence,
+ * head) never reaches the threshold; lead [n_seg,Hv]: where any_fallback is 0, the number of
+ * chunks of the neighbouring segment (the one before it, forward; after it, from_start != 0) the
+ * recurrence kernel walks first from a zero state (lead_chunks of fqla_fwd_seq), else 0;
+ * exact_warm [n_seg,Hv]: warm where any_fallback is 1, else -1 (the warm_chunks of the separate
+ * state-only pass, which then skips the segment).  With any_fallback given, fqla_merge_states
+ * only copies the edge state of sequences without a chain.
+ * Replaces get_warmup_chunks / get_warmup_chunks_bidi and the bookkeeping of
+ * intra_card_cp_preprocess, chunk/cp_context.py:148-227. */
+int fqla_segment_scan(const float* g_cum, int T, int Hv, const void* seg_cu_seqlens, int idx_is64,
+                      const int* seg_begin, int n_raw, float threshold, int from_start, int* warm,
+                      int* fallback, int* lead, int* exact_warm, int* any_fallback, void* stream);
 
 /* Forward (o and, optionally, the final state ht) for hosts that cannot allocate device memory
  * where they call this library: an inference engine that gave all device memory to its own arena

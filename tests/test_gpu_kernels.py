@@ -220,7 +220,7 @@ def test_forward_cache_tiles_replace_the_recomputation(cu, T):
     assert torch.equal(o, o2) and torch.equal(ht, ht2)
     args = (d["q"], d["k"], d["v"], g_cum, d["beta"], A, d["do"], d["dht"], None, d["h0"], cu_t)
     with_tiles = fq.chunk_gated_delta_rule_bwd(*args, cp_cache=cache)
-    recomputed = fq.chunk_gated_delta_rule_bwd(*args, cp_cache=(cache[0], None, None))
+    recomputed = fq.chunk_gated_delta_rule_bwd(*args, cp_cache=(cache[0], None, None, cache[3]))
     for x, y, name in zip(with_tiles, recomputed, ("dq", "dk", "dv", "db", "dg", "dh0")):
         assert torch.equal(x, y), name
     # the switch turns the tiles off again
@@ -273,3 +273,60 @@ def test_float16_inputs_are_accepted_and_computed_in_bfloat16():
                                           initial_state=d["h0"], output_final_state=True)
     assert o_h.dtype == torch.float16
     assert orc.rel_err(o_h.float(), o_bf.float()) < 2e-3 and orc.rel_err(ht_h, ht_bf) < 1e-6
+
+
+@pytest.mark.parametrize("gate", ["logsigmoid", "weak"])
+def test_segment_scan_matches_per_segment_scan_and_decides_lead_in(gate):
+    """The one-launch scan of a split plan: same warm / fallback as the per-segment scan, and the
+    lead-in decision per (sequence, head) restated on the host."""
+    from flashqla_b200 import cp, ops
+
+    cu = [0, 2100, 2100, 3700, 5000]
+    cu_t = torch.tensor(cu, dtype=torch.int32)
+    x = orc.make_inputs(1, cu[-1], 1, 4, 128, 128, seed=71, cu_seqlens=cu_t, gate=gate)
+    g_cum = ops.chunk_local_cumsum(x["g"].to(DEV), 64, cu_t.to(DEV))
+    plan = cp.plan_segments(ops.SeqTables(1, cu[-1], cu_t.to(DEV)), 4, device=torch.device(DEV, 0))
+    assert plan is not None
+    begin = plan.seg_begin.tolist()
+    for from_start, keep in ((False, plan.keep_fwd), (True, plan.keep_bwd)):
+        w_old, f_old = ops.warmup_scan(g_cum, plan.seg_tables.cu, cp.THRESHOLD, from_start, keep)
+        warm, fb, lead, exact, any_fb = ops.segment_scan(g_cum, plan.seg_tables.cu,
+                                                         plan.seg_begin, cp.THRESHOLD, from_start)
+        torch.cuda.synchronize()
+        assert torch.equal(warm, w_old) and torch.equal(fb, f_old)
+        warm, fb, lead, exact, any_fb = (t.cpu() for t in (warm, fb, lead, exact, any_fb))
+        if gate == "weak":
+            assert int(any_fb.sum()) > 0  # the gate-free heads never reach the threshold
+        for r, (s0, s1) in enumerate(zip(begin[:-1], begin[1:])):
+            for hv in range(4):
+                a = int(fb[s0:s1, hv].sum() > 0)
+                assert int(any_fb[r, hv]) == a
+                for s in range(s0, s1):
+                    giver = s + 1 if from_start else s - 1
+                    has = giver < s1 if from_start else giver >= s0
+                    assert int(lead[s, hv]) == (int(warm[giver, hv]) if has and not a else 0)
+                    assert int(exact[s, hv]) == (int(warm[s, hv]) if a else -1)
+                    if has and not a:
+                        assert int(lead[s, hv]) >= 1
+
+
+def test_lead_in_forward_agrees_with_explicit_start_states():
+    """The recurrence kernel that starts a segment a few chunks early from zero against the same
+    kernel fed by the separate state-only pass and merge chain: same truncation of the past, so
+    the results agree far inside the forward tolerance (the state copy is rounded at different
+    points, so not bit for bit)."""
+    import flashqla_b200 as fq
+    from flashqla_b200 import cp
+
+    d = _inputs(64 * 70 + 13, 2, 4, seed=72)
+    run = lambda: fq.chunk_gated_delta_rule_fwd(d["q"], d["k"], d["v"], d["g"], d["beta"], None,  # noqa: E731
+                                                d["h0"], None, output_final_state=True)
+    assert cp.LEAD_IN
+    _, _, o_lead, _, ht_lead, _ = run()
+    cp.LEAD_IN = False
+    try:
+        _, _, o_sep, _, ht_sep, _ = run()
+    finally:
+        cp.LEAD_IN = True
+    assert orc.rel_err(o_lead.float(), o_sep.float()) < 2e-3
+    assert orc.rel_err(ht_lead, ht_sep) < 2e-3
