@@ -8,23 +8,29 @@
 //   off the serial chain, prepared one chunk ahead (WY form, FLA's w and u):
 //     A'  = A diag(beta),  A'' = A diag(beta gamma)                               (prep warps)
 //     u^T [v x tok] = V^T A'^T          (A operand = V tile read MN-major)        -> TM_UV
-//     w   [tok x k] = A'' K             (B operand = K tile read MN-major)        -> TM_W -> smem
+//     w^T [k x tok] = K^T A''^T         (A operand = K tile read MN-major)        -> TM_PW -> smem
 //     P   [tok x tok'] = Q K^T,  Pg = s P exp(g_tok - g_tok') for tok >= tok'     (O group)
 //   on the chain (two products):
 //     Vn^T [v x tok] = u^T - S^T w^T    (A = bf16 copy of S^T, negated; accumulates onto u^T)
 //     S^T  [v x k]   = gamma_last S^T + (rho Vn)^T K     (B = K tile read MN-major)
-//   output:
-//     O [tok x v] = s gamma_tok (Q S) + Pg Vn      (two M = 64 accumulators, one thread per row)
+//   output, transposed so that it shares the A operands of the chain:
+//     O1^T [v x tok] = S^T Q^T,   O2^T [v x tok] = Vn^T Pg^T,   o = s gamma_tok O1 + O2
 //
-// The state path is kept TRANSPOSED so that the 128-wide value dimension sits on the MMA M axis
-// (tensor-memory lane = value index, one thread per lane).  This is the algebra of the
+// The state path is kept TRANSPOSED: the 128-wide value dimension sits on the MMA M axis
+// (tensor-memory lane = value index, one thread per lane), so every product but P has M = 128.
+// Every operand that a read-out warp derives from an accumulator - the bf16 copy of S^T, Vn^T and
+// rho Vn^T - goes back into TENSOR MEMORY (two bf16 per 32-bit column) and is consumed as the A
+// operand of the next product straight from there (tcgen05.mma with A in tensor memory): the
+// chunk-to-chunk chain never touches shared memory, and the tensor pipe, which is bound by the
+// shared-memory fetch of its operands, reads half as much.  This is the algebra of the
 // reference's blackwell/fused_fwd.py:349-596 (and the X/Y form of prepare_h.py:312-318) with the
 // gate folded into A.
 //
 // Warp roles (thread ranges):
-//     128-255 S group : fp32 master state in tensor memory; per chunk writes the bf16 operand copy
-//                       of S^T to shared memory (on the chain), then decays S^T in place
-//     256-383 V group : Vn^T -> rho-scaled and plain bf16 operand copies; w -> bf16 operand tile
+//     128-255 S group : fp32 master state in tensor memory; per chunk packs the bf16 operand copy
+//                       of S^T into tensor memory (on the chain), then decays S^T in place
+//     256-383 V group : Vn^T -> rho-scaled and plain bf16 operand copies (tensor memory);
+//                       w^T -> bf16 operand tile (shared memory)
 //     384-511 O group : P -> Pg (operand); output epilogue o = s gamma O1 + O2
 //     warp 0  : issues every tcgen05.mma (one elected lane)
 //     warp 1  : producer: per-chunk gate vectors (fetched one chunk ahead), TMA loads of the
@@ -45,11 +51,19 @@ using namespace tc;
 
 // 0 = ok; 1 after some kernel abandoned a bounded wait (its outputs are then invalid)
 __device__ int g_device_status = 0;
-// Diagnostics (FQLA_PROFILE=1): cycles the first CTA's role leaders spent per barrier wait and
-// per section, [role 0..5][slot 0..23], plus [6][0] = total cycles of the CTA.
-__device__ long long g_wait_profile[7 * 24];
-// Diagnostics: (1 << 24 | warp << 16 | barrier << 8 | parity) of the first wait that was given up
-__device__ int g_fwd_abort_info = 0;
+
+#ifdef FQLA_DIAGNOSTICS
+// Development builds only: clock stamps of the role leaders of CTA 0 over a window of chunks,
+// [role 0..5][chunk in window 0..15][tag 0..9].
+__device__ long long g_fwd_trace[6 * 16 * 10];
+#define FQLA_TRACE(role, tag)                                                         \
+  do {                                                                                \
+    if (blockIdx.x == 0 && it >= 24 && it < 40)                                       \
+      g_fwd_trace[((role) * 16 + (it - 24)) * 10 + (tag)] = clock64();               \
+  } while (0)
+#else
+#define FQLA_TRACE(role, tag) do { } while (0)
+#endif
 
 struct FwdTcParams {
   const float* g;
@@ -64,7 +78,6 @@ struct FwdTcParams {
   long long T_rows;
   float scale;
   SeqLayout lay;
-  int profile;
   int tiled;  // h and vnew are written as operand tiles (h^T per chunk, v_new^T per chunk) by TMA
   // [N, Hv] or null: lead-in.  A CTA with lead > 0 starts from a ZERO state `lead` chunks before
   // its sequence (segment) and walks those chunks state-only (no q, no output, nothing stored):
@@ -78,29 +91,41 @@ constexpr int D = 128;
 constexpr int TILE_QK = 16384, TILE_V = 16384, TILE_A = 8192;
 constexpr int STAGE_BYTES = 2 * TILE_QK + TILE_V + TILE_A;  // 57344
 constexpr int OFF_STAGE = 0;
-constexpr int OFF_ST = 2 * STAGE_BYTES;          // S^T copy, 2 blocks of [128 x 128B]
-constexpr int OFF_VNT = OFF_ST + 32768;          // Vn^T  [128 x 128B]
-constexpr int OFF_W = OFF_VNT + 16384;           // w     2 blocks of [64 x 128B]
-constexpr int OFF_VRT = OFF_W + 16384;           // rho-scaled Vn^T [128 x 128B]
-constexpr int OFF_P = OFF_VRT + 16384;            // Pg    [64 x 128B]
+constexpr int OFF_W = 2 * STAGE_BYTES;           // w^T   [128 k rows x 128B (64 tokens)]
+constexpr int OFF_P = OFF_W + 16384;             // Pg    [64 x 128B]
 constexpr int OFF_AP = OFF_P + 8192;             // A diag(beta)
 constexpr int OFF_APP = OFF_AP + 8192;           // A diag(beta gamma)
-constexpr int OFF_VEC = OFF_APP + 8192;          // 4 slots x 6 vectors x 64 floats
+constexpr int OFF_O = OFF_APP + 8192;            // o tile [64 tok x 128 v] bf16, source of its TMA store
+constexpr int OFF_VEC = OFF_O + 16384;           // 4 slots x 6 vectors x 64 floats
 constexpr int VEC_SLOT_FLOATS = 6 * CHUNK;
 constexpr int OFF_BAR = OFF_VEC + 4 * VEC_SLOT_FLOATS * 4;
-constexpr int N_BARS = 30;
+constexpr int N_BARS = 32;
 constexpr int OFF_MISC = OFF_BAR + N_BARS * 8;
-constexpr int SMEM_BYTES = OFF_MISC + 16 + 1024;  // + slack for 1024-byte alignment of the base
-// tensor-memory columns.  An M = 64 accumulator only occupies lanes 0-15 of each 32-lane
-// quarter, so a second one fits at lane +16 of the same columns: P under O1, w under O2.
-constexpr uint32_t TM_S = 0, TM_UV = 128, TM_O1 = 256, TM_O2 = 384;
-constexpr uint32_t TM_P = TM_O1 + (16u << 16), TM_W = TM_O2 + (16u << 16);
+// only the variants that hand per-chunk tiles to the backward pass keep shared-memory copies of
+// S^T and Vn^T (the sources of their TMA stores)
+constexpr int OFF_ST = (OFF_MISC + 16 + 1023) / 1024 * 1024;  // S^T copy, 2 blocks of [128 x 128B]
+constexpr int OFF_VNT = OFF_ST + 32768;                       // Vn^T  [128 x 128B]
+constexpr int SMEM_BYTES = OFF_ST + 1024;  // + slack for 1024-byte alignment of the base
+constexpr int SMEM_BYTES_EXTRA = OFF_VNT + 16384 + 1024;
+// tensor-memory columns (512).  The bf16 operands hold two elements per column.
+constexpr uint32_t TM_S = 0;      // S^T fp32                      128 columns
+constexpr uint32_t TM_SB = 128;   // S^T bf16 (A operand, K = 128)  64 columns
+constexpr uint32_t TM_UV = 192;   // u^T, then Vn^T fp32            64 columns
+constexpr uint32_t TM_VNB = 256;  // Vn^T bf16 (A operand, K = 64)  32 columns
+constexpr uint32_t TM_VRB = 288;  // rho Vn^T bf16                  32 columns
+constexpr uint32_t TM_O1 = 320;   // O1^T fp32                      64 columns
+constexpr uint32_t TM_O2 = 384;   // O2^T fp32                      64 columns
+// P (M = 64: lanes 0-15 of each quarter) and w^T of the NEXT chunk (M = 128) take turns in the
+// same columns: w^T is issued only after the output group has read P, and the next P only after
+// the value group has turned w^T into its operand tile (the chain's first product waits for it).
+constexpr uint32_t TM_PW = 448;
 // barrier indices
 enum { FULL0 = 0, FULL1, EMPTY0, EMPTY1, S_COPY, S_DEC, VN_DONE, S_DONE, P_DONE, O_DONE, W_DONE,
-       VN_READY, W_READY, P_READY, O_FREE, AP_READY, VR_READY, PRIV,
-       SEC_A = 18, SEC_B, SEC_C, SEC_D, SEC_E, SEC_F,  // SEC_*: profiling slots only
+       VB_READY, W_READY, P_READY, O_FREE, AP_READY, PRIV,
        // the A tile and the per-row vectors of a chunk travel one chunk ahead of q, k, v
-       FULLA0 = 24, FULLA1, EMPTYA0, EMPTYA1, PRIVA };
+       FULLA0, FULLA1, EMPTYA0, EMPTYA1, PRIVA,
+       // tile outputs: the shared-memory copies of S^T / Vn^T are complete
+       ST_READY, VN_READY };
 // vectors inside a slot; V_GL holds gamma_last at [0]
 enum { V_G = 0, V_BETA = 1, V_BG = 2, V_RHO = 3, V_SGAM = 4, V_GL = 5 };
 }  // namespace fwdtc
@@ -110,17 +135,16 @@ __device__ __forceinline__ uint32_t scale_bf16x2(uint32_t packed, float lo, floa
   return pack_bf16(f.x * lo, f.y * hi);
 }
 
-// PROFILE: wait/section cycle counters (diagnostics).  EXTRA: per-chunk state and v_new outputs.
-// Both are compiled out of the common instantiation: the six roles run six different code
-// regions at once, and the kernel is sensitive to its instruction-cache footprint.
-// NO_O: state-only walk (recomputation for the backward pass): no q, no output products, the
-// output warps stay idle.
-template <bool PROFILE, bool EXTRA, bool NO_O>
+// EXTRA: per-chunk state and v_new outputs (compiled out of the common instantiation: the six
+// roles run six different code regions at once, and the kernel is sensitive to its
+// instruction-cache footprint).  NO_O: state-only walk (recomputation for the backward pass): no q,
+// no output products, the output warps stay idle.
+template <bool EXTRA, bool NO_O>
 __global__ void __launch_bounds__(512, 1)
 fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
               const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
               const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_h,
-              const __grid_constant__ CUtensorMap map_vn) {
+              const __grid_constant__ CUtensorMap map_vn, const __grid_constant__ CUtensorMap map_o) {
   using namespace fwdtc;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
@@ -137,6 +161,7 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
   // iteration j handles chunk c = j - lead of the sequence; c < 0 are the lead-in chunks
   const int lead = p.lead ? p.lead[n * p.Hv + hv] : 0;
   const int n_it = sp.n_chunks == 0 ? 0 : sp.n_chunks + lead;
+  const bool tile_h = EXTRA && p.tiled && p.h, tile_vn = EXTRA && p.tiled && p.vnew;
 
   if (tid == 0) {
     mbar_init(&bars[FULL0], 1);
@@ -155,13 +180,14 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
     mbar_init(&bars[P_DONE], 1);
     mbar_init(&bars[O_DONE], 1);
     mbar_init(&bars[W_DONE], 1);
-    mbar_init(&bars[VN_READY], 128);
+    mbar_init(&bars[VB_READY], 128);
     mbar_init(&bars[W_READY], 128);
     mbar_init(&bars[P_READY], 128);
     mbar_init(&bars[O_FREE], 128);
     mbar_init(&bars[AP_READY], 2);
-    mbar_init(&bars[VR_READY], 128);
     mbar_init(&bars[PRIV], 1);
+    mbar_init(&bars[ST_READY], 128);
+    mbar_init(&bars[VN_READY], 128);
     *abort_flag = 0;
     fence_mbar_init();
     tma_prefetch_desc(&map_q);
@@ -182,25 +208,7 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
   const uint32_t lane_sel = (uint32_t)((warp & 3) * 32) << 16;  // this warp's lane quarter
   const long long state_off = ((long long)n * p.Hv + hv) * D * D;
   bool ok = true;
-  long long waited[24];
-#pragma unroll
-  for (int i = 0; i < 24; ++i) waited[i] = 0;
-  const long long t_start = clock64();
-  long long t_sec = 0;
-  auto WAIT = [&](int idx, uint32_t parity) {
-    if constexpr (!PROFILE) {
-      const bool r = mbar_wait(&bars[idx], parity, abort_flag);
-      if (!r) atomicCAS(&g_fwd_abort_info, 0, (1 << 24) | (warp << 16) | (idx << 8) | (int)parity);
-      return r;
-    } else {
-      long long t0 = clock64();
-      bool r = mbar_wait(&bars[idx], parity, abort_flag);
-      if (idx < 24) waited[idx] += clock64() - t0;
-      return r;
-    }
-  };
-#define SEC_BEGIN() do { if constexpr (PROFILE) t_sec = clock64(); } while (0)
-#define SEC_END(slot) do { if constexpr (PROFILE) waited[slot] += clock64() - t_sec; } while (0)
+  auto WAIT = [&](int idx, uint32_t parity) { return mbar_wait(&bars[idx], parity, abort_flag); };
 
   // Role of each warp.  The MMA issuer is warp 0 and the producer warp 1 on purpose: among the
   // warps of one scheduler the oldest (lowest id) wins when several are ready, and these two
@@ -208,7 +216,7 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
   if (warp >= 4 && warp < 8) {
     // =============================== S group ===============================
     const int v = tid - 128;  // lane of tensor memory = value index
-    // initial state -> tensor memory (S^T[v][k] = h0[k][v])
+    // initial state -> tensor memory (S^T[v][k] = h0[k][v]); a lead-in starts from zero
 #pragma unroll 1
     for (int k0 = 0; k0 < D; k0 += 32) {
       float x[32];
@@ -220,45 +228,67 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
     tmem_st_wait();
     for (int it = 0; it < n_it && ok; ++it) {
       const int s = it & 1;
+      if (v == 0) FQLA_TRACE(0, 0);
       if (it > 0) ok = WAIT(S_DONE, (it - 1) & 1);
       if (!ok) break;
       tc_fence_after();
-      SEC_BEGIN();
-      bf16* hdst = (EXTRA && p.h && it >= lead)
-                       ? p.h + ((sp.chunk_base + (it - lead)) * p.Hv + hv) * (long long)D * D : nullptr;
-      // on the chain: the bf16 operand copy of S^T
+      if (v == 0) FQLA_TRACE(0, 1);
+      // on the chain: the bf16 operand copy of S^T, packed back into tensor memory.  (The products
+      // that read the copy of the chunk before were issued ahead of the state update whose
+      // completion was just waited for, and the tensor pipe runs in issue order.)
 #pragma unroll 1
-      for (int kb = 0; kb < 2; ++kb) {  // 64 columns (one operand block) per round
-        float x[32], y[32];
-        tmem_ld32(tmem + lane_sel + TM_S + kb * 64, x);
-        tmem_ld32(tmem + lane_sel + TM_S + kb * 64 + 32, y);
+      for (int k0 = 0; k0 < D; k0 += 32) {
+        float x[32];
+        tmem_ld32(tmem + lane_sel + TM_S + k0, x);
         tmem_ld_wait();
-        unsigned char* row = smem + OFF_ST + kb * 16384 + v * 128;
+        uint32_t pk[16];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          *reinterpret_cast<uint4*>(row + ((c ^ (v & 7)) << 4)) =
-              make_uint4(pack_bf16(x[8 * c + 0], x[8 * c + 1]), pack_bf16(x[8 * c + 2], x[8 * c + 3]),
-                         pack_bf16(x[8 * c + 4], x[8 * c + 5]), pack_bf16(x[8 * c + 6], x[8 * c + 7]));
-          *reinterpret_cast<uint4*>(row + (((c + 4) ^ (v & 7)) << 4)) =
-              make_uint4(pack_bf16(y[8 * c + 0], y[8 * c + 1]), pack_bf16(y[8 * c + 2], y[8 * c + 3]),
-                         pack_bf16(y[8 * c + 4], y[8 * c + 5]), pack_bf16(y[8 * c + 6], y[8 * c + 7]));
-        }
-        if (EXTRA && hdst && !p.tiled) {
+        for (int i = 0; i < 16; ++i) pk[i] = pack_bf16(x[2 * i], x[2 * i + 1]);
+        tmem_st16(tmem + lane_sel + TM_SB + (k0 >> 1), pk);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&bars[S_COPY]);
+      if (v == 0) FQLA_TRACE(0, 2);
+      if constexpr (EXTRA) {
+        // off the chain: the state entering this chunk as an output
+        if (p.h && it >= lead) {
+          bf16* hdst = p.h + ((sp.chunk_base + (it - lead)) * p.Hv + hv) * (long long)D * D;
+#pragma unroll 1
+          for (int kb = 0; kb < 2; ++kb) {  // 64 columns (one operand block) per round
+            float x[32], y[32];
+            tmem_ld32(tmem + lane_sel + TM_S + kb * 64, x);
+            tmem_ld32(tmem + lane_sel + TM_S + kb * 64 + 32, y);
+            tmem_ld_wait();
+            if (p.tiled) {
+              unsigned char* row = smem + OFF_ST + kb * 16384 + v * 128;
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            hdst[(long long)(kb * 64 + j) * D + v] = __float2bfloat16(x[j]);
-            hdst[(long long)(kb * 64 + 32 + j) * D + v] = __float2bfloat16(y[j]);
+              for (int c = 0; c < 4; ++c) {
+                *reinterpret_cast<uint4*>(row + ((c ^ (v & 7)) << 4)) =
+                    make_uint4(pack_bf16(x[8 * c + 0], x[8 * c + 1]), pack_bf16(x[8 * c + 2], x[8 * c + 3]),
+                               pack_bf16(x[8 * c + 4], x[8 * c + 5]), pack_bf16(x[8 * c + 6], x[8 * c + 7]));
+                *reinterpret_cast<uint4*>(row + (((c + 4) ^ (v & 7)) << 4)) =
+                    make_uint4(pack_bf16(y[8 * c + 0], y[8 * c + 1]), pack_bf16(y[8 * c + 2], y[8 * c + 3]),
+                               pack_bf16(y[8 * c + 4], y[8 * c + 5]), pack_bf16(y[8 * c + 6], y[8 * c + 7]));
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                hdst[(long long)(kb * 64 + j) * D + v] = __float2bfloat16(x[j]);
+                hdst[(long long)(kb * 64 + 32 + j) * D + v] = __float2bfloat16(y[j]);
+              }
+            }
+          }
+          if (p.tiled) {
+            fence_proxy_async();
+            mbar_arrive(&bars[ST_READY]);
           }
         }
       }
-      fence_proxy_async();
-      tc_fence_before();
-      mbar_arrive(&bars[S_COPY]);
-      SEC_END(SEC_A);
       // off the chain: decay in place, needed only by the state update at the end of the chunk
       ok = WAIT(FULL0 + s, (it >> 1) & 1);
       if (!ok) break;
-      SEC_BEGIN();
+      if (v == 0) FQLA_TRACE(0, 3);
       const float gl = vec[(it & 3) * VEC_SLOT_FLOATS + V_GL * CHUNK];
 #pragma unroll 1
       for (int kb = 0; kb < 2; ++kb) {
@@ -277,7 +307,7 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&bars[S_DEC]);
-      SEC_END(SEC_B);
+      if (v == 0) FQLA_TRACE(0, 4);
     }
     if (ok && n_it > 0) ok = WAIT(S_DONE, (n_it - 1) & 1);
     if (ok && p.ht) {
@@ -293,32 +323,28 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
     }
   } else if (warp >= 8 && warp < 12) {
     // =============================== V group ===============================
-    const int v = tid - 256;
-    const int wq = warp & 3;
-    const int tok_w = 16 * wq + (lane & 15);  // lanes 16-31 of each quarter hold a row of w
-    // w of chunk `it` (tensor memory, M = 64 layout at lane +16) -> bf16 operand tile
+    const int v = tid - 256;  // tensor-memory lane: value index for Vn^T, key index for w^T
+    // w^T of chunk `it` (tensor memory, [k][tok]) -> bf16 operand tile, row k = 64 tokens
     auto convert_w = [&](int it) {
       if (!WAIT(W_DONE, it & 1)) return false;
       tc_fence_after();
-      SEC_BEGIN();
-#pragma unroll 1
-      for (int c0 = 0; c0 < D; c0 += 32) {
-        float x[32];
-        tmem_ld32(tmem + lane_sel + TM_O2 + c0, x);
-        tmem_ld_wait();
-        if (lane >= 16) {
-          unsigned char* row = smem + OFF_W + (c0 >> 6) * 8192 + tok_w * 128;
+      float x[32], y[32];
+      tmem_ld32(tmem + lane_sel + TM_PW, x);
+      tmem_ld32(tmem + lane_sel + TM_PW + 32, y);
+      tmem_ld_wait();
+      tc_fence_before();
+      unsigned char* row = smem + OFF_W + v * 128;
 #pragma unroll
-          for (int c = 0; c < 4; ++c)
-            *reinterpret_cast<uint4*>(row + (((((c0 & 63) >> 3) + c) ^ (tok_w & 7)) << 4)) =
-                make_uint4(pack_bf16(x[8 * c + 0], x[8 * c + 1]), pack_bf16(x[8 * c + 2], x[8 * c + 3]),
-                           pack_bf16(x[8 * c + 4], x[8 * c + 5]), pack_bf16(x[8 * c + 6], x[8 * c + 7]));
-        }
+      for (int c = 0; c < 4; ++c) {
+        *reinterpret_cast<uint4*>(row + ((c ^ (v & 7)) << 4)) =
+            make_uint4(pack_bf16(x[8 * c + 0], x[8 * c + 1]), pack_bf16(x[8 * c + 2], x[8 * c + 3]),
+                       pack_bf16(x[8 * c + 4], x[8 * c + 5]), pack_bf16(x[8 * c + 6], x[8 * c + 7]));
+        *reinterpret_cast<uint4*>(row + (((c + 4) ^ (v & 7)) << 4)) =
+            make_uint4(pack_bf16(y[8 * c + 0], y[8 * c + 1]), pack_bf16(y[8 * c + 2], y[8 * c + 3]),
+                       pack_bf16(y[8 * c + 4], y[8 * c + 5]), pack_bf16(y[8 * c + 6], y[8 * c + 7]));
       }
       fence_proxy_async();
-      tc_fence_before();
       mbar_arrive(&bars[W_READY]);
-      SEC_END(SEC_B);
       return true;
     };
     if (n_it > 0) ok = convert_w(0);
@@ -326,112 +352,140 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
       const int c = it - lead;
       const long long row0 = sp.bos + (long long)c * CHUNK;
       const int valid = c < 0 ? 0 : min(CHUNK, sp.len - c * CHUNK);  // 0: nothing is stored
+      if (v == 0) FQLA_TRACE(1, 0);
       ok = WAIT(FULL0 + (it & 1), (it >> 1) & 1) && WAIT(VN_DONE, it & 1);
       if (!ok) break;
       tc_fence_after();
-      SEC_BEGIN();
-      {
-        float x[32], y[32];
-        tmem_ld32(tmem + lane_sel + TM_UV, x);
-        tmem_ld32(tmem + lane_sel + TM_UV + 32, y);
+      if (v == 0) FQLA_TRACE(1, 1);
+      const float* rho = vec + (it & 3) * VEC_SLOT_FLOATS + V_RHO * CHUNK;
+      // on the chain: Vn^T as the two bf16 operands (rho-scaled for the state update, plain for
+      // the output product), 32 tokens = 16 packed columns at a time
+#pragma unroll 1
+      for (int t0 = 0; t0 < CHUNK; t0 += 32) {
+        float x[32];
+        tmem_ld32(tmem + lane_sel + TM_UV + t0, x);
         tmem_ld_wait();
-        // first the rho-scaled copy (operand of the state update, on the chain) ...
-        const float* rho = vec + (it & 3) * VEC_SLOT_FLOATS + V_RHO * CHUNK;
-        unsigned char* rowr = smem + OFF_VRT + v * 128;
+        uint32_t pr[16], pn[16];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const float4 r0 = *reinterpret_cast<const float4*>(rho + 8 * c);
-          const float4 r1 = *reinterpret_cast<const float4*>(rho + 8 * c + 4);
-          const float4 r2 = *reinterpret_cast<const float4*>(rho + 32 + 8 * c);
-          const float4 r3 = *reinterpret_cast<const float4*>(rho + 32 + 8 * c + 4);
-          *reinterpret_cast<uint4*>(rowr + ((c ^ (v & 7)) << 4)) = make_uint4(
-              pack_bf16(r0.x * x[8 * c + 0], r0.y * x[8 * c + 1]),
-              pack_bf16(r0.z * x[8 * c + 2], r0.w * x[8 * c + 3]),
-              pack_bf16(r1.x * x[8 * c + 4], r1.y * x[8 * c + 5]),
-              pack_bf16(r1.z * x[8 * c + 6], r1.w * x[8 * c + 7]));
-          *reinterpret_cast<uint4*>(rowr + (((c + 4) ^ (v & 7)) << 4)) = make_uint4(
-              pack_bf16(r2.x * y[8 * c + 0], r2.y * y[8 * c + 1]),
-              pack_bf16(r2.z * y[8 * c + 2], r2.w * y[8 * c + 3]),
-              pack_bf16(r3.x * y[8 * c + 4], r3.y * y[8 * c + 5]),
-              pack_bf16(r3.z * y[8 * c + 6], r3.w * y[8 * c + 7]));
+        for (int i = 0; i < 8; ++i) {
+          const float4 r = *reinterpret_cast<const float4*>(rho + t0 + 4 * i);
+          pr[2 * i] = pack_bf16(r.x * x[4 * i], r.y * x[4 * i + 1]);
+          pr[2 * i + 1] = pack_bf16(r.z * x[4 * i + 2], r.w * x[4 * i + 3]);
+          pn[2 * i] = pack_bf16(x[4 * i], x[4 * i + 1]);
+          pn[2 * i + 1] = pack_bf16(x[4 * i + 2], x[4 * i + 3]);
         }
-        fence_proxy_async();
-        tc_fence_before();
-        mbar_arrive(&bars[VR_READY]);
-        SEC_END(SEC_A);
-        // ... then the plain copy (operand of the output product)
-        unsigned char* row = smem + OFF_VNT + v * 128;
+        tmem_st16(tmem + lane_sel + TM_VRB + (t0 >> 1), pr);
+        tmem_st16(tmem + lane_sel + TM_VNB + (t0 >> 1), pn);
+        if constexpr (EXTRA) {
+          if (p.vnew && c >= 0) {
+            if (p.tiled) {  // the tile of the TMA store (the store of the chunk before has read it)
+              unsigned char* row = smem + OFF_VNT + v * 128;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          *reinterpret_cast<uint4*>(row + ((c ^ (v & 7)) << 4)) =
-              make_uint4(pack_bf16(x[8 * c + 0], x[8 * c + 1]), pack_bf16(x[8 * c + 2], x[8 * c + 3]),
-                         pack_bf16(x[8 * c + 4], x[8 * c + 5]), pack_bf16(x[8 * c + 6], x[8 * c + 7]));
-          *reinterpret_cast<uint4*>(row + (((c + 4) ^ (v & 7)) << 4)) =
-              make_uint4(pack_bf16(y[8 * c + 0], y[8 * c + 1]), pack_bf16(y[8 * c + 2], y[8 * c + 3]),
-                         pack_bf16(y[8 * c + 4], y[8 * c + 5]), pack_bf16(y[8 * c + 6], y[8 * c + 7]));
-        }
-        fence_proxy_async();
-        mbar_arrive(&bars[VN_READY]);
-        if (EXTRA && p.vnew && !p.tiled) {
+              for (int q4 = 0; q4 < 4; ++q4)
+                *reinterpret_cast<uint4*>(row + ((((t0 >> 3) + q4) ^ (v & 7)) << 4)) =
+                    make_uint4(pn[4 * q4], pn[4 * q4 + 1], pn[4 * q4 + 2], pn[4 * q4 + 3]);
+            } else {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            if (j < valid) p.vnew[((row0 + j) * p.Hv + hv) * D + v] = __float2bfloat16(x[j]);
-            if (32 + j < valid)
-              p.vnew[((row0 + 32 + j) * p.Hv + hv) * D + v] = __float2bfloat16(y[j]);
+              for (int j = 0; j < 32; ++j)
+                if (t0 + j < valid)
+                  p.vnew[((row0 + t0 + j) * p.Hv + hv) * D + v] = __float2bfloat16(x[j]);
+            }
           }
         }
       }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&bars[VB_READY]);
+      if (v == 0) FQLA_TRACE(1, 2);
+      if constexpr (EXTRA) {
+        if (tile_vn && c >= 0) {
+          fence_proxy_async();
+          mbar_arrive(&bars[VN_READY]);
+        }
+      }
       if (it + 1 < n_it) ok = convert_w(it + 1);
+      if (v == 0) FQLA_TRACE(1, 3);
     }
   } else if (warp >= 12) {
     if constexpr (!NO_O) {
     // =============================== O group ===============================
-    // M = 64 accumulators are read with the 16-lane shape: lane l of warp q owns rows
+    // P is an M = 64 accumulator read with the 16-lane shape: lane l of warp q owns rows
     // 16q + l/4 and 16q + l/4 + 8, and in every group of 8 columns the pair 2*(l%4), +1.
+    // The output accumulators are M = 128: one thread per value index, 64 tokens each.
     const int wq = warp & 3;
+    const int v = tid - 384;
     const int row_a = 16 * wq + (lane >> 2), row_b = row_a + 8, cp = 2 * (lane & 3);
-    const uint32_t lanes_o = (uint32_t)(wq * 32) << 16;        // O1 / O2: lanes 0-15 of the quarter
-    const uint32_t lanes_p = (uint32_t)(wq * 32 + 16) << 16;   // P: lanes 16-31
+    const uint32_t lanes_p = (uint32_t)(wq * 32) << 16;  // P: lanes 0-15 of the quarter
     // c counts the chunks of the sequence itself; the lead-in chunks (iterations j < lead) have no
     // output products, so the barriers of this group's products are phased by c, while stages and
     // vector slots follow the iteration j = c + lead
+    // The output tile leaves through shared memory and one TMA store per 64-column box: a
+    // read-out thread owns one value index of all 64 tokens, and global stores of that shape (two
+    // 64-byte pieces per warp instruction) are an order of magnitude slower than the rest of the
+    // chunk.  Only a sequence's ragged last chunk is written with plain stores, row by row.
     auto epilogue = [&](int c) {
-      const float* vs = vec + ((c + lead) & 3) * VEC_SLOT_FLOATS;
+      const int it = c + lead;  // (trace window index)
+      const float* sg = vec + (it & 3) * VEC_SLOT_FLOATS + V_SGAM * CHUNK;
       const long long row0 = sp.bos + (long long)c * CHUNK;
       const int valid = min(CHUNK, sp.len - c * CHUNK);
-      const float sg_a = vs[V_SGAM * CHUNK + row_a], sg_b = vs[V_SGAM * CHUNK + row_b];
-      bf16* o_a = p.o + ((row0 + row_a) * p.Hv + hv) * D + cp;
-      bf16* o_b = p.o + ((row0 + row_b) * p.Hv + hv) * D + cp;
-      const bool wr_a = p.o != nullptr && row_a < valid, wr_b = p.o != nullptr && row_b < valid;
+      if (v == 0) tma_store_wait_read();  // the store of the chunk before has read the tile
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      // The accumulators hold o transposed ([value index][token]).  Read with the 16-lane shape, a
+      // lane gets mma-style fragments: rows l/4 and l/4 + 8 of a 16-row half, token pairs
+      // 8 i + 2 (l%4), +1.  stmatrix with .trans writes each 8 x 8 fragment block transposed, i.e.
+      // as eight 16-byte pieces "8 value indices of one token": the tile comes out token-major
+      // without a single shuffle.
+      const int l4 = lane & 3, mtx = lane >> 3, r8 = lane & 7;
+      float2 sgv[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) sgv[i] = *reinterpret_cast<const float2*>(sg + 8 * i + 2 * l4);
 #pragma unroll 1
-      for (int c0 = 0; c0 < D; c0 += 64) {
+      for (int h = 0; h < 2; ++h) {
+        if (v == 0) FQLA_TRACE(2, h ? 7 : 5);
+        const uint32_t lanes = (uint32_t)(wq * 32 + 16 * h) << 16;
         float a[32], b[32];
-        tmem_ld_16x64(tmem + lanes_o + TM_O1 + c0, a);
-        tmem_ld_16x64(tmem + lanes_o + TM_O2 + c0, b);
+        tmem_ld_16x64(tmem + lanes + TM_O1, a);
+        tmem_ld_16x64(tmem + lanes + TM_O2, b);
         tmem_ld_wait();
-        if (c0 + 64 >= D) {  // all tensor-memory reads of this chunk's output are done
+        if (v == 0) FQLA_TRACE(2, h ? 8 : 6);
+        if (h == 1) {  // all tensor-memory reads of this chunk's output are done
           tc_fence_before();
           mbar_arrive(&bars[O_FREE]);
         }
-        // A lane holds one column pair of every group of 8 columns; the four lanes of a quad
-        // (same rows) exchange words (4 x 4 transposes, two butterfly steps each) so that each
-        // lane ends up with 8 consecutive columns: a store instruction then writes 64 contiguous
-        // bytes of 8 rows instead of 16 bytes of 8 rows.
-        uint32_t wa[8], wb[8];
+        // this lane supplies the address of row r8 of matrix mtx of every store: matrices 0, 1 are
+        // the two 8-row blocks of token block i, matrices 2, 3 those of token block i + 1
+        const int pv = ((wq & 1) * 32 + 16 * h) >> 3;  // 16-byte piece of rows 0-7 inside the box
+        const uint32_t base = s32(smem + OFF_O + (wq >> 1) * 8192) +
+                              (uint32_t)((8 * (mtx >> 1) + r8) * 128 + (((pv + (mtx & 1)) ^ r8) << 4));
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          wa[i] = pack_bf16(sg_a * a[4 * i] + b[4 * i], sg_a * a[4 * i + 1] + b[4 * i + 1]);
-          wb[i] = pack_bf16(sg_b * a[4 * i + 2] + b[4 * i + 2], sg_b * a[4 * i + 3] + b[4 * i + 3]);
+        for (int i = 0; i < 8; i += 2) {
+          uint32_t w[4];
+#pragma unroll
+          for (int z = 0; z < 2; ++z) {
+            const float2 s2 = sgv[i + z];
+            const float* aa = a + 4 * (i + z);
+            const float* bb = b + 4 * (i + z);
+            w[2 * z] = pack_bf16(s2.x * aa[0] + bb[0], s2.y * aa[1] + bb[1]);
+            w[2 * z + 1] = pack_bf16(s2.x * aa[2] + bb[2], s2.y * aa[3] + bb[3]);
+          }
+          stmatrix_x4_trans(base + (uint32_t)(i * 1024), w[0], w[1], w[2], w[3]);
         }
-#pragma unroll
-        for (int h4 = 0; h4 < 8; h4 += 4) {
-          quad_transpose(wa + h4, lane);
-          quad_transpose(wb + h4, lane);
-          // lane j of the quad now holds columns c0 + 8 h4 + 8 j .. + 7 (o_a, o_b include 2 j)
-          if (wr_a)
-            *reinterpret_cast<uint4*>(o_a + c0 + 8 * h4 + 3 * cp) = make_uint4(wa[h4], wa[h4 + 1], wa[h4 + 2], wa[h4 + 3]);
-          if (wr_b)
-            *reinterpret_cast<uint4*>(o_b + c0 + 8 * h4 + 3 * cp) = make_uint4(wb[h4], wb[h4 + 1], wb[h4 + 2], wb[h4 + 3]);
+      }
+      fence_proxy_async();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (valid == CHUNK) {
+        if (v == 0) {
+          tma_store_2d(&map_o, hv * D, (int)row0, smem + OFF_O);
+          tma_store_2d(&map_o, hv * D + 64, (int)row0, smem + OFF_O + 8192);
+          tma_store_commit();
+        }
+      } else {
+        // 16 pieces of 16 bytes per row; piece pc of row r sits at pc ^ (r & 7) inside its box
+        for (int i = v; i < valid * 16; i += 128) {
+          const int r = i >> 4, pc = i & 15;
+          const uint4 w = *reinterpret_cast<const uint4*>(smem + OFF_O + (pc >> 3) * 8192 + r * 128 +
+                                                          (((pc & 7) ^ (r & 7)) << 4));
+          *reinterpret_cast<uint4*>(p.o + ((row0 + r) * p.Hv + hv) * D + pc * 8) = w;
         }
       }
     };
@@ -444,25 +498,29 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
       // the same parity; the wait for this chunk's P below is what orders the reads)
       ok = WAIT(FULL0 + (j & 1), (j >> 1) & 1);
       if (!ok) break;
+      // the epilogue of the chunk before first: the issuing thread needs its accumulators free
+      // (O_FREE) before this chunk's state update, and Pg only after it
       if (it > 0) {
         ok = WAIT(O_DONE, (it - 1) & 1);
         if (!ok) break;
         tc_fence_after();
-        SEC_BEGIN();
+        if (v == 0) FQLA_TRACE(2, 1);
         epilogue(it - 1);
-        SEC_END(SEC_A);
+        if (v == 0) FQLA_TRACE(2, 0);
       }
+      if (v == 0) FQLA_TRACE(2, 2);
       ok = WAIT(P_DONE, it & 1);
       if (!ok) break;
       tc_fence_after();
-      SEC_BEGIN();
+      if (v == 0) FQLA_TRACE(2, 3);
       // Pg = s P exp(g_row - g_col) = P exp2((g_row - g_col) log2e + log2 s), col <= row
       {
         const float ga2 = vs[V_G * CHUNK + row_a] * 1.4426950408889634f + log2_scale;
         const float gb2 = vs[V_G * CHUNK + row_b] * 1.4426950408889634f + log2_scale;
         float x[32];
-        tmem_ld_16x64(tmem + lanes_p + TM_O1, x);
+        tmem_ld_16x64(tmem + lanes_p + TM_PW, x);
         tmem_ld_wait();
+        tc_fence_before();
         unsigned char* pa = smem + OFF_P + row_a * 128 + cp * 2;
         unsigned char* pb = smem + OFF_P + row_b * 128 + cp * 2;
         // column groups entirely above this warp's rows stay zero (written once at start)
@@ -481,9 +539,8 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
         }
       }
       fence_proxy_async();
-      tc_fence_before();
       mbar_arrive(&bars[P_READY]);
-      SEC_END(SEC_B);
+      if (v == 0) FQLA_TRACE(2, 4);
     }
     if (ok && n_out > 0) {
       ok = WAIT(O_DONE, (n_out - 1) & 1);
@@ -492,6 +549,7 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
         epilogue(n_out - 1);
       }
     }
+    if (v == 0) tma_store_wait_all();
     // rows of o past the end of the last packed sequence come out zero
     if (p.o && p.lay.cu.ptr && n == p.N - 1) {
       const long long end = sp.bos + sp.len;
@@ -504,16 +562,13 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
     // =============================== MMA issuer ===============================
     if (lane == 0) {
       constexpr uint32_t ID_P = idesc_bf16(64, 64, 0, 0);
-      constexpr uint32_t ID_O = idesc_bf16(64, 128, 0, 0);
-      constexpr uint32_t ID_UT = idesc_bf16(128, 64, 1, 0);            // A = V tile, MN-major
-      constexpr uint32_t ID_W = idesc_bf16(64, 128, 0, 1);             // B = K tile, MN-major
-      constexpr uint32_t ID_VN = idesc_bf16(128, 64, 0, 0) | (1u << 13);  // A negated
+      constexpr uint32_t ID_UT = idesc_bf16(128, 64, 1, 0);            // A = V / K tile, MN-major
+      constexpr uint32_t ID_VN = idesc_bf16(128, 64, 0, 1) | (1u << 13);  // A negated; B = w^T tile
+      constexpr uint32_t ID_OT = idesc_bf16(128, 64, 0, 0);            // A from tensor memory
       constexpr uint32_t ID_S = idesc_bf16(128, 128, 0, 1);
       // low descriptor words of every operand tile (see umma_lo); steps are 32-bit adds
-      const uint32_t st_lo = desc_lo_kmajor(smem + OFF_ST), vnt_lo = desc_lo_kmajor(smem + OFF_VNT);
-      const uint32_t w_lo = desc_lo_kmajor(smem + OFF_W), p_lo = desc_lo_kmajor(smem + OFF_P);
+      const uint32_t wmn_lo = desc_lo_mnmajor(smem + OFF_W, 16384), p_lo = desc_lo_kmajor(smem + OFF_P);
       const uint32_t ap_lo = desc_lo_kmajor(smem + OFF_AP), app_lo = desc_lo_kmajor(smem + OFF_APP);
-      const uint32_t vrt_lo = desc_lo_kmajor(smem + OFF_VRT);
       const uint32_t q0_lo = desc_lo_kmajor(smem + OFF_STAGE);
       const uint32_t k0_lo = desc_lo_kmajor(smem + OFF_STAGE + TILE_QK);
       const uint32_t kmn0_lo = desc_lo_mnmajor(smem + OFF_STAGE + TILE_QK, 8192);
@@ -521,94 +576,94 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
       constexpr uint32_t STAGE_LO = STAGE_BYTES >> 4;
       auto issue_u_w = [&](uint32_t so) {  // so = stage offset in descriptor units
         umma_group<4, 128, 0, 2, 0, false>(tmem + TM_UV, vmn0_lo + so, ap_lo, ID_UT);
-        umma_group<4, 2, 0, 128, 0, false>(tmem + TM_W, app_lo, kmn0_lo + so, ID_W);
+        umma_group<4, 128, 0, 2, 0, false>(tmem + TM_PW, kmn0_lo + so, app_lo, ID_UT);
         umma_commit(&bars[W_DONE]);
       };
-      auto issue_p = [&](uint32_t so) {
-        umma_group<8, 2, 512, 2, 512, false>(tmem + TM_P, q0_lo + so, k0_lo + so, ID_P);
-        umma_commit(&bars[P_DONE]);
-      };
       auto store_vn = [&](int it) {  // after VN_READY: the v_new^T tile is complete
-        if (p.tiled && p.vnew && it >= lead) {
-          tma_store_2d(&map_vn, 0, (int)(((sp.chunk_base + (it - lead)) * p.Hv + hv) * D), smem + OFF_VNT);
-          tma_store_commit();
-        }
+        tma_store_2d(&map_vn, 0, (int)(((sp.chunk_base + (it - lead)) * p.Hv + hv) * D), smem + OFF_VNT);
+        tma_store_commit();
       };
       for (int it = 0; it < n_it && ok; ++it) {
-        const int s = it & 1;
+        const int s = it & 1, c = it - lead;  // c < 0: lead-in chunk, no output products
         const uint32_t so = s ? STAGE_LO : 0u, so_next = s ? 0u : STAGE_LO;
+        const bool with_o = !NO_O && c >= 0;
         if (it == 0) {
           ok = WAIT(FULL0, 0) && WAIT(AP_READY, 0);
           if (!ok) break;
           tc_fence_after();
           issue_u_w(0);
         }
+        FQLA_TRACE(3, 0);
         ok = WAIT(S_COPY, it & 1) && WAIT(W_READY, it & 1);
         if (!ok) break;
         tc_fence_after();
-        SEC_BEGIN();
-        // Vn^T = u^T - S^T w^T   (accumulates onto u^T)
-        umma_group<8, 2, 1024, 2, 512, true>(tmem + TM_UV, st_lo, w_lo, ID_VN);
+        FQLA_TRACE(3, 1);
+        // Vn^T = u^T - S^T w^T   (accumulates onto u^T; A = packed S^T in tensor memory)
+        umma_ts_group<8, 8, 128, true>(tmem + TM_UV, tmem + TM_SB, wmn_lo, ID_VN);
         if constexpr (EXTRA) tma_store_wait_read();  // v_new^T of the chunk before has left its tile
         umma_commit(&bars[VN_DONE]);
-        if constexpr (EXTRA) {
-          if (p.tiled && p.h && it >= lead) {  // the operand copy of S^T is the state entering this chunk
-            const int y = (int)(((sp.chunk_base + (it - lead)) * p.Hv + hv) * D);
-            tma_store_2d(&map_h, 0, y, smem + OFF_ST);
-            tma_store_2d(&map_h, 64, y, smem + OFF_ST + 16384);
-            tma_store_commit();
-          }
-        }
-        SEC_END(SEC_A);
-        const int c = it - lead;  // < 0: lead-in chunk, no output products
-        if (!NO_O && c >= 0) {
+        FQLA_TRACE(3, 2);
+        if (with_o) {
+          // P of this chunk goes here, into the time the value group needs for Vn: the output
+          // group turns it into Pg right away (its columns held w^T of this chunk until the value
+          // group made the operand tile of it: W_READY above)
+          umma_group<8, 2, 512, 2, 512, false>(tmem + TM_PW, q0_lo + so, k0_lo + so, ID_P);
+          umma_commit(&bars[P_DONE]);
           if (c > 0) {
             ok = WAIT(O_FREE, (c - 1) & 1);
             if (!ok) break;
             tc_fence_after();
           }
-          SEC_BEGIN();
-          // O1 = Q S      (B = S^T copy: N = v rows, K = k)
-          umma_group<8, 2, 512, 2, 1024, false>(tmem + TM_O1, q0_lo + so, st_lo, ID_O);
-          // P of this chunk goes here, into the time the value group needs for Vn: the output
-          // group turns it into Pg while the state update runs (it read P of the chunk before
-          // ahead of the output product issued at the end of the previous iteration)
-          issue_p(so);
-          SEC_END(SEC_B);
+          // O1^T = S^T Q^T   (B = q tile, K-major)
+          umma_ts_group_kmajor_b<8>(tmem + TM_O1, tmem + TM_SB, q0_lo + so, ID_OT);
         }
-        ok = WAIT(VR_READY, it & 1) && WAIT(S_DEC, it & 1);
+        if constexpr (EXTRA) {
+          if (tile_h && c >= 0) {  // the state entering this chunk, as an operand tile
+            ok = WAIT(ST_READY, c & 1);
+            if (!ok) break;
+            const int y = (int)(((sp.chunk_base + c) * p.Hv + hv) * D);
+            tma_store_2d(&map_h, 0, y, smem + OFF_ST);
+            tma_store_2d(&map_h, 64, y, smem + OFF_ST + 16384);
+            tma_store_commit();
+          }
+        }
+        FQLA_TRACE(3, 3);
+        ok = WAIT(VB_READY, it & 1) && WAIT(S_DEC, it & 1);
         if (!ok) break;
         tc_fence_after();
-        SEC_BEGIN();
-        // S^T += (rho Vn)^T K      (B = K tile read MN-major: contraction over its 64 rows)
-        umma_group<4, 2, 0, 128, 0, true>(tmem + TM_S, vrt_lo, kmn0_lo + so, ID_S);
+        FQLA_TRACE(3, 4);
+        // S^T += (rho Vn)^T K      (A = packed rho Vn^T; B = K tile read MN-major)
+        umma_ts_group<4, 8, 128, true>(tmem + TM_S, tmem + TM_VRB, kmn0_lo + so, ID_S);
         if constexpr (EXTRA) tma_store_wait_read();  // the S^T tile may be rewritten after this
         umma_commit(&bars[S_DONE]);
         umma_commit(&bars[EMPTY0 + s]);  // last product that reads this stage
-        SEC_END(SEC_C);
-        if (it + 1 < n_it) {
-          ok = WAIT(FULL0 + (s ^ 1), ((it + 1) >> 1) & 1) && WAIT(AP_READY, (it + 1) & 1) &&
-               WAIT(VN_READY, it & 1);  // the V group has read Vn^T out of TM_UV
+        FQLA_TRACE(3, 5);
+        if constexpr (EXTRA) {
+          if (tile_vn && c >= 0) {
+            ok = WAIT(VN_READY, c & 1);
+            if (!ok) break;
+            store_vn(it);
+          }
+        }
+        if (with_o) {
+          ok = WAIT(P_READY, c & 1);
           if (!ok) break;
           tc_fence_after();
-          SEC_BEGIN();
-          issue_u_w(so_next);
-          SEC_END(SEC_D);
-          if constexpr (EXTRA) store_vn(it);
-        }
-        ok = (NO_O || c < 0 || WAIT(P_READY, c & 1)) && (it + 1 < n_it || WAIT(VN_READY, it & 1));
-        if (!ok) break;
-        tc_fence_after();
-        if constexpr (EXTRA) {
-          if (it + 1 >= n_it) store_vn(it);
-        }
-        if (!NO_O && c >= 0) {
-          SEC_BEGIN();
-          // O2 = Pg Vn     (B = Vn^T copy: N = v rows, K = tok')
-          umma_group<4, 2, 0, 2, 0, false>(tmem + TM_O2, p_lo, vnt_lo, ID_O);
+          // O2^T = Vn^T Pg^T   (A = packed Vn^T; B = Pg, K-major)
+          umma_ts_group<4, 8, 2, false>(tmem + TM_O2, tmem + TM_VNB, p_lo, ID_OT);
           umma_commit(&bars[O_DONE]);
-          SEC_END(SEC_E);
         }
+        FQLA_TRACE(3, 6);
+        if (it + 1 < n_it) {
+          // u^T and w^T of the next chunk: u^T overwrites Vn^T (read by the value group: VB_READY
+          // above), w^T overwrites P (read by the output group: P_READY above)
+          ok = WAIT(FULL0 + (s ^ 1), ((it + 1) >> 1) & 1) && WAIT(AP_READY, (it + 1) & 1);
+          if (!ok) break;
+          tc_fence_after();
+          FQLA_TRACE(3, 7);
+          issue_u_w(so_next);
+        }
+        FQLA_TRACE(3, 8);
       }
       if constexpr (EXTRA) tma_store_wait_all();
     }
@@ -729,7 +784,6 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
       ok = WAIT(FULLA0 + s, (it >> 1) & 1);
       if (ok && it > 0) ok = WAIT(W_DONE, (it - 1) & 1);  // u, w of the chunk before are done
       if (!ok) break;
-      SEC_BEGIN();
       const float* vs = vec + (it & 3) * VEC_SLOT_FLOATS;
       const float4 b0 = *reinterpret_cast<const float4*>(vs + V_BETA * CHUNK + 8 * c8);
       const float4 b1 = *reinterpret_cast<const float4*>(vs + V_BETA * CHUNK + 8 * c8 + 4);
@@ -753,17 +807,9 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
         mbar_arrive(&bars[AP_READY]);
         mbar_arrive(&bars[EMPTYA0 + s]);  // the A tile of this stage is no longer read here
       }
-      SEC_END(SEC_A);
     }
   }
 
-  if (PROFILE && blockIdx.x == 0 && (tid % 128 == 0 || tid == 32 || tid == 64)) {
-    int role = tid == 128 ? 0 : tid == 256 ? 1 : tid == 384 ? 2 : tid == 0 ? 3 : tid == 32 ? 4 : 5;
-    for (int i = 0; i < 24; ++i) g_wait_profile[role * 24 + i] = waited[i];
-    if (tid == 128) g_wait_profile[6 * 24] = clock64() - t_start;
-  }
-#undef SEC_BEGIN
-#undef SEC_END
   // ---- teardown: everybody meets, then the allocating warp frees tensor memory
   if (!ok) *abort_flag = 1;
   tc_fence_before();
@@ -786,7 +832,7 @@ int launch_fwd_tc(const void* q, const void* k, const void* v, const void* A, co
                   void* vnew, int tiled, const int* lead, int N, int Hq, int Hv, long long T_rows,
                   float scale, SeqLayout lay, cudaStream_t st) {
   using namespace fwdtc;
-  CUtensorMap mq, mk, mv, ma, mh, mvn;
+  CUtensorMap mq, mk, mv, ma, mh, mvn, mo;
   int rc;
   // without q (recomputation of h and v_new for the backward pass) the state-only variant runs;
   // its q map is never used and only has to be a valid map
@@ -796,6 +842,8 @@ int launch_fwd_tc(const void* q, const void* k, const void* v, const void* A, co
   if ((rc = make_map(&ma, A, T_rows, (long long)Hv * CHUNK))) return rc;
   mh = mq;
   mvn = mq;
+  mo = mq;
+  if (o && (rc = make_map(&mo, o, T_rows, (long long)Hv * D))) return rc;
   if (tiled) {
     // an upper bound of the chunk count: the maps only have to cover what the kernel stores
     const long long max_chunks = (T_rows + CHUNK - 1) / CHUNK + N;
@@ -808,33 +856,23 @@ int launch_fwd_tc(const void* q, const void* k, const void* v, const void* A, co
   p.g = g; p.beta = beta; p.beta_is_f32 = beta_is_f32; p.h0 = h0; p.ht = ht;
   p.o = (bf16*)o; p.h = (bf16*)h; p.vnew = (bf16*)vnew;
   p.N = N; p.Hq = Hq; p.Hv = Hv; p.T_rows = T_rows; p.scale = scale; p.lay = lay;
-  p.profile = 0;
   const bool extra = h != nullptr || vnew != nullptr;
-  auto launch = [&](auto kernel) {
-    int err = configure_smem((const void*)kernel, SMEM_BYTES);
+  auto launch = [&](auto kernel, int smem_bytes) {
+    int err = configure_smem((const void*)kernel, smem_bytes);
     if (err != 0) return err;
-    kernel<<<(unsigned)(N * Hv), 512, SMEM_BYTES, st>>>(p, mq, mk, mv, ma, mh, mvn);
+    kernel<<<(unsigned)(N * Hv), 512, smem_bytes, st>>>(p, mq, mk, mv, ma, mh, mvn, mo);
     return (int)cudaGetLastError();
   };
-#ifdef FQLA_DIAGNOSTICS  // wait/section cycle counters of the first CTA (development builds only)
-  static const bool profile = getenv("FQLA_PROFILE") != nullptr;
-  p.profile = profile ? 1 : 0;
-  if (p.profile) return launch(fwd_tc_kernel<true, true, false>);
-#endif
-  if (!q && !o) return launch(fwd_tc_kernel<false, true, true>);  // recomputation of h, v_new
-  if (extra) return launch(fwd_tc_kernel<false, true, false>);
-  return launch(fwd_tc_kernel<false, false, false>);
+  if (!q && !o) return launch(fwd_tc_kernel<true, true>, SMEM_BYTES_EXTRA);  // recomputation of h, v_new
+  if (extra) return launch(fwd_tc_kernel<true, false>, SMEM_BYTES_EXTRA);
+  return launch(fwd_tc_kernel<false, false>, SMEM_BYTES);
 }
 
 }  // namespace fqla
 
 #ifdef FQLA_DIAGNOSTICS
-extern "C" int fqla_debug_abort_info(int* out) {
-  return (int)cudaMemcpyFromSymbol(out, fqla::g_fwd_abort_info, sizeof(int));
-}
-
-extern "C" int fqla_debug_wait_profile(long long* out168) {
-  return (int)cudaMemcpyFromSymbol(out168, fqla::g_wait_profile, sizeof(long long) * 7 * 24);
+extern "C" int fqla_debug_fwd_trace(long long* out960) {
+  return (int)cudaMemcpyFromSymbol(out960, fqla::g_fwd_trace, sizeof(long long) * 960);
 }
 #endif
 

@@ -90,6 +90,17 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
   return false;
 }
 
+// Four 8 x 8 bf16 matrices from registers to shared memory, each stored TRANSPOSED: register i of
+// lane l carries the elements (row l/4, columns 2(l%4), +1) of matrix i - the layout of an
+// mma / 16x256b tensor-memory fragment - and lands at (row 2(l%4) + {0,1}, column l/4) of the
+// stored matrix, whose row r (16 bytes) starts at the address given by lane 8i + r.
+__device__ __forceinline__ void stmatrix_x4_trans(uint32_t saddr, uint32_t r0, uint32_t r1,
+                                                  uint32_t r2, uint32_t r3) {
+  asm volatile("stmatrix.sync.aligned.m8n8.x4.trans.shared.b16 [%0], {%1, %2, %3, %4};" ::"r"(saddr),
+               "r"(r0), "r"(r1), "r"(r2), "r"(r3)
+               : "memory");
+}
+
 // ---- proxy / tcgen05 fences ------------------------------------------------------------------
 __device__ __forceinline__ void fence_proxy_async() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -179,6 +190,18 @@ __device__ __forceinline__ void tmem_ld_16x64(uint32_t taddr, float (&v)[32]) {
       : "r"(taddr)
       : "memory");
 }
+// 32 lanes x 16 consecutive columns -> 16 registers per thread
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
@@ -193,6 +216,16 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) 
       "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]),
       "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
       "r"(r[30]), "r"(r[31]), "r"(taddr)
+      : "memory");
+}
+// 32 lanes x 16 consecutive columns from 16 registers per thread (e.g. 32 packed bf16 per lane)
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15};" ::"r"(r[0]),
+      "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+      "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+      "r"(taddr)
       : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() {
@@ -283,6 +316,56 @@ __device__ __forceinline__ void umma_group(uint32_t d_tmem, uint32_t a_lo, uint3
     const uint32_t b = b_lo + (uint32_t)((j & 3) * B_STEP + (j >> 2) * B_BLK);
     if (j == 0 && !ACC_FIRST) umma_lo<false>(d_tmem, a, b, idesc);
     else umma_lo<true>(d_tmem, a, b, idesc);
+  }
+}
+
+// ---- A operand in tensor memory ("TS" form) -------------------------------------------------------
+// The A matrix [M = 128 rows][K] sits in tensor memory: lane = row, one 32-bit column holds the
+// two bf16 elements k = 2c (low half) and k = 2c + 1 (high half); a K step of 16 elements is 8
+// columns.  It is written there with tcgen05.st by the thread that owns the lane.  B comes from
+// shared memory as usual.  The product reads no shared memory for A: the tensor pipe, whose rate
+// in the SS form is set by the 128 B/clk operand fetch, runs at its arithmetic rate.
+template <bool ACCUMULATE>
+__device__ __forceinline__ void umma_ts_lo(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo,
+                                           uint32_t idesc) {
+  if (ACCUMULATE) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+        "setp.ne.b32 p, 1, 0;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_tmem), "r"(b_lo), "r"(DESC_HI), "r"(idesc)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+        "setp.ne.b32 p, 0, 0;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_tmem), "r"(b_lo), "r"(DESC_HI), "r"(idesc)
+        : "memory");
+  }
+}
+// NK K-steps; A advances A_COLS columns per step, B by B_STEP descriptor units (16 bytes) per step
+// (an MN-major B tile: 128 = 16 rows; a K-major B tile of one 64-column block: 2).
+template <int NK, int A_COLS, int B_STEP, bool ACC_FIRST>
+__device__ __forceinline__ void umma_ts_group(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo,
+                                              uint32_t idesc) {
+#pragma unroll
+  for (int j = 0; j < NK; ++j) {
+    if (j == 0 && !ACC_FIRST) umma_ts_lo<false>(d_tmem, a_tmem, b_lo, idesc);
+    else umma_ts_lo<true>(d_tmem, a_tmem + (uint32_t)(j * A_COLS), b_lo + (uint32_t)(j * B_STEP), idesc);
+  }
+}
+// B = a K-major tile of NK / 4 blocks of 64 columns (block stride 8192 bytes), fresh accumulator.
+template <int NK>
+__device__ __forceinline__ void umma_ts_group_kmajor_b(uint32_t d_tmem, uint32_t a_tmem,
+                                                       uint32_t b_lo, uint32_t idesc) {
+#pragma unroll
+  for (int j = 0; j < NK; ++j) {
+    const uint32_t b = b_lo + (uint32_t)((j & 3) * 2 + (j >> 2) * 512);
+    if (j == 0) umma_ts_lo<false>(d_tmem, a_tmem, b, idesc);
+    else umma_ts_lo<true>(d_tmem, a_tmem + (uint32_t)(j * 8), b, idesc);
   }
 }
 
