@@ -56,13 +56,24 @@ __device__ int g_device_status = 0;
 // Development builds only: clock stamps of the role leaders of CTA 0 over a window of chunks,
 // [role 0..5][chunk in window 0..15][tag 0..9].
 __device__ long long g_fwd_trace[6 * 16 * 10];
+__device__ int g_trace_cta = 0;               // which CTA records the role trace
+__device__ long long g_cta_cycles[2 * 1024];  // per CTA: SM id, cycles from entry to exit
+// chain issuer of CTA 0 and CTA 77: clock at the start of every chunk, [cta 0/1][chunk 0..127];
+// entries 126, 127: kernel entry and exit of that CTA
+__device__ long long g_fwd_chunk_clock[2 * 128];
+#define FQLA_CHUNK_CLOCK(idx)                                                              \
+  do {                                                                                     \
+    if ((blockIdx.x == 0 || blockIdx.x == 77) && (idx) < 128)                              \
+      g_fwd_chunk_clock[(blockIdx.x == 0 ? 0 : 128) + (idx)] = clock64();                  \
+  } while (0)
 #define FQLA_TRACE(role, tag)                                                         \
   do {                                                                                \
-    if (blockIdx.x == 0 && it >= 24 && it < 40)                                       \
+    if (blockIdx.x == g_trace_cta && it >= 24 && it < 40)                             \
       g_fwd_trace[((role) * 16 + (it - 24)) * 10 + (tag)] = clock64();               \
   } while (0)
 #else
 #define FQLA_TRACE(role, tag) do { } while (0)
+#define FQLA_CHUNK_CLOCK(idx) do { } while (0)
 #endif
 
 struct FwdTcParams {
@@ -125,7 +136,9 @@ enum { FULL0 = 0, FULL1, EMPTY0, EMPTY1, S_COPY, S_DEC, VN_DONE, S_DONE, P_DONE,
        // the A tile and the per-row vectors of a chunk travel one chunk ahead of q, k, v
        FULLA0, FULLA1, EMPTYA0, EMPTYA1, PRIVA,
        // tile outputs: the shared-memory copies of S^T / Vn^T are complete
-       ST_READY, VN_READY };
+       ST_READY, VN_READY,
+       // the output product that reads the packed copy of S^T has completed
+       SB_FREE };
 // vectors inside a slot; V_GL holds gamma_last at [0]
 enum { V_G = 0, V_BETA = 1, V_BG = 2, V_RHO = 3, V_SGAM = 4, V_GL = 5 };
 }  // namespace fwdtc
@@ -163,15 +176,20 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
   const int n_it = sp.n_chunks == 0 ? 0 : sp.n_chunks + lead;
   const bool tile_h = EXTRA && p.tiled && p.h, tile_vn = EXTRA && p.tiled && p.vnew;
 
+  if (tid == 0) FQLA_CHUNK_CLOCK(126);
+#ifdef FQLA_DIAGNOSTICS
+  const long long g_fwd_chunk_clock_entry = clock64();
+#endif
   if (tid == 0) {
     mbar_init(&bars[FULL0], 1);
     mbar_init(&bars[FULL1], 1);
-    mbar_init(&bars[EMPTY0], 1);  // MMA commit
-    mbar_init(&bars[EMPTY1], 1);
+    mbar_init(&bars[EMPTY0], 2);  // MMA commits of the two issuing threads
+    mbar_init(&bars[EMPTY1], 2);
+    mbar_init(&bars[SB_FREE], 1);
     mbar_init(&bars[FULLA0], 1);
     mbar_init(&bars[FULLA1], 1);
-    mbar_init(&bars[EMPTYA0], 2);  // the two prep warps, the only readers of the raw A tile
-    mbar_init(&bars[EMPTYA1], 2);
+    mbar_init(&bars[EMPTYA0], 128);  // the output group, the only reader of the raw A tile
+    mbar_init(&bars[EMPTYA1], 128);
     mbar_init(&bars[PRIVA], 1);
     mbar_init(&bars[S_COPY], 128);
     mbar_init(&bars[S_DEC], 128);
@@ -184,7 +202,7 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
     mbar_init(&bars[W_READY], 128);
     mbar_init(&bars[P_READY], 128);
     mbar_init(&bars[O_FREE], 128);
-    mbar_init(&bars[AP_READY], 2);
+    mbar_init(&bars[AP_READY], 128);
     mbar_init(&bars[PRIV], 1);
     mbar_init(&bars[ST_READY], 128);
     mbar_init(&bars[VN_READY], 128);
@@ -210,6 +228,7 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
   bool ok = true;
   auto WAIT = [&](int idx, uint32_t parity) { return mbar_wait(&bars[idx], parity, abort_flag); };
 
+
   // Role of each warp.  The MMA issuer is warp 0 and the producer warp 1 on purpose: among the
   // warps of one scheduler the oldest (lowest id) wins when several are ready, and these two
   // single-thread roles must never queue behind the arithmetic of the compute groups.
@@ -230,6 +249,8 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
       const int s = it & 1;
       if (v == 0) FQLA_TRACE(0, 0);
       if (it > 0) ok = WAIT(S_DONE, (it - 1) & 1);
+      // the output product of the chunk before, issued by the other thread, has read the copy
+      if (!NO_O && ok && it - 1 >= lead) ok = WAIT(SB_FREE, (it - 1 - lead) & 1);
       if (!ok) break;
       tc_fence_after();
       if (v == 0) FQLA_TRACE(0, 1);
@@ -355,6 +376,11 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
       if (v == 0) FQLA_TRACE(1, 0);
       ok = WAIT(FULL0 + (it & 1), (it >> 1) & 1) && WAIT(VN_DONE, it & 1);
       if (!ok) break;
+      // the output product that reads Vn^T of the chunk before is issued by the other thread
+      if (!NO_O && c >= 1 && !WAIT(O_DONE, (c - 1) & 1)) {
+        ok = false;
+        break;
+      }
       tc_fence_after();
       if (v == 0) FQLA_TRACE(1, 1);
       const float* rho = vec + (it & 3) * VEC_SLOT_FLOATS + V_RHO * CHUNK;
@@ -407,11 +433,12 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
       if (v == 0) FQLA_TRACE(1, 3);
     }
   } else if (warp >= 12) {
-    if constexpr (!NO_O) {
     // =============================== O group ===============================
+    // Per chunk: the epilogue of the chunk before, Pg of this chunk, and A' = A diag(beta),
+    // A'' = A diag(beta gamma) of the NEXT chunk (the scaled tiles the issuing thread needs for
+    // u^T, w^T at the end of this chunk).  The state-only variant keeps only the last part.
     // P is an M = 64 accumulator read with the 16-lane shape: lane l of warp q owns rows
     // 16q + l/4 and 16q + l/4 + 8, and in every group of 8 columns the pair 2*(l%4), +1.
-    // The output accumulators are M = 128: one thread per value index, 64 tokens each.
     const int wq = warp & 3;
     const int v = tid - 384;
     const int row_a = 16 * wq + (lane >> 2), row_b = row_a + 8, cp = 2 * (lane & 3);
@@ -489,112 +516,134 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
         }
       }
     };
-    const float log2_scale = log2f(p.scale);
-    const int n_out = n_it - lead;  // chunks with output
-    for (int it = 0; it < n_out && ok; ++it) {
-      const int j = it + lead;
+    // A', A'': thread t owns the 8 columns 8 (t%8) .. of the rows t/8 + 16 i: its 16 scale factors
+    // stay in registers, and the eight threads of a row touch the eight 16-byte pieces of that row
+    // (one 128-byte line per access, conflict-free)
+    auto scale_a = [&](int j) {
+      const int sj = j & 1, c8 = v & 7, r0 = v >> 3;
+      const int pc = c8 ^ (r0 & 7);  // physical piece: rows r0 + 16 i all have (row & 7) == r0 & 7
+      if (!WAIT(FULLA0 + sj, (j >> 1) & 1)) return false;
+      if (j > 0 && !WAIT(W_DONE, (j - 1) & 1)) return false;  // u, w of the chunk before are done
       const float* vs = vec + (j & 3) * VEC_SLOT_FLOATS;
-      // (after a lead-in of four or more chunks the first of these waits may see an older phase of
-      // the same parity; the wait for this chunk's P below is what orders the reads)
-      ok = WAIT(FULL0 + (j & 1), (j >> 1) & 1);
-      if (!ok) break;
-      // the epilogue of the chunk before first: the issuing thread needs its accumulators free
-      // (O_FREE) before this chunk's state update, and Pg only after it
-      if (it > 0) {
-        ok = WAIT(O_DONE, (it - 1) & 1);
-        if (!ok) break;
-        tc_fence_after();
-        if (v == 0) FQLA_TRACE(2, 1);
-        epilogue(it - 1);
-        if (v == 0) FQLA_TRACE(2, 0);
-      }
-      if (v == 0) FQLA_TRACE(2, 2);
-      ok = WAIT(P_DONE, it & 1);
-      if (!ok) break;
-      tc_fence_after();
-      if (v == 0) FQLA_TRACE(2, 3);
-      // Pg = s P exp(g_row - g_col) = P exp2((g_row - g_col) log2e + log2 s), col <= row
-      {
-        const float ga2 = vs[V_G * CHUNK + row_a] * 1.4426950408889634f + log2_scale;
-        const float gb2 = vs[V_G * CHUNK + row_b] * 1.4426950408889634f + log2_scale;
-        float x[32];
-        tmem_ld_16x64(tmem + lanes_p + TM_PW, x);
-        tmem_ld_wait();
-        tc_fence_before();
-        unsigned char* pa = smem + OFF_P + row_a * 128 + cp * 2;
-        unsigned char* pb = smem + OFF_P + row_b * 128 + cp * 2;
-        // column groups entirely above this warp's rows stay zero (written once at start)
+      const float4 b0 = *reinterpret_cast<const float4*>(vs + V_BETA * CHUNK + 8 * c8);
+      const float4 b1 = *reinterpret_cast<const float4*>(vs + V_BETA * CHUNK + 8 * c8 + 4);
+      const float4 g0 = *reinterpret_cast<const float4*>(vs + V_BG * CHUNK + 8 * c8);
+      const float4 g1 = *reinterpret_cast<const float4*>(vs + V_BG * CHUNK + 8 * c8 + 4);
+      const unsigned char* src = smem + OFF_STAGE + sj * STAGE_BYTES + 2 * TILE_QK + TILE_V;
+      uint4 a[4];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          if (i > 2 * wq + 1) continue;
-          const float2 gc = *reinterpret_cast<const float2*>(vs + V_G * CHUNK + 8 * i + cp);
-          const int col = 8 * i + cp;
-          const float e0 = -1.4426950408889634f * gc.x, e1 = -1.4426950408889634f * gc.y;
-          const float a0 = col <= row_a ? x[4 * i] * exp2f(e0 + ga2) : 0.f;
-          const float a1 = col + 1 <= row_a ? x[4 * i + 1] * exp2f(e1 + ga2) : 0.f;
-          const float b0 = col <= row_b ? x[4 * i + 2] * exp2f(e0 + gb2) : 0.f;
-          const float b1 = col + 1 <= row_b ? x[4 * i + 3] * exp2f(e1 + gb2) : 0.f;
-          *reinterpret_cast<uint32_t*>(pa + ((i ^ (row_a & 7)) << 4)) = pack_bf16(a0, a1);
-          *reinterpret_cast<uint32_t*>(pb + ((i ^ (row_b & 7)) << 4)) = pack_bf16(b0, b1);
-        }
+      for (int i = 0; i < 4; ++i)
+        a[i] = *reinterpret_cast<const uint4*>(src + (r0 + 16 * i) * 128 + pc * 16);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int off = (r0 + 16 * i) * 128 + pc * 16;
+        *reinterpret_cast<uint4*>(smem + OFF_AP + off) =
+            make_uint4(scale_bf16x2(a[i].x, b0.x, b0.y), scale_bf16x2(a[i].y, b0.z, b0.w),
+                       scale_bf16x2(a[i].z, b1.x, b1.y), scale_bf16x2(a[i].w, b1.z, b1.w));
+        *reinterpret_cast<uint4*>(smem + OFF_APP + off) =
+            make_uint4(scale_bf16x2(a[i].x, g0.x, g0.y), scale_bf16x2(a[i].y, g0.z, g0.w),
+                       scale_bf16x2(a[i].z, g1.x, g1.y), scale_bf16x2(a[i].w, g1.z, g1.w));
       }
       fence_proxy_async();
-      mbar_arrive(&bars[P_READY]);
-      if (v == 0) FQLA_TRACE(2, 4);
-    }
-    if (ok && n_out > 0) {
-      ok = WAIT(O_DONE, (n_out - 1) & 1);
-      if (ok) {
+      mbar_arrive(&bars[AP_READY]);
+      mbar_arrive(&bars[EMPTYA0 + sj]);  // the A tile of this stage is no longer read here
+      return true;
+    };
+    const float log2_scale = log2f(p.scale);
+    if (n_it > 0) ok = scale_a(0);
+    for (int j = 0; j < n_it && ok; ++j) {
+      const int it = j - lead;  // chunk of the sequence; < 0: lead-in, no output
+      if (!NO_O && it >= 0) {
+        const float* vs = vec + (j & 3) * VEC_SLOT_FLOATS;
+        // the epilogue of the chunk before first: the issuing thread needs its accumulators free
+        // (O_FREE) for this chunk's first output product
+        if (it > 0) {
+          ok = WAIT(O_DONE, (it - 1) & 1);
+          if (!ok) break;
+          tc_fence_after();
+          epilogue(it - 1);
+        }
+        ok = WAIT(FULL0 + (j & 1), (j >> 1) & 1) && WAIT(P_DONE, it & 1);
+        if (!ok) break;
         tc_fence_after();
-        epilogue(n_out - 1);
+        // Pg = s P exp(g_row - g_col) = P exp2((g_row - g_col) log2e + log2 s), col <= row
+        {
+          const float ga2 = vs[V_G * CHUNK + row_a] * 1.4426950408889634f + log2_scale;
+          const float gb2 = vs[V_G * CHUNK + row_b] * 1.4426950408889634f + log2_scale;
+          float x[32];
+          tmem_ld_16x64(tmem + lanes_p + TM_PW, x);
+          tmem_ld_wait();
+          tc_fence_before();
+          unsigned char* pa = smem + OFF_P + row_a * 128 + cp * 2;
+          unsigned char* pb = smem + OFF_P + row_b * 128 + cp * 2;
+          // column groups entirely above this warp's rows stay zero (written once at start)
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            if (i > 2 * wq + 1) continue;
+            const float2 gc = *reinterpret_cast<const float2*>(vs + V_G * CHUNK + 8 * i + cp);
+            const int col = 8 * i + cp;
+            const float e0 = -1.4426950408889634f * gc.x, e1 = -1.4426950408889634f * gc.y;
+            const float a0 = col <= row_a ? x[4 * i] * exp2f(e0 + ga2) : 0.f;
+            const float a1 = col + 1 <= row_a ? x[4 * i + 1] * exp2f(e1 + ga2) : 0.f;
+            const float b0 = col <= row_b ? x[4 * i + 2] * exp2f(e0 + gb2) : 0.f;
+            const float b1 = col + 1 <= row_b ? x[4 * i + 3] * exp2f(e1 + gb2) : 0.f;
+            *reinterpret_cast<uint32_t*>(pa + ((i ^ (row_a & 7)) << 4)) = pack_bf16(a0, a1);
+            *reinterpret_cast<uint32_t*>(pb + ((i ^ (row_b & 7)) << 4)) = pack_bf16(b0, b1);
+          }
+        }
+        fence_proxy_async();
+        mbar_arrive(&bars[P_READY]);
+      }
+      if (j + 1 < n_it) ok = scale_a(j + 1);
+    }
+    if constexpr (!NO_O) {
+      const int n_out = n_it - lead;  // chunks with output
+      if (ok && n_out > 0) {
+        ok = WAIT(O_DONE, (n_out - 1) & 1);
+        if (ok) {
+          tc_fence_after();
+          epilogue(n_out - 1);
+        }
+      }
+      if (v == 0) tma_store_wait_all();
+      // rows of o past the end of the last packed sequence come out zero
+      if (p.o && p.lay.cu.ptr && n == p.N - 1) {
+        const long long end = sp.bos + sp.len;
+        for (long long i = tid - 384; i < (p.T_rows - end) * 16; i += 128)
+          *reinterpret_cast<uint4*>(p.o + ((end + (i >> 4)) * p.Hv + hv) * D + (i & 15) * 8) =
+              make_uint4(0, 0, 0, 0);
       }
     }
-    if (v == 0) tma_store_wait_all();
-    // rows of o past the end of the last packed sequence come out zero
-    if (p.o && p.lay.cu.ptr && n == p.N - 1) {
-      const long long end = sp.bos + sp.len;
-      for (long long i = tid - 384; i < (p.T_rows - end) * 16; i += 128)
-        *reinterpret_cast<uint4*>(p.o + ((end + (i >> 4)) * p.Hv + hv) * D + (i & 15) * 8) =
-            make_uint4(0, 0, 0, 0);
-    }
-    }  // !NO_O
-  } else if (warp == 0) {
-    // =============================== MMA issuer ===============================
-    if (lane == 0) {
-      constexpr uint32_t ID_P = idesc_bf16(64, 64, 0, 0);
-      constexpr uint32_t ID_UT = idesc_bf16(128, 64, 1, 0);            // A = V / K tile, MN-major
-      constexpr uint32_t ID_VN = idesc_bf16(128, 64, 0, 1) | (1u << 13);  // A negated; B = w^T tile
-      constexpr uint32_t ID_OT = idesc_bf16(128, 64, 0, 0);            // A from tensor memory
-      constexpr uint32_t ID_S = idesc_bf16(128, 128, 0, 1);
+  } else if (warp == 0 || warp == 1) {
+    // =============================== MMA issuers ===============================
+    // Two threads issue, each with its own waits and its own tcgen05.commit (a commit covers the
+    // MMAs of the committing thread only):
+    //   warp 0, the chain: Vn^T and the state update, nothing else: twelve MMAs per chunk;
+    //   warp 1, everything off the chain: P, O1^T, O2^T and u^T / w^T of the next chunk.  It is the
+    //           one that waits for the output group, so the chain never stands behind an epilogue.
+    // The tensor pipe runs products in issue order whoever issued them; the extra barriers
+    // (SB_FREE, the O_DONE wait of the value group) cover what one thread's program order would.
+    constexpr uint32_t ID_P = idesc_bf16(64, 64, 0, 0);
+    constexpr uint32_t ID_UT = idesc_bf16(128, 64, 1, 0);            // A = V / K tile, MN-major
+    constexpr uint32_t ID_VN = idesc_bf16(128, 64, 0, 1) | (1u << 13);  // A negated; B = w^T tile
+    constexpr uint32_t ID_OT = idesc_bf16(128, 64, 0, 0);            // A from tensor memory
+    constexpr uint32_t ID_S = idesc_bf16(128, 128, 0, 1);
+    constexpr uint32_t STAGE_LO = STAGE_BYTES >> 4;
+    if (warp == 0 && lane == 0) {
+      auto SPIN = [&](int idx, uint32_t parity) { return mbar_wait_spin(&bars[idx], parity, abort_flag); };
       // low descriptor words of every operand tile (see umma_lo); steps are 32-bit adds
-      const uint32_t wmn_lo = desc_lo_mnmajor(smem + OFF_W, 16384), p_lo = desc_lo_kmajor(smem + OFF_P);
-      const uint32_t ap_lo = desc_lo_kmajor(smem + OFF_AP), app_lo = desc_lo_kmajor(smem + OFF_APP);
-      const uint32_t q0_lo = desc_lo_kmajor(smem + OFF_STAGE);
-      const uint32_t k0_lo = desc_lo_kmajor(smem + OFF_STAGE + TILE_QK);
+      const uint32_t wmn_lo = desc_lo_mnmajor(smem + OFF_W, 16384);
       const uint32_t kmn0_lo = desc_lo_mnmajor(smem + OFF_STAGE + TILE_QK, 8192);
-      const uint32_t vmn0_lo = desc_lo_mnmajor(smem + OFF_STAGE + 2 * TILE_QK, 8192);
-      constexpr uint32_t STAGE_LO = STAGE_BYTES >> 4;
-      auto issue_u_w = [&](uint32_t so) {  // so = stage offset in descriptor units
-        umma_group<4, 128, 0, 2, 0, false>(tmem + TM_UV, vmn0_lo + so, ap_lo, ID_UT);
-        umma_group<4, 128, 0, 2, 0, false>(tmem + TM_PW, kmn0_lo + so, app_lo, ID_UT);
-        umma_commit(&bars[W_DONE]);
-      };
       auto store_vn = [&](int it) {  // after VN_READY: the v_new^T tile is complete
         tma_store_2d(&map_vn, 0, (int)(((sp.chunk_base + (it - lead)) * p.Hv + hv) * D), smem + OFF_VNT);
         tma_store_commit();
       };
       for (int it = 0; it < n_it && ok; ++it) {
-        const int s = it & 1, c = it - lead;  // c < 0: lead-in chunk, no output products
-        const uint32_t so = s ? STAGE_LO : 0u, so_next = s ? 0u : STAGE_LO;
-        const bool with_o = !NO_O && c >= 0;
-        if (it == 0) {
-          ok = WAIT(FULL0, 0) && WAIT(AP_READY, 0);
-          if (!ok) break;
-          tc_fence_after();
-          issue_u_w(0);
-        }
+        const int s = it & 1, c = it - lead;  // c < 0: lead-in chunk
+        const uint32_t so = s ? STAGE_LO : 0u;
         FQLA_TRACE(3, 0);
-        ok = WAIT(S_COPY, it & 1) && WAIT(W_READY, it & 1);
+        if (it < 126) FQLA_CHUNK_CLOCK(it);
+        ok = SPIN(S_COPY, it & 1) && SPIN(W_READY, it & 1);
         if (!ok) break;
         tc_fence_after();
         FQLA_TRACE(3, 1);
@@ -603,20 +652,6 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
         if constexpr (EXTRA) tma_store_wait_read();  // v_new^T of the chunk before has left its tile
         umma_commit(&bars[VN_DONE]);
         FQLA_TRACE(3, 2);
-        if (with_o) {
-          // P of this chunk goes here, into the time the value group needs for Vn: the output
-          // group turns it into Pg right away (its columns held w^T of this chunk until the value
-          // group made the operand tile of it: W_READY above)
-          umma_group<8, 2, 512, 2, 512, false>(tmem + TM_PW, q0_lo + so, k0_lo + so, ID_P);
-          umma_commit(&bars[P_DONE]);
-          if (c > 0) {
-            ok = WAIT(O_FREE, (c - 1) & 1);
-            if (!ok) break;
-            tc_fence_after();
-          }
-          // O1^T = S^T Q^T   (B = q tile, K-major)
-          umma_ts_group_kmajor_b<8>(tmem + TM_O1, tmem + TM_SB, q0_lo + so, ID_OT);
-        }
         if constexpr (EXTRA) {
           if (tile_h && c >= 0) {  // the state entering this chunk, as an operand tile
             ok = WAIT(ST_READY, c & 1);
@@ -628,7 +663,7 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
           }
         }
         FQLA_TRACE(3, 3);
-        ok = WAIT(VB_READY, it & 1) && WAIT(S_DEC, it & 1);
+        ok = SPIN(VB_READY, it & 1) && SPIN(S_DEC, it & 1);
         if (!ok) break;
         tc_fence_after();
         FQLA_TRACE(3, 4);
@@ -636,7 +671,7 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
         umma_ts_group<4, 8, 128, true>(tmem + TM_S, tmem + TM_VRB, kmn0_lo + so, ID_S);
         if constexpr (EXTRA) tma_store_wait_read();  // the S^T tile may be rewritten after this
         umma_commit(&bars[S_DONE]);
-        umma_commit(&bars[EMPTY0 + s]);  // last product that reads this stage
+        umma_commit(&bars[EMPTY0 + s]);  // this thread's last product that reads the stage
         FQLA_TRACE(3, 5);
         if constexpr (EXTRA) {
           if (tile_vn && c >= 0) {
@@ -645,29 +680,70 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
             store_vn(it);
           }
         }
-        if (with_o) {
-          ok = WAIT(P_READY, c & 1);
-          if (!ok) break;
-          tc_fence_after();
-          // O2^T = Vn^T Pg^T   (A = packed Vn^T; B = Pg, K-major)
-          umma_ts_group<4, 8, 2, false>(tmem + TM_O2, tmem + TM_VNB, p_lo, ID_OT);
-          umma_commit(&bars[O_DONE]);
-        }
-        FQLA_TRACE(3, 6);
-        if (it + 1 < n_it) {
-          // u^T and w^T of the next chunk: u^T overwrites Vn^T (read by the value group: VB_READY
-          // above), w^T overwrites P (read by the output group: P_READY above)
-          ok = WAIT(FULL0 + (s ^ 1), ((it + 1) >> 1) & 1) && WAIT(AP_READY, (it + 1) & 1);
-          if (!ok) break;
-          tc_fence_after();
-          FQLA_TRACE(3, 7);
-          issue_u_w(so_next);
-        }
         FQLA_TRACE(3, 8);
       }
       if constexpr (EXTRA) tma_store_wait_all();
+    } else if (warp == 1 && lane == 0) {
+      const uint32_t p_lo = desc_lo_kmajor(smem + OFF_P);
+      const uint32_t q0_lo = desc_lo_kmajor(smem + OFF_STAGE);
+      const uint32_t k0_lo = desc_lo_kmajor(smem + OFF_STAGE + TILE_QK);
+      const uint32_t ap_lo = desc_lo_kmajor(smem + OFF_AP), app_lo = desc_lo_kmajor(smem + OFF_APP);
+      const uint32_t kmn0_lo = desc_lo_mnmajor(smem + OFF_STAGE + TILE_QK, 8192);
+      const uint32_t vmn0_lo = desc_lo_mnmajor(smem + OFF_STAGE + 2 * TILE_QK, 8192);
+      auto issue_u_w = [&](uint32_t so) {  // so = stage offset in descriptor units
+        umma_group<4, 128, 0, 2, 0, false>(tmem + TM_UV, vmn0_lo + so, ap_lo, ID_UT);
+        umma_group<4, 128, 0, 2, 0, false>(tmem + TM_PW, kmn0_lo + so, app_lo, ID_UT);
+        umma_commit(&bars[W_DONE]);
+      };
+      if (n_it > 0) {
+        ok = WAIT(FULL0, 0) && WAIT(AP_READY, 0);
+        if (ok) {
+          tc_fence_after();
+          issue_u_w(0);
+        }
+      }
+      for (int it = 0; it < n_it && ok; ++it) {
+        const int s = it & 1, c = it - lead;
+        const uint32_t so = s ? STAGE_LO : 0u, so_next = s ? 0u : STAGE_LO;
+        const bool with_o = !NO_O && c >= 0;
+        if (with_o) {
+          // P = Q K^T goes first: the output group turns it into Pg while everything else runs.
+          // Its columns held w^T of this chunk until the value group made the operand tile of it.
+          ok = WAIT(W_READY, it & 1);
+          if (!ok) break;
+          tc_fence_after();
+          umma_group<8, 2, 512, 2, 512, false>(tmem + TM_PW, q0_lo + so, k0_lo + so, ID_P);
+          umma_commit(&bars[P_DONE]);
+          // O1^T = S^T Q^T   (A = packed S^T; B = q tile, K-major)
+          ok = WAIT(S_COPY, it & 1) && (c == 0 || WAIT(O_FREE, (c - 1) & 1));
+          if (!ok) break;
+          tc_fence_after();
+          umma_ts_group_kmajor_b<8>(tmem + TM_O1, tmem + TM_SB, q0_lo + so, ID_OT);
+          umma_commit(&bars[SB_FREE]);
+        }
+        // this thread's products that read the stage (u^T, w^T of this chunk, issued a chunk ago,
+        // and the two above) are all issued
+        umma_commit(&bars[EMPTY0 + s]);
+        if (with_o) {
+          // O2^T = Vn^T Pg^T   (A = packed Vn^T; B = Pg, K-major)
+          ok = WAIT(P_READY, c & 1) && WAIT(VB_READY, it & 1);
+          if (!ok) break;
+          tc_fence_after();
+          umma_ts_group<4, 8, 2, false>(tmem + TM_O2, tmem + TM_VNB, p_lo, ID_OT);
+          umma_commit(&bars[O_DONE]);
+        }
+        if (it + 1 < n_it) {
+          // u^T and w^T of the next chunk: u^T overwrites Vn^T (read by the value group:
+          // VB_READY), w^T overwrites P (read by the output group: P_READY above)
+          ok = WAIT(FULL0 + (s ^ 1), ((it + 1) >> 1) & 1) && WAIT(AP_READY, (it + 1) & 1) &&
+               WAIT(VB_READY, it & 1);
+          if (!ok) break;
+          tc_fence_after();
+          issue_u_w(so_next);
+        }
+      }
     }
-  } else if (warp == 1) {
+  } else if (warp == 2) {
     // =============================== producer ===============================
     float g_r[2] = {0.f, 0.f}, b_r[2] = {0.f, 0.f}, gl_r = 0.f;
     // (lead-in chunks, c < 0, are whole chunks of the rows before the sequence)
@@ -772,42 +848,6 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
         if (ok && it + 2 < n_it) fetch(it + 2);
       }
     }
-  } else {
-    // =============================== prep (warps 2, 3) ===============================
-    // A' = A diag(beta), A'' = A diag(beta gamma).  Thread t owns the 8 columns 8 (t%8) .. of the
-    // rows t/8 + 8 i: its 16 scale factors stay in registers, and the eight threads of a row touch
-    // the eight 16-byte pieces of that row (one 128-byte line per access, conflict-free).
-    const int t = tid - 64, c8 = t & 7, r0 = t >> 3;
-    const int pc = c8 ^ r0;  // physical piece: rows r0 + 8 i all have (row & 7) == r0
-    for (int it = 0; it < n_it && ok; ++it) {
-      const int s = it & 1;
-      ok = WAIT(FULLA0 + s, (it >> 1) & 1);
-      if (ok && it > 0) ok = WAIT(W_DONE, (it - 1) & 1);  // u, w of the chunk before are done
-      if (!ok) break;
-      const float* vs = vec + (it & 3) * VEC_SLOT_FLOATS;
-      const float4 b0 = *reinterpret_cast<const float4*>(vs + V_BETA * CHUNK + 8 * c8);
-      const float4 b1 = *reinterpret_cast<const float4*>(vs + V_BETA * CHUNK + 8 * c8 + 4);
-      const float4 g0 = *reinterpret_cast<const float4*>(vs + V_BG * CHUNK + 8 * c8);
-      const float4 g1 = *reinterpret_cast<const float4*>(vs + V_BG * CHUNK + 8 * c8 + 4);
-      const unsigned char* src = smem + OFF_STAGE + s * STAGE_BYTES + 2 * TILE_QK + TILE_V;
-#pragma unroll 4
-      for (int i = 0; i < 8; ++i) {
-        const int off = (r0 + 8 * i) * 128 + pc * 16;
-        const uint4 a = *reinterpret_cast<const uint4*>(src + off);
-        *reinterpret_cast<uint4*>(smem + OFF_AP + off) =
-            make_uint4(scale_bf16x2(a.x, b0.x, b0.y), scale_bf16x2(a.y, b0.z, b0.w),
-                       scale_bf16x2(a.z, b1.x, b1.y), scale_bf16x2(a.w, b1.z, b1.w));
-        *reinterpret_cast<uint4*>(smem + OFF_APP + off) =
-            make_uint4(scale_bf16x2(a.x, g0.x, g0.y), scale_bf16x2(a.y, g0.z, g0.w),
-                       scale_bf16x2(a.z, g1.x, g1.y), scale_bf16x2(a.w, g1.z, g1.w));
-      }
-      fence_proxy_async();
-      __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&bars[AP_READY]);
-        mbar_arrive(&bars[EMPTYA0 + s]);  // the A tile of this stage is no longer read here
-      }
-    }
   }
 
   // ---- teardown: everybody meets, then the allocating warp frees tensor memory
@@ -816,6 +856,15 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, 512);
   if (tid == 0 && *abort_flag) atomicCAS(&g_device_status, 0, 1);
+  if (tid == 0) FQLA_CHUNK_CLOCK(127);
+#ifdef FQLA_DIAGNOSTICS
+  if (tid == 0 && blockIdx.x < 1024) {
+    unsigned smid;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+    g_cta_cycles[2 * blockIdx.x] = smid;
+    g_cta_cycles[2 * blockIdx.x + 1] = clock64() - g_fwd_chunk_clock_entry;
+  }
+#endif
 }
 
 // ---- host side --------------------------------------------------------------------------------
@@ -873,6 +922,13 @@ int launch_fwd_tc(const void* q, const void* k, const void* v, const void* A, co
 #ifdef FQLA_DIAGNOSTICS
 extern "C" int fqla_debug_fwd_trace(long long* out960) {
   return (int)cudaMemcpyFromSymbol(out960, fqla::g_fwd_trace, sizeof(long long) * 960);
+}
+extern "C" int fqla_debug_cta_cycles(long long* out2048, int trace_cta) {
+  cudaMemcpyToSymbol(fqla::g_trace_cta, &trace_cta, sizeof(int));
+  return (int)cudaMemcpyFromSymbol(out2048, fqla::g_cta_cycles, sizeof(long long) * 2048);
+}
+extern "C" int fqla_debug_fwd_chunk_clock(long long* out256) {
+  return (int)cudaMemcpyFromSymbol(out256, fqla::g_fwd_chunk_clock, sizeof(long long) * 256);
 }
 #endif
 

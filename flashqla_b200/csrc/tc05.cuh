@@ -101,6 +101,17 @@ __device__ __forceinline__ void stmatrix_x4_trans(uint32_t saddr, uint32_t r0, u
                : "memory");
 }
 
+// The same bounded wait for a thread that is alone in its warp and on the critical path: it polls
+// (about 13 cycles per test) for a while before it lets the hardware suspend it, because waking
+// from the suspended form costs several hundred cycles.
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity,
+                                               volatile int* abort_flag) {
+#pragma unroll 1
+  for (int i = 0; i < 2048; ++i)
+    if (mbar_test_wait(bar, parity)) return true;
+  return mbar_wait(bar, parity, abort_flag);
+}
+
 // ---- proxy / tcgen05 fences ------------------------------------------------------------------
 __device__ __forceinline__ void fence_proxy_async() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
