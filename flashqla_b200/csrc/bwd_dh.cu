@@ -32,6 +32,7 @@ struct BwdDhParams {
   bf16* du;          // [rows, Hv, D] or null
   float* dh0;        // [N, Hv, D, D] or null
   const int* warm;   // [N, Hv] or null: walk only the first warm[n,hv] chunks (dh0-only pass)
+  const int* order;  // [N] or null: block index -> sequence (longest first shortens the tail)
   int N, Hq, Hv;
   float scale;
   SeqLayout lay;
@@ -81,7 +82,8 @@ __global__ void __launch_bounds__(256, 1) bwd_dh_kernel(const BwdDhParams p) {
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int wm = warp & 3, wn = warp >> 2;
-  const int n = blockIdx.x / p.Hv, hv = blockIdx.x % p.Hv;
+  const int hv = blockIdx.x % p.Hv;
+  const int n = p.order ? p.order[blockIdx.x / p.Hv] : (int)(blockIdx.x / p.Hv);
   const int hq = hv / (p.Hv / p.Hq);
   const int v0 = blockIdx.y * BV;
   const SeqSpan sp = p.lay.span(n);
@@ -293,8 +295,8 @@ static int launch_bwd_dh(const BwdDhParams& p, cudaStream_t st) {
 // tcgen05 version for K = V = 128, full walks only (bwd_dh_tc.cu)
 int launch_bwd_dh_tc(const void* q, const void* k, const void* A, const float* g, const void* beta,
                      int beta_is_f32, const void* dO, const float* dht, void* dh, void* du,
-                     float* dh0, int tiled, int N, int Hq, int Hv, long long T_rows, float scale,
-                     SeqLayout lay, cudaStream_t st);
+                     float* dh0, int tiled, const int* order, int N, int Hq, int Hv,
+                     long long T_rows, float scale, SeqLayout lay, cudaStream_t st);
 
 }  // namespace fqla
 
@@ -302,8 +304,9 @@ using namespace fqla;
 
 extern "C" int fqla_bwd_dh(const void* q, const void* k, const void* A, const float* g_cum,
                            const void* beta, int beta_is_f32, const void* dO, const float* dht,
-                           void* dh, void* du, float* dh0, const int* warm_chunks, int B, int T,
-                           int Hq, int Hv, int D, float scale, const void* cu_seqlens,
+                           void* dh, void* du, float* dh0, const int* warm_chunks,
+                           const int* seq_order, int B, int T, int Hq, int Hv, int D, float scale,
+                           const void* cu_seqlens,
                            const void* chunk_offsets, int idx_is64, int N, int operand_tiles,
                            void* stream) {
   if (!q || !k || !A || !g_cum || !beta || !dO || Hq <= 0 || Hv % Hq)
@@ -313,7 +316,7 @@ extern "C" int fqla_bwd_dh(const void* q, const void* k, const void* A, const fl
   BwdDhParams p;
   p.q = (const bf16*)q; p.k = (const bf16*)k; p.A = (const bf16*)A; p.g = g_cum;
   p.beta = beta; p.beta_is_f32 = beta_is_f32; p.dO = (const bf16*)dO; p.dht = dht;
-  p.dh = (bf16*)dh; p.du = (bf16*)du; p.dh0 = dh0; p.warm = warm_chunks;
+  p.dh = (bf16*)dh; p.du = (bf16*)du; p.dh0 = dh0; p.warm = warm_chunks; p.order = seq_order;
   p.N = cu_seqlens ? N : B; p.Hq = Hq; p.Hv = Hv; p.scale = scale;
   p.lay = SeqLayout{{cu_seqlens, idx_is64}, {chunk_offsets, idx_is64}, T};
   if (p.N <= 0) return FQLA_OK;
@@ -321,7 +324,8 @@ extern "C" int fqla_bwd_dh(const void* q, const void* k, const void* A, const fl
   static const bool force_legacy = getenv("FQLA_FORCE_MMA_SYNC") != nullptr;
   if (D == 128 && !warm_chunks && !force_legacy)
     return launch_bwd_dh_tc(q, k, A, g_cum, beta, beta_is_f32, dO, dht, dh, du, dh0,
-                            operand_tiles, p.N, Hq, Hv, (long long)B * T, scale, p.lay, st);
+                            operand_tiles, seq_order, p.N, Hq, Hv, (long long)B * T, scale, p.lay,
+                            st);
   if (operand_tiles) return FQLA_ERR_UNSUPPORTED_DIM;  // only the tcgen05 kernel writes tiles
   if (D == 128) return launch_bwd_dh<128>(p, st);
   if (D == 64) return launch_bwd_dh<64>(p, st);

@@ -41,6 +41,7 @@ struct BwdDhTcParams {
   float scale;
   SeqLayout lay;
   int tiled;  // dh and du are written as operand tiles (dh^T, du^T per chunk) by TMA
+  const int* order;  // [N] or null: block index -> sequence (longest first shortens the tail)
 };
 
 namespace bdtc {
@@ -88,7 +89,8 @@ bwd_dh_tc_kernel(const BwdDhTcParams p, const __grid_constant__ CUtensorMap map_
   float* vec = reinterpret_cast<float*>(smem + OFF_VEC);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int n = blockIdx.x / p.Hv, hv = blockIdx.x % p.Hv;
+  const int hv = blockIdx.x % p.Hv;
+  const int n = p.order ? p.order[blockIdx.x / p.Hv] : (int)(blockIdx.x / p.Hv);
   const int hq = hv / (p.Hv / p.Hq);
   const SeqSpan sp = p.lay.span(n);
   const int n_it = sp.n_chunks;  // iteration `it` handles chunk n_it - 1 - it
@@ -588,8 +590,8 @@ int make_tile_map(CUtensorMap* m, const void* ptr, long long rows, long long col
 
 int launch_bwd_dh_tc(const void* q, const void* k, const void* A, const float* g, const void* beta,
                      int beta_is_f32, const void* dO, const float* dht, void* dh, void* du,
-                     float* dh0, int tiled, int N, int Hq, int Hv, long long T_rows, float scale,
-                     SeqLayout lay, cudaStream_t st) {
+                     float* dh0, int tiled, const int* order, int N, int Hq, int Hv,
+                     long long T_rows, float scale, SeqLayout lay, cudaStream_t st) {
   using namespace bdtc;
   CUtensorMap mq, mk, mdo, ma, mdh, mdu;
   int rc;
@@ -607,6 +609,7 @@ int launch_bwd_dh_tc(const void* q, const void* k, const void* A, const float* g
   }
   BwdDhTcParams p;
   p.tiled = tiled;
+  p.order = order;
   p.g = g; p.beta = beta; p.beta_is_f32 = beta_is_f32; p.dht = dht;
   p.dh = (bf16*)dh; p.du = (bf16*)du; p.dh0 = dh0;
   p.N = N; p.Hq = Hq; p.Hv = Hv; p.scale = scale; p.lay = lay;

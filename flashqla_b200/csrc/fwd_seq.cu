@@ -26,8 +26,8 @@ namespace fqla {
 // tcgen05 implementation of the full forward (fwd_tc.cu)
 int launch_fwd_tc(const void* q, const void* k, const void* v, const void* A, const float* g,
                   const void* beta, int beta_is_f32, const float* h0, float* ht, void* o, void* h,
-                  void* vnew, int tiled, const int* lead, int N, int Hq, int Hv, long long T_rows,
-                  float scale, SeqLayout lay, cudaStream_t st);
+                  void* vnew, int tiled, const int* lead, const int* order, int N, int Hq, int Hv,
+                  long long T_rows, float scale, SeqLayout lay, cudaStream_t st);
 
 struct FwdSeqParams {
   const bf16* q;      // may be null (state-only pass)
@@ -45,6 +45,7 @@ struct FwdSeqParams {
   float* M;           // [N, Hv, D, D] or null: transition matrix (state_end = local + M state_0)
   const int* warm;    // [N, Hv] or null: process only the last warm[n,hv] chunks (state-only)
   const int* m_mask;  // [N, Hv] or null: compute M only where non-zero
+  const int* order;   // [N] or null: block index -> sequence (longest first shortens the tail)
   int N, Hq, Hv;
   long long T_rows;   // total rows of the token axis (for zero-filling the tail of o)
   float scale;
@@ -95,7 +96,8 @@ __global__ void __launch_bounds__(256, 1) fwd_seq_kernel(const FwdSeqParams p) {
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int wm = warp & 3, wn = warp >> 2;
-  const int n = blockIdx.x / p.Hv, hv = blockIdx.x % p.Hv;
+  const int hv = blockIdx.x % p.Hv;
+  const int n = p.order ? p.order[blockIdx.x / p.Hv] : (int)(blockIdx.x / p.Hv);
   const int hq = hv / (p.Hv / p.Hq);
   constexpr int V_SLICES = D / BV;
   const bool m_slice = (int)blockIdx.y >= V_SLICES;  // transition-matrix slice
@@ -349,7 +351,8 @@ extern "C" int fqla_fwd_seq(const void* q, const void* k, const void* v, const v
                             const float* g_cum, const void* beta, int beta_is_f32,
                             const float* h0, float* ht, void* o, void* h, void* vnew, float* M,
                             const int* warm_chunks, const int* m_mask, const int* lead_chunks,
-                            int B, int T, int Hq, int Hv, int D, float scale, const void* cu_seqlens,
+                            const int* seq_order, int B, int T, int Hq, int Hv, int D, float scale,
+                            const void* cu_seqlens,
                             const void* chunk_offsets, int idx_is64, int N, int operand_tiles,
                             void* stream) {
   if (!k || !v || !A || !g_cum || !beta || Hq <= 0 || Hv % Hq) return FQLA_ERR_INVALID_ARG;
@@ -363,6 +366,7 @@ extern "C" int fqla_fwd_seq(const void* q, const void* k, const void* v, const v
   p.h0 = h0; p.ht = ht; p.o = (bf16*)o; p.h = (bf16*)h; p.vnew = (bf16*)vnew; p.M = M;
   p.warm = warm_chunks;
   p.m_mask = m_mask;
+  p.order = seq_order;
   p.N = cu_seqlens ? N : B; p.Hq = Hq; p.Hv = Hv;
   p.T_rows = (long long)B * T;
   p.scale = scale;
@@ -376,7 +380,7 @@ extern "C" int fqla_fwd_seq(const void* q, const void* k, const void* v, const v
   const bool full = q && o, recompute = !q && !o && (h || vnew);
   if (D == 128 && (full || recompute) && !M && !warm_chunks && !m_mask && !force_legacy)
     return launch_fwd_tc(q, k, v, A, g_cum, beta, beta_is_f32, h0, ht, o, h, vnew, operand_tiles,
-                         lead_chunks, p.N, Hq, Hv, p.T_rows, scale, p.lay, st);
+                         lead_chunks, seq_order, p.N, Hq, Hv, p.T_rows, scale, p.lay, st);
   if (operand_tiles || lead_chunks) return FQLA_ERR_UNSUPPORTED_DIM;  // tcgen05 kernel only
   if (D == 128) return launch_fwd_seq<128>(p, st);
   if (D == 64) return launch_fwd_seq<64>(p, st);

@@ -95,6 +95,9 @@ struct FwdTcParams {
   // the rows just before a segment are the tail of the segment before it, whose influence dies
   // out within `lead` chunks.  h0 is ignored for such a CTA.
   const int* lead;
+  // [N] or null: the CTAs of block index i / Hv walk sequence order[i].  Blocks start in index
+  // order, so a table that lists the longest sequences first shortens the tail of a ragged batch.
+  const int* order;
 };
 
 namespace fwdtc {
@@ -168,7 +171,8 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
   float* vec = reinterpret_cast<float*>(smem + OFF_VEC);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int n = blockIdx.x / p.Hv, hv = blockIdx.x % p.Hv;
+  const int hv = blockIdx.x % p.Hv;
+  const int n = p.order ? p.order[blockIdx.x / p.Hv] : (int)(blockIdx.x / p.Hv);
   const int hq = hv / (p.Hv / p.Hq);
   const SeqSpan sp = p.lay.span(n);
   // iteration j handles chunk c = j - lead of the sequence; c < 0 are the lead-in chunks
@@ -878,8 +882,8 @@ static int make_map(CUtensorMap* m, const void* ptr, long long rows, long long c
 
 int launch_fwd_tc(const void* q, const void* k, const void* v, const void* A, const float* g,
                   const void* beta, int beta_is_f32, const float* h0, float* ht, void* o, void* h,
-                  void* vnew, int tiled, const int* lead, int N, int Hq, int Hv, long long T_rows,
-                  float scale, SeqLayout lay, cudaStream_t st) {
+                  void* vnew, int tiled, const int* lead, const int* order, int N, int Hq, int Hv,
+                  long long T_rows, float scale, SeqLayout lay, cudaStream_t st) {
   using namespace fwdtc;
   CUtensorMap mq, mk, mv, ma, mh, mvn, mo;
   int rc;
@@ -902,6 +906,7 @@ int launch_fwd_tc(const void* q, const void* k, const void* v, const void* A, co
   FwdTcParams p;
   p.tiled = tiled;
   p.lead = lead;
+  p.order = order;
   p.g = g; p.beta = beta; p.beta_is_f32 = beta_is_f32; p.h0 = h0; p.ht = ht;
   p.o = (bf16*)o; p.h = (bf16*)h; p.vnew = (bf16*)vnew;
   p.N = N; p.Hq = Hq; p.Hv = Hv; p.T_rows = T_rows; p.scale = scale; p.lay = lay;

@@ -105,7 +105,7 @@ __device__ __forceinline__ void store_frag(float* C, int ldc, const float (&c)[N
 //   3. X = (I+L)^-1 by blocked forward substitution in fp32, 4. bf16 rows out.
 // ------------------------------------------------------------------------------------------
 template <int D>
-__global__ void __launch_bounds__(128, 5) kkt_solve_kernel(
+__global__ void __launch_bounds__(128, 6) kkt_solve_kernel(
     const bf16* __restrict__ k, const void* __restrict__ beta, int beta_is_f32,
     const float* __restrict__ g, float* __restrict__ g_cum_out, bf16* __restrict__ A, int Hq,
     int Hv, SeqLayout lay, IndexTable chunk_indices) {
@@ -119,8 +119,10 @@ __global__ void __launch_bounds__(128, 5) kkt_solve_kernel(
   float* sL = reinterpret_cast<float*>(smem_raw + REGION0);
   float* sG = sL + CHUNK * LDL;
   float* sB = sG + CHUNK;
-  constexpr int LDY = 40;         // partial products [32][LDY]
-  float* sY = sB + CHUNK;
+  // partial products [32][32]: they live in the rows 0-31, columns 32-63 of L, a part of its
+  // upper triangle that is neither written nor read (six CTAs per SM fit with that)
+  constexpr int LDY = LDL;
+  float* sY = sL + 32;
 
   int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int hq = blockIdx.y, G = Hv / Hq;
@@ -320,7 +322,7 @@ static int launch_kkt(const void* k, const void* beta, int beta_is_f32, const fl
                       float* g_cum_out, void* A, int Hq, int Hv, SeqLayout lay, IndexTable ci,
                       long long n, cudaStream_t st) {
   constexpr int k_tile = CHUNK * (D + 8) * 2, x_tile = CHUNK * (CHUNK + 4) * 4;
-  constexpr int smem = (k_tile > x_tile ? k_tile : x_tile) + x_tile + 2 * CHUNK * 4 + 32 * 40 * 4;
+  constexpr int smem = (k_tile > x_tile ? k_tile : x_tile) + x_tile + 2 * CHUNK * 4;
   int rc = configure_smem((const void*)kkt_solve_kernel<D>, smem);
   if (rc != 0) return rc;
   kkt_solve_kernel<D><<<dim3((unsigned)n, Hq), 128, smem, st>>>(

@@ -71,6 +71,8 @@ class SeqTables:
             self.chunk_indices = _kernel_chunk_indices(cu_seqlens)
             self.chunk_offsets, self.num_chunks = prepare_chunk_offsets(cu_seqlens, CHUNK_SIZE)
             self.is64 = int(cu_seqlens.dtype == torch.int64)
+        # block index -> sequence, longest first (None: identity)
+        self.order = None if cu_seqlens is None or self.N < 2 else _longest_first(cu_seqlens)
 
     @property
     def total(self) -> int:
@@ -98,6 +100,14 @@ def _kernel_chunk_indices(cu_seqlens: torch.Tensor) -> torch.Tensor:
     fixed = table.clone()
     fixed[:, 0] = seq.to(table.dtype)
     return fixed
+
+
+@tensor_cache
+def _longest_first(cu_seqlens: torch.Tensor) -> torch.Tensor:
+    """int32 ``[N]``: the sequences sorted by length, longest first.  The sequential kernels start
+    their CTAs in block-index order; handing the long sequences out first shortens the tail of a
+    ragged batch (computed on the device, cached per ``cu_seqlens`` tensor)."""
+    return torch.argsort(torch.diff(cu_seqlens), descending=True, stable=True).to(torch.int32)
 
 
 @tensor_cache
@@ -206,8 +216,8 @@ def fwd_seq(q, k, v, a, g_cum, b, scale, initial_state=None, *, output_final_sta
         _ptr(q) if output_o else None, _ptr(k), _ptr(v), _ptr(a), _ptr(g_cum), _ptr(b),
         _beta_flag(b), _ptr(initial_state), _ptr(out.get("ht")), _ptr(out.get("o")),
         _ptr(out.get("h")), _ptr(out.get("vnew")), _ptr(out.get("M")), _ptr(warm_chunks),
-        _ptr(m_mask), _ptr(lead_chunks), tb.B, tb.T, Hq, Hv, D, float(scale), cu, offs, is64, N,
-        int(operand_tiles), _stream(k))
+        _ptr(m_mask), _ptr(lead_chunks), _ptr(tb.order), tb.B, tb.T, Hq, Hv, D, float(scale), cu,
+        offs, is64, N, int(operand_tiles), _stream(k))
     _lib.check(st, "fwd_seq")
     return out
 
@@ -240,7 +250,8 @@ def bwd_dh(q, k, a, g_cum, b, do, scale, dht=None, *, output_dh=True, output_du=
     st = _lib.load().fqla_bwd_dh(
         _ptr(q), _ptr(k), _ptr(a), _ptr(g_cum), _ptr(b), _beta_flag(b), _ptr(do), _ptr(dht),
         _ptr(out.get("dh")), _ptr(out.get("du")), _ptr(out.get("dh0")), _ptr(warm_chunks),
-        tb.B, tb.T, Hq, Hv, D, float(scale), cu, offs, is64, N, int(operand_tiles), _stream(k))
+        _ptr(tb.order), tb.B, tb.T, Hq, Hv, D, float(scale), cu, offs, is64, N, int(operand_tiles),
+        _stream(k))
     _lib.check(st, "bwd_dh")
     return out
 

@@ -75,25 +75,30 @@ int fqla_kkt_solve(const void* k, const void* beta, int beta_is_f32, const float
  * many chunks BEFORE the segment (those rows are the tail of the segment before it) from a zero
  * state, state-only, and only then enters the segment: the start state needs no separate pass.
  * h0 is ignored for such a (segment, head); outputs cover the segment's own rows only.
+ * seq_order [N] (int32, optional; a permutation of 0..N-1): the CTAs of block index i / Hv walk
+ * sequence seq_order[i].  Blocks start in index order, so listing the longest sequences first
+ * shortens the tail of a ragged batch; the results do not depend on it.
  * Replaces fused_gdr_fwd (blackwell/fused_fwd.py:775-915) and fused_gdr_h
  * (blackwell/prepare_h.py:669-784). */
 int fqla_fwd_seq(const void* q, const void* k, const void* v, const void* A, const float* g_cum,
                  const void* beta, int beta_is_f32, const float* h0, float* ht, void* o, void* h,
                  void* vnew, float* M, const int* warm_chunks, const int* m_mask,
-                 const int* lead_chunks, int B, int T, int Hq, int Hv, int D, float scale,
-                 const void* cu_seqlens, const void* chunk_offsets, int idx_is64, int N,
-                 int operand_tiles, void* stream);
+                 const int* lead_chunks, const int* seq_order, int B, int T, int Hq, int Hv, int D,
+                 float scale, const void* cu_seqlens, const void* chunk_offsets, int idx_is64,
+                 int N, int operand_tiles, void* stream);
 
 /* Sequential reverse recurrence of the state gradient.  Optional outputs: per-chunk dh, du (the
  * gradient of vnew), dh0.  warm_chunks (optional, dh0-only calls): walk only the first
  * warm_chunks[n,hv] chunks from a zero gradient.  operand_tiles != 0 (K = V = 128, no
  * warm_chunks): dh is written as [chunks, Hv, V, K] and du as [chunks, Hv, V, 64], the operand
- * layouts of fqla_fwd_seq's h and vnew; FQLA_ERR_UNSUPPORTED_DIM otherwise.
+ * layouts of fqla_fwd_seq's h and vnew; FQLA_ERR_UNSUPPORTED_DIM otherwise.  seq_order: as for
+ * fqla_fwd_seq.
  * Replaces fused_gdr_dh_ws (blackwell/cp_bwd.py:592-701) and the dS chain of fused_gdr_bwd
  * (blackwell/fused_bwd.py:336-474). */
 int fqla_bwd_dh(const void* q, const void* k, const void* A, const float* g_cum, const void* beta,
                 int beta_is_f32, const void* dO, const float* dht, void* dh, void* du, float* dh0,
-                const int* warm_chunks, int B, int T, int Hq, int Hv, int D, float scale,
+                const int* warm_chunks, const int* seq_order, int B, int T, int Hq, int Hv, int D,
+                float scale,
                 const void* cu_seqlens, const void* chunk_offsets, int idx_is64, int N,
                 int operand_tiles, void* stream);
 

@@ -330,3 +330,27 @@ def test_lead_in_forward_agrees_with_explicit_start_states():
         cp.LEAD_IN = True
     assert orc.rel_err(o_lead.float(), o_sep.float()) < 2e-3
     assert orc.rel_err(ht_lead, ht_sep) < 2e-3
+
+
+def test_longest_first_block_order_does_not_change_results():
+    """Packed batches hand their sequences to the sequential kernels longest first (a block-index
+    -> sequence table); the outputs must be the same bits as in index order."""
+    from flashqla_b200 import ops
+
+    d = _inputs(1500, 2, 4, seed=73, cu=[0, 70, 700, 701, 1100, 1500])
+    tables, g_cum, A = _prep(d)
+    assert tables.order is not None and sorted(tables.order.tolist()) == [0, 1, 2, 3, 4]
+    assert tables.order.tolist()[0] == 1  # the 630-token sequence goes first
+    scale = 128 ** -0.5
+
+    def run(tb):
+        fw = ops.fwd_seq(d["q"], d["k"], d["v"], A, g_cum, d["beta"], scale, d["h0"],
+                         output_final_state=True, tables=tb)
+        bw = ops.bwd_dh(d["q"], d["k"], A, g_cum, d["beta"], d["do"], scale, d["dht"], tables=tb)
+        return fw["o"], fw["ht"], bw["dh"], bw["du"], bw["dh0"]
+
+    with_order = run(tables)
+    plain = ops.SeqTables(1, 1500, d["cu_seqlens"])
+    plain.order = None
+    for a, b, name in zip(with_order, run(plain), ("o", "ht", "dh", "du", "dh0")):
+        assert torch.equal(a, b), name
