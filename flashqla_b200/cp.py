@@ -31,9 +31,9 @@ from .utils import tensor_cache
 
 THRESHOLD = -10.0
 MIN_SEGMENT_CHUNKS = 8
-FILL_FRACTION = 0.75  # split only when the raw streams fill less than this share of the SMs
 VALUE_SLICES = 1  # CTAs per (segment, head) of the tcgen05 forward kernel
 SEGMENT_OVERHEAD_CHUNKS = 2  # cost of a hand-off, in chunk steps of the main kernel
+CTA_START_CHUNKS = 2  # cost of starting a CTA (tensor-memory allocation, first loads), same unit
 # True: the tcgen05 recurrence kernel starts a segment a few chunks early from a zero state
 # (``forward_start``); False: every segment's start state comes from the separate state-only pass
 # and the merge chain (``forward_segment_states``), as the mma.sync kernels always do.
@@ -55,48 +55,79 @@ class SegmentPlan:
     n_seg: int
 
 
+def _makespan(costs: list[int], copies: int, machines: int) -> int:
+    """Length of the schedule the hardware produces for CTAs of the given costs (each present
+    ``copies`` times, one per head) handed out longest first to ``machines`` SMs, one CTA per SM:
+    every CTA goes to the SM that frees up first."""
+    import heapq
+
+    items = sorted(costs, reverse=True)
+    n = len(items) * copies
+    if n <= machines:
+        return items[0] if items else 0
+    loads = [0] * machines
+    heapq.heapify(loads)
+    for c in items:
+        for _ in range(copies):
+            heapq.heappush(loads, heapq.heappop(loads) + c)
+    return max(loads)
+
+
 def split_sequences(bounds: list[int], num_heads: int, n_sm: int,
-                    min_chunks: int = MIN_SEGMENT_CHUNKS, fill: float = FILL_FRACTION,
-                    slices: int = VALUE_SLICES):
+                    min_chunks: int = MIN_SEGMENT_CHUNKS, slices: int = VALUE_SLICES):
     """Host-side segment planner.  ``bounds`` are the raw cumulative sequence lengths.
 
-    The sequential kernels keep one CTA per SM and walk their chunks in order, so a launch
-    takes about ``waves * longest_segment`` chunk steps, ``waves = ceil(CTAs / SMs)``.  The
-    planner tries every maximum segment length ``ceil(longest / p)`` and keeps the cheapest,
-    charging ``SEGMENT_OVERHEAD_CHUNKS`` per wave for the hand-off (warm-up pass and merge).
+    The sequential kernels keep one CTA per SM and walk their chunks in order; the CTAs of a
+    launch are handed out longest first, each to the SM that frees up first.  The planner
+    evaluates that schedule (``_makespan``) for the unsplit batch and for every maximum segment
+    length ``ceil(longest / p)`` (sequences longer than the limit are cut into equal, chunk
+    aligned parts), charging ``CTA_START_CHUNKS`` per CTA and ``SEGMENT_OVERHEAD_CHUNKS`` more
+    per segment that needs a start state, and keeps the cheapest.  It therefore splits a single
+    long sequence to fill the GPU, splits only the few long documents of a ragged batch that
+    would otherwise be the tail of the launch, and leaves a batch alone that already keeps every
+    SM busy.
 
-    Returns ``None`` when splitting does not pay (the raw sequences already fill the GPU, or no
-    split beats the unsplit schedule), else ``(seg_bounds, seg_begin)``: the cumulative lengths
-    of the segments and, per raw sequence, the index of its first segment.
+    Returns ``None`` when no split beats the unsplit schedule by at least 3 %, else
+    ``(seg_bounds, seg_begin)``: the cumulative lengths of the segments and, per raw sequence, the
+    index of its first segment.
     """
     lens = [e - s for s, e in zip(bounds[:-1], bounds[1:])]
     chunks = [(n + CHUNK_SIZE - 1) // CHUNK_SIZE for n in lens]
     longest = max(chunks) if chunks else 0
-    if longest == 0:
+    if longest < 2 * min_chunks:
         return None
-    ctas_per_seg = num_heads * slices
-    if len(lens) * ctas_per_seg >= fill * n_sm:
-        return None
+    copies = num_heads * slices
 
     def layout(limit):
         parts = [max(1, math.ceil(c / limit)) for c in chunks]
         per = [math.ceil(c / p) if c else 0 for c, p in zip(chunks, parts)]
-        waves = math.ceil(sum(parts) * ctas_per_seg / n_sm)
-        return parts, per, waves * (max(per) + SEGMENT_OVERHEAD_CHUNKS)
+        costs = []
+        for c, p, pc in zip(chunks, parts, per):
+            for i in range(p):
+                seg = min(pc, c - i * pc)
+                if seg > 0:
+                    costs.append(seg + CTA_START_CHUNKS + (SEGMENT_OVERHEAD_CHUNKS if i else 0))
+        return parts, per, _makespan(costs, copies, n_sm)
 
-    _, _, best_cost = layout(longest)
-    best_cost -= SEGMENT_OVERHEAD_CHUNKS  # the unsplit schedule has no hand-off
-    best = None
+    _, _, unsplit = layout(longest)
+    tried, cands = set(), []
     for p in range(2, longest // min_chunks + 1):
         limit = math.ceil(longest / p)
         if limit < min_chunks:
             break
+        if limit in tried:
+            continue
+        tried.add(limit)
         parts, per, cost = layout(limit)
-        if cost < best_cost:
-            best_cost, best = cost, (parts, per)
-    if best is None:
+        cands.append((cost, parts, per))
+    if not cands:
         return None
-    parts, per = best
+    cheapest = min(c[0] for c in cands)
+    if cheapest > 0.97 * unsplit:
+        return None
+    # among near-ties the coarsest split: fewer CTAs, fewer hand-offs
+    best = next(c for c in cands if c[0] <= 1.03 * cheapest)
+    _, parts, per = best
     seg_bounds, seg_begin = [], []
     for s, np_, pc in zip(bounds[:-1], parts, per):
         seg_begin.append(len(seg_bounds))

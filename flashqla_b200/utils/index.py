@@ -64,7 +64,8 @@ def tensor_cache(fn: Callable[..., Any]) -> Callable[..., Any]:
         result = fn(*args, **kwargs)
         unpinned = [e for e in entries if not e[3]]
         if len(unpinned) >= _CACHE_SLOTS:
-            entries.remove(unpinned[0])
+            # by identity: list.remove would compare the cached tensors element by element
+            del entries[next(i for i, e in enumerate(entries) if e is unpinned[0])]
         entries.append([args, kwargs, result, False])
         return result
 

@@ -76,8 +76,12 @@ def test_segment_planner_properties():
     # 4 sequences x 16 heads = 64 streams on 148 SMs: halving each sequence gives one full wave
     seg, begin = split_sequences([0, 8192, 16384, 24576, 32768], 16, 148)
     assert len(seg) - 1 == 8 and begin == [0, 2, 4, 6, 8]
-    # 10 sequences x 16 heads already fill the SMs
-    assert split_sequences(list(range(0, 11 * 4096, 4096)), 16, 148) is None
+    # 148 equal streams: exactly one wave, nothing to gain
+    assert split_sequences(list(range(0, 38 * 4096, 4096)), 4, 148) is None
+    # a ragged batch whose longest document would be the tail of the launch: only long ones are cut
+    bounds = [0, 8192] + [8192 + 512 * i for i in range(1, 41)]
+    seg, begin = split_sequences(bounds, 8, 148)
+    assert begin[1] - begin[0] > 1 and all(b - a == 1 for a, b in zip(begin[1:-1], begin[2:]))
     for bounds, heads in (([0, 262144], 8), ([0, 8192, 16384, 24576, 32768], 2),
                           ([0, 100, 5000, 5064, 30000], 2), ([0, 4096 + 77], 2)):
         res = split_sequences(bounds, heads, 148)
@@ -116,6 +120,11 @@ def test_tensor_cache_identity_and_eviction():
     f(xs[0], 1)  # evicted by now (4 slots)
     assert len(calls) == n + 1
     assert len(f.cache_entries) <= 4
+    # eviction goes by identity even when a pinned entry with tensors of another size comes first
+    f.cache_entries[0][3] = True
+    for size in (2, 3, 5, 7, 11):
+        f(torch.zeros(size), 1)
+    assert sum(1 for e in f.cache_entries if not e[3]) <= 4 and f.cache_entries[0][3]
 
 
 def test_pack_helpers_round_trip():
