@@ -179,13 +179,16 @@ def chunk_gated_delta_rule_bwd(
 
     cached = (tuple(cp_cache) if cp_cache is not None else ()) + (None, None, None, None)
     plan = cp.plan_segments(tables, Hv, is_bwd=True, device=k.device) if auto_cp else None
-    lead = None
+    lead = lead_out = None
     if plan is not None:
         if cached[0] is not None:
             seg_h0, lead = cached[0], cached[3]
         else:
             seg_h0, lead = _segment_starts(plan, k, v, A, g, beta_k, scale, h0)
-        seg_dht = cp.backward_segment_states(plan, q, k, v, A, g, beta_k, do, scale, dht_k)
+        if cp.LEAD_IN and _tiles_ok(D):
+            seg_dht, lead_out = cp.backward_end(plan, q, k, v, A, g, beta_k, do, scale, dht_k)
+        else:
+            seg_dht = cp.backward_segment_states(plan, q, k, v, A, g, beta_k, do, scale, dht_k)
         run_tables, run_h0, run_dht = plan.seg_tables, seg_h0, seg_dht
     else:
         run_tables, run_h0, run_dht = tables, h0, dht_k
@@ -200,7 +203,7 @@ def chunk_gated_delta_rule_bwd(
                          output_vnew=True, tables=run_tables, operand_tiles=tiles,
                          lead_chunks=lead if tiles else None)
     bw = ops.bwd_dh(q, k, A, g, beta_k, do, scale, run_dht, tables=run_tables,
-                    operand_tiles=tiles)
+                    operand_tiles=tiles, lead_chunks=lead_out)
     dq, dk, dv, db, dg = ops.bwd_main(q, k, v, fw["vnew"], A, g, beta_k, do, bw["du"], fw["h"],
                                       bw["dh"], scale, tables=run_tables, operand_tiles=tiles)
     dh0 = bw["dh0"]

@@ -34,9 +34,10 @@ MIN_SEGMENT_CHUNKS = 8
 VALUE_SLICES = 1  # CTAs per (segment, head) of the tcgen05 forward kernel
 SEGMENT_OVERHEAD_CHUNKS = 2  # cost of a hand-off, in chunk steps of the main kernel
 CTA_START_CHUNKS = 2  # cost of starting a CTA (tensor-memory allocation, first loads), same unit
-# True: the tcgen05 recurrence kernel starts a segment a few chunks early from a zero state
-# (``forward_start``); False: every segment's start state comes from the separate state-only pass
-# and the merge chain (``forward_segment_states``), as the mma.sync kernels always do.
+# True: the tcgen05 recurrence kernels start a segment a few chunks early (forward,
+# ``forward_start``) or late (reverse, ``backward_end``) from a zero state; False: every segment's
+# start state comes from the separate state-only pass and the merge chain
+# (``forward_segment_states``, ``backward_segment_states``), as the mma.sync kernels always do.
 LEAD_IN = True
 
 
@@ -230,3 +231,22 @@ def backward_segment_states(plan: SegmentPlan, q, k, v, A, g_cum, beta, do, scal
     m = ops.fwd_seq(None, k, v, A, g_cum, beta, scale, None, output_o=False, output_m=True,
                     m_mask=fallback, tables=seg)["M"]
     return ops.merge_states(local, m, fallback, dht, plan.seg_begin, reverse=True)
+
+
+def backward_end(plan: SegmentPlan, q, k, v, A, g_cum, beta, do, scale, dht):
+    """Mirror image of ``forward_start`` for the state gradient, for the tcgen05 reverse
+    recurrence kernel: returns ``(seg_dht, lead)``.  Where no segment of a (sequence, head) falls
+    back, segment ``i`` starts ``lead[i]`` chunks after its end (the head of segment ``i + 1``)
+    from a zero gradient inside the recurrence kernel itself and ``seg_dht`` only carries the
+    gradient of the sequence's own final state; elsewhere the exact chain of
+    ``backward_segment_states`` runs and ``lead`` is 0."""
+    seg = plan.seg_tables
+    _, fallback, lead, exact_warm, any_fb = ops.segment_scan(g_cum, seg.cu, plan.seg_begin,
+                                                             THRESHOLD, from_start=True)
+    local = ops.bwd_dh(q, k, A, g_cum, beta, do, scale, None, output_dh=False, output_du=False,
+                       output_dh0=True, warm_chunks=exact_warm, tables=seg)["dh0"]
+    m = ops.fwd_seq(None, k, v, A, g_cum, beta, scale, None, output_o=False, output_m=True,
+                    m_mask=fallback, tables=seg)["M"]
+    seg_dht = ops.merge_states(local, m, fallback, dht, plan.seg_begin, reverse=True,
+                               any_fallback=any_fb)
+    return seg_dht, lead

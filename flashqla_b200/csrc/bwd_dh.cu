@@ -31,7 +31,8 @@ struct BwdDhParams {
   bf16* dh;          // [chunks, Hv, D, D] or null
   bf16* du;          // [rows, Hv, D] or null
   float* dh0;        // [N, Hv, D, D] or null
-  const int* warm;   // [N, Hv] or null: walk only the first warm[n,hv] chunks (dh0-only pass)
+  const int* warm;   // [N, Hv] or null: walk only the first warm[n,hv] chunks (dh0-only pass);
+                     // a negative entry skips the (sequence, head) altogether
   const int* order;  // [N] or null: block index -> sequence (longest first shortens the tail)
   int N, Hq, Hv;
   float scale;
@@ -88,7 +89,11 @@ __global__ void __launch_bounds__(256, 1) bwd_dh_kernel(const BwdDhParams p) {
   const int v0 = blockIdx.y * BV;
   const SeqSpan sp = p.lay.span(n);
   int c_end = sp.n_chunks;  // exclusive
-  if (p.warm) c_end = min(sp.n_chunks, p.warm[n * p.Hv + hv]);
+  if (p.warm) {
+    const int w = p.warm[n * p.Hv + hv];
+    if (w < 0) return;  // nothing is wanted of this (sequence, head): no output is written
+    c_end = min(sp.n_chunks, w);
+  }
 
   float dS[MTS][NTV][4];
   const long long state_off = ((long long)n * p.Hv + hv) * D * D;
@@ -295,7 +300,7 @@ static int launch_bwd_dh(const BwdDhParams& p, cudaStream_t st) {
 // tcgen05 version for K = V = 128, full walks only (bwd_dh_tc.cu)
 int launch_bwd_dh_tc(const void* q, const void* k, const void* A, const float* g, const void* beta,
                      int beta_is_f32, const void* dO, const float* dht, void* dh, void* du,
-                     float* dh0, int tiled, const int* order, int N, int Hq, int Hv,
+                     float* dh0, int tiled, const int* lead, const int* order, int N, int Hq, int Hv,
                      long long T_rows, float scale, SeqLayout lay, cudaStream_t st);
 
 }  // namespace fqla
@@ -305,7 +310,7 @@ using namespace fqla;
 extern "C" int fqla_bwd_dh(const void* q, const void* k, const void* A, const float* g_cum,
                            const void* beta, int beta_is_f32, const void* dO, const float* dht,
                            void* dh, void* du, float* dh0, const int* warm_chunks,
-                           const int* seq_order, int B, int T, int Hq, int Hv, int D, float scale,
+                           const int* lead_chunks, const int* seq_order, int B, int T, int Hq, int Hv, int D, float scale,
                            const void* cu_seqlens,
                            const void* chunk_offsets, int idx_is64, int N, int operand_tiles,
                            void* stream) {
@@ -313,6 +318,7 @@ extern "C" int fqla_bwd_dh(const void* q, const void* k, const void* A, const fl
     return FQLA_ERR_INVALID_ARG;
   if (cu_seqlens && (!chunk_offsets || B != 1)) return FQLA_ERR_INVALID_ARG;
   if (warm_chunks && (dh || du)) return FQLA_ERR_INVALID_ARG;
+  if (lead_chunks && warm_chunks) return FQLA_ERR_INVALID_ARG;
   BwdDhParams p;
   p.q = (const bf16*)q; p.k = (const bf16*)k; p.A = (const bf16*)A; p.g = g_cum;
   p.beta = beta; p.beta_is_f32 = beta_is_f32; p.dO = (const bf16*)dO; p.dht = dht;
@@ -324,9 +330,10 @@ extern "C" int fqla_bwd_dh(const void* q, const void* k, const void* A, const fl
   static const bool force_legacy = getenv("FQLA_FORCE_MMA_SYNC") != nullptr;
   if (D == 128 && !warm_chunks && !force_legacy)
     return launch_bwd_dh_tc(q, k, A, g_cum, beta, beta_is_f32, dO, dht, dh, du, dh0,
-                            operand_tiles, seq_order, p.N, Hq, Hv, (long long)B * T, scale, p.lay,
+                            operand_tiles, lead_chunks, seq_order, p.N, Hq, Hv, (long long)B * T, scale, p.lay,
                             st);
-  if (operand_tiles) return FQLA_ERR_UNSUPPORTED_DIM;  // only the tcgen05 kernel writes tiles
+  // only the tcgen05 kernel writes tiles or leads out
+  if (operand_tiles || lead_chunks) return FQLA_ERR_UNSUPPORTED_DIM;
   if (D == 128) return launch_bwd_dh<128>(p, st);
   if (D == 64) return launch_bwd_dh<64>(p, st);
   return FQLA_ERR_UNSUPPORTED_DIM;

@@ -42,6 +42,12 @@ struct BwdDhTcParams {
   SeqLayout lay;
   int tiled;  // dh and du are written as operand tiles (dh^T, du^T per chunk) by TMA
   const int* order;  // [N] or null: block index -> sequence (longest first shortens the tail)
+  // [N, Hv] or null: lead-out.  A CTA with lead > 0 starts from a ZERO state gradient `lead`
+  // chunks after the end of its segment (those rows are the head of segment n + 1 of the same
+  // sequence), walks them without output and enters its own last chunk with the gradient it
+  // would have been handed, up to what the gates let through of anything later.  dht is ignored
+  // for such a CTA.
+  const int* lead;
 };
 
 namespace bdtc {
@@ -93,7 +99,11 @@ bwd_dh_tc_kernel(const BwdDhTcParams p, const __grid_constant__ CUtensorMap map_
   const int n = p.order ? p.order[blockIdx.x / p.Hv] : (int)(blockIdx.x / p.Hv);
   const int hq = hv / (p.Hv / p.Hq);
   const SeqSpan sp = p.lay.span(n);
-  const int n_it = sp.n_chunks;  // iteration `it` handles chunk n_it - 1 - it
+  // iteration `it` handles chunk n_it - 1 - it of the segment; chunks >= sp.n_chunks are the
+  // lead-out chunks (whole chunks, except possibly the very last one of the sequence)
+  const int lead = (p.lead && sp.n_chunks > 0) ? p.lead[n * p.Hv + hv] : 0;
+  const int n_it = sp.n_chunks + lead;
+  const int len_ext = sp.len + (lead > 0 ? min(lead * CHUNK, p.lay.span(n + 1).len) : 0);
 
   if (tid == 0) {
     mbar_init(&bars[FULL0], 1);
@@ -147,7 +157,7 @@ bwd_dh_tc_kernel(const BwdDhTcParams p, const __grid_constant__ CUtensorMap map_
       float x[32];
 #pragma unroll
       for (int j = 0; j < 32; ++j)
-        x[j] = p.dht ? p.dht[state_off + (long long)(k0 + j) * D + v] : 0.f;
+        x[j] = (p.dht && lead == 0) ? p.dht[state_off + (long long)(k0 + j) * D + v] : 0.f;
       tmem_st32(tmem + lane_sel + TM_S + k0, x);
     }
     tmem_st_wait();
@@ -156,7 +166,8 @@ bwd_dh_tc_kernel(const BwdDhTcParams p, const __grid_constant__ CUtensorMap map_
       if (it > 0) ok = WAIT(S_DONE, (it - 1) & 1);
       if (!ok) break;
       tc_fence_after();
-      bf16* hdst = p.dh ? p.dh + ((sp.chunk_base + c) * p.Hv + hv) * (long long)D * D : nullptr;
+      bf16* hdst = (p.dh && it >= lead)
+                       ? p.dh + ((sp.chunk_base + c) * p.Hv + hv) * (long long)D * D : nullptr;
 #pragma unroll 1
       for (int kb = 0; kb < 2; ++kb) {
         float x[32], y[32];
@@ -249,7 +260,7 @@ bwd_dh_tc_kernel(const BwdDhTcParams p, const __grid_constant__ CUtensorMap map_
     for (int it = 0; it < n_it && ok; ++it) {
       const int c = n_it - 1 - it;
       const long long row0 = sp.bos + (long long)c * CHUNK;
-      const int valid = min(CHUNK, sp.len - c * CHUNK);
+      const int valid = min(CHUNK, len_ext - c * CHUNK);
       ok = WAIT(FULL0 + (it & 1), (it >> 1) & 1) && WAIT(X2_DONE, it & 1) && WAIT(X1_DONE, it & 1);
       if (!ok) break;
       tc_fence_after();
@@ -279,7 +290,7 @@ bwd_dh_tc_kernel(const BwdDhTcParams p, const __grid_constant__ CUtensorMap map_
           tc_fence_before();
           mbar_arrive(&bars[DV_READY]);
         }
-        if (p.du && !p.tiled) {
+        if (p.du && !p.tiled && it >= lead) {
 #pragma unroll
           for (int j = 0; j < 32; ++j)
             if (32 * h + j < valid)
@@ -376,7 +387,7 @@ bwd_dh_tc_kernel(const BwdDhTcParams p, const __grid_constant__ CUtensorMap map_
         tma_store_wait_read();  // du^T of the chunk before has left its tile
         umma_commit(&bars[X1_DONE]);
         const int y_tile = (int)(((sp.chunk_base + (n_it - 1 - it)) * p.Hv + hv) * D);
-        if (p.tiled && p.dh) {  // the operand copy of dS^T is dh of this chunk
+        if (p.tiled && p.dh && it >= lead) {  // the operand copy of dS^T is dh of this chunk
           tma_store_2d(&map_dh, 0, y_tile, smem + OFF_ST);
           tma_store_2d(&map_dh, 64, y_tile, smem + OFF_ST + 16384);
           tma_store_commit();
@@ -395,7 +406,7 @@ bwd_dh_tc_kernel(const BwdDhTcParams p, const __grid_constant__ CUtensorMap map_
         umma_group<4, 128, 0, 128, 0, true>(tmem + TM_S, domn0_lo + so, qsmn_lo, ID_UPD_Q);
         tma_store_wait_read();  // the dS^T tile may be rewritten after this
         umma_commit(&bars[S_DONE]);
-        if (p.tiled && p.du) {
+        if (p.tiled && p.du && it >= lead) {
           tma_store_2d(&map_du, 0, y_tile, smem + OFF_DVT);
           tma_store_commit();
         }
@@ -419,7 +430,7 @@ bwd_dh_tc_kernel(const BwdDhTcParams p, const __grid_constant__ CUtensorMap map_
     auto fetch = [&](int it) {
       const int c = n_it - 1 - it;
       const long long row0 = sp.bos + (long long)c * CHUNK;
-      const int valid = min(CHUNK, sp.len - c * CHUNK);
+      const int valid = min(CHUNK, len_ext - c * CHUNK);
       gl_r = p.g[(row0 + valid - 1) * p.Hv + hv];
 #pragma unroll
       for (int z = 0; z < 2; ++z) {
@@ -433,7 +444,7 @@ bwd_dh_tc_kernel(const BwdDhTcParams p, const __grid_constant__ CUtensorMap map_
     auto a_part = [&](int j) {
       const int sj = j & 1, c = n_it - 1 - j;
       const long long row0 = sp.bos + (long long)c * CHUNK;
-      const int valid = min(CHUNK, sp.len - c * CHUNK);
+      const int valid = min(CHUNK, len_ext - c * CHUNK);
       if (j >= 2 && !WAIT(EMPTYA0 + sj, ((j >> 1) - 1) & 1)) return false;
       float* vs = vec + (j & 3) * VEC_SLOT_FLOATS;
 #pragma unroll
@@ -473,7 +484,7 @@ bwd_dh_tc_kernel(const BwdDhTcParams p, const __grid_constant__ CUtensorMap map_
     for (int it = 0; it < n_it && ok; ++it) {
       const int s = it & 1, c = n_it - 1 - it;
       const long long row0 = sp.bos + (long long)c * CHUNK;
-      const int valid = min(CHUNK, sp.len - c * CHUNK);
+      const int valid = min(CHUNK, len_ext - c * CHUNK);
       if (it >= 2) {
         ok = WAIT(EMPTY0 + s, ((it >> 1) - 1) & 1);
         if (!ok) break;
@@ -590,7 +601,7 @@ int make_tile_map(CUtensorMap* m, const void* ptr, long long rows, long long col
 
 int launch_bwd_dh_tc(const void* q, const void* k, const void* A, const float* g, const void* beta,
                      int beta_is_f32, const void* dO, const float* dht, void* dh, void* du,
-                     float* dh0, int tiled, const int* order, int N, int Hq, int Hv,
+                     float* dh0, int tiled, const int* lead, const int* order, int N, int Hq, int Hv,
                      long long T_rows, float scale, SeqLayout lay, cudaStream_t st) {
   using namespace bdtc;
   CUtensorMap mq, mk, mdo, ma, mdh, mdu;
@@ -610,6 +621,7 @@ int launch_bwd_dh_tc(const void* q, const void* k, const void* A, const float* g
   BwdDhTcParams p;
   p.tiled = tiled;
   p.order = order;
+  p.lead = lead;
   p.g = g; p.beta = beta; p.beta_is_f32 = beta_is_f32; p.dht = dht;
   p.dh = (bf16*)dh; p.du = (bf16*)du; p.dh0 = dh0;
   p.N = N; p.Hq = Hq; p.Hv = Hv; p.scale = scale; p.lay = lay;

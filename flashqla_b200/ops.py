@@ -224,11 +224,13 @@ def fwd_seq(q, k, v, a, g_cum, b, scale, initial_state=None, *, output_final_sta
 
 @on_tensor_device
 def bwd_dh(q, k, a, g_cum, b, do, scale, dht=None, *, output_dh=True, output_du=True,
-           output_dh0=True, warm_chunks=None, cu_seqlens=None, tables: SeqTables | None = None,
-           operand_tiles: bool = False):
+           output_dh0=True, warm_chunks=None, lead_chunks=None, cu_seqlens=None,
+           tables: SeqTables | None = None, operand_tiles: bool = False):
     """Reverse recurrence of the state gradient; returns a dict with ``dh, du, dh0``
     (reference: ``blackwell/cp_bwd.py:592-701`` and the dS chain of ``blackwell/fused_bwd.py``).
-    ``operand_tiles``: ``dh`` as ``[chunks, Hv, V, K]``, ``du`` as ``[chunks, Hv, V, 64]``."""
+    ``operand_tiles``: ``dh`` as ``[chunks, Hv, V, K]``, ``du`` as ``[chunks, Hv, V, 64]``.
+    ``lead_chunks`` (``[N, Hv]`` int32, segments of a split plan): segment ``n`` starts that many
+    chunks after its end from a zero gradient instead of taking ``dht[n]``."""
     _require_cuda(q, k, a, g_cum, b, do)
     _check_bf16(q=q, k=k, a=a, do=do)
     B, T, Hq, D = k.shape
@@ -250,7 +252,7 @@ def bwd_dh(q, k, a, g_cum, b, do, scale, dht=None, *, output_dh=True, output_du=
     st = _lib.load().fqla_bwd_dh(
         _ptr(q), _ptr(k), _ptr(a), _ptr(g_cum), _ptr(b), _beta_flag(b), _ptr(do), _ptr(dht),
         _ptr(out.get("dh")), _ptr(out.get("du")), _ptr(out.get("dh0")), _ptr(warm_chunks),
-        _ptr(tb.order), tb.B, tb.T, Hq, Hv, D, float(scale), cu, offs, is64, N, int(operand_tiles),
+        _ptr(lead_chunks), _ptr(tb.order), tb.B, tb.T, Hq, Hv, D, float(scale), cu, offs, is64, N, int(operand_tiles),
         _stream(k))
     _lib.check(st, "bwd_dh")
     return out

@@ -91,15 +91,17 @@ int fqla_fwd_seq(const void* q, const void* k, const void* v, const void* A, con
  * gradient of vnew), dh0.  warm_chunks (optional, dh0-only calls): walk only the first
  * warm_chunks[n,hv] chunks from a zero gradient.  operand_tiles != 0 (K = V = 128, no
  * warm_chunks): dh is written as [chunks, Hv, V, K] and du as [chunks, Hv, V, 64], the operand
- * layouts of fqla_fwd_seq's h and vnew; FQLA_ERR_UNSUPPORTED_DIM otherwise.  seq_order: as for
- * fqla_fwd_seq.
+ * layouts of fqla_fwd_seq's h and vnew; FQLA_ERR_UNSUPPORTED_DIM otherwise.  lead_chunks
+ * (optional, [N, Hv] int32, K = V = 128, not with warm_chunks): the mirror image of
+ * fqla_fwd_seq's lead_chunks; sequence n is a segment of a longer sequence, whose following rows
+ * belong to segment n + 1, and starts lead_chunks[n,hv] chunks after its end from a zero
+ * gradient (dht is ignored for it) instead of being handed one.  seq_order: as for fqla_fwd_seq.
  * Replaces fused_gdr_dh_ws (blackwell/cp_bwd.py:592-701) and the dS chain of fused_gdr_bwd
  * (blackwell/fused_bwd.py:336-474). */
 int fqla_bwd_dh(const void* q, const void* k, const void* A, const float* g_cum, const void* beta,
                 int beta_is_f32, const void* dO, const float* dht, void* dh, void* du, float* dh0,
-                const int* warm_chunks, const int* seq_order, int B, int T, int Hq, int Hv, int D,
-                float scale,
-                const void* cu_seqlens, const void* chunk_offsets, int idx_is64, int N,
+                const int* warm_chunks, const int* lead_chunks, const int* seq_order, int B, int T,
+                int Hq, int Hv, int D, float scale, const void* cu_seqlens, const void* chunk_offsets, int idx_is64, int N,
                 int operand_tiles, void* stream);
 
 /* Chunk-parallel backward: dq, dk (per VALUE head, [B,T,Hv,D] bf16), dv, dbeta and the

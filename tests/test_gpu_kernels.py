@@ -332,6 +332,81 @@ def test_lead_in_forward_agrees_with_explicit_start_states():
     assert orc.rel_err(ht_lead, ht_sep) < 2e-3
 
 
+@pytest.mark.parametrize("case", ["one_sequence", "packed_ragged"])
+def test_lead_out_backward_agrees_with_explicit_end_gradients(case):
+    """The reverse recurrence kernel that starts a segment a few chunks late from a zero gradient
+    against the same kernel fed by the separate dh0-only pass and the transposed merge chain, and
+    both against the fp32 oracle.  The ragged case ends every sequence in a partial chunk, which
+    a lead-out may have to walk first."""
+    import flashqla_b200 as fq
+    from flashqla_b200 import cp
+
+    if case == "one_sequence":
+        d = _inputs(64 * 70 + 13, 2, 4, seed=74)
+        cu = None
+    else:
+        d = _inputs(64 * 40 + 5 + 64 * 17 + 30 + 64 * 9 + 1, 2, 4, seed=75,
+                    cu=[0, 64 * 40 + 5, 64 * 57 + 35, 64 * 66 + 36])
+        cu = d["cu_seqlens"]
+
+    def run():
+        g_cum, A, _, _, _, cache = fq.chunk_gated_delta_rule_fwd(
+            d["q"], d["k"], d["v"], d["g"], d["beta"], None, d["h0"], cu,
+            output_final_state=True)
+        return fq.chunk_gated_delta_rule_bwd(d["q"], d["k"], d["v"], g_cum, d["beta"], A, d["do"],
+                                             d["dht"], None, d["h0"], cu, cp_cache=cache)
+
+    from flashqla_b200 import ops
+
+    tb = ops.SeqTables(1, d["k"].shape[1], cu)
+    plan = cp.plan_segments(tb, 4, device=d["k"].device)
+    assert plan is not None and plan.n_seg > tb.N
+    assert cp.LEAD_IN
+    lead = run()
+    cp.LEAD_IN = False
+    try:
+        sep = run()
+    finally:
+        cp.LEAD_IN = True
+    for a, b, name in zip(lead, sep, ("dq", "dk", "dv", "db", "dg", "dh0")):
+        assert orc.rel_err(a.float(), b.float()) < 3e-3, name
+    want = orc.chunk_gdr_bwd(d["q"].float().cpu(), d["k"].float().cpu(), d["v"].float().cpu(),
+                             d["g"].cpu(), d["beta"].float().cpu(), d["do"].float().cpu(),
+                             d["dht"].cpu(), None, d["h0"].cpu(),
+                             None if cu is None else cu.cpu())
+    for a, b, name in zip(lead, want, ("dq", "dk", "dv", "db", "dg", "dh0")):
+        assert orc.rel_err(a.float().cpu(), b) < 1e-2, name
+
+
+@pytest.mark.parametrize("tiles", [False, True], ids=["row_major", "operand_tiles"])
+def test_lead_out_over_a_partial_last_chunk_is_exact(tiles):
+    """A lead-out that covers ALL rows after the segment, the partial last chunk of the sequence
+    included, from a zero end gradient is no approximation: the segment's dh, du and dh0 must be
+    the bits of the unsplit walk."""
+    from flashqla_b200 import ops
+
+    T = 64 * 10 + 30
+    d = _inputs(T, 2, 4, seed=76)
+    _, g_cum, A = _prep(d)
+    scale = 128 ** -0.5
+    full = ops.bwd_dh(d["q"], d["k"], A, g_cum, d["beta"], d["do"], scale, None,
+                      tables=ops.SeqTables(1, T, None), operand_tiles=tiles)
+    seg_cu = torch.tensor([0, 640, T], dtype=torch.int32, device=DEV)
+    lead = torch.tensor([[1] * 4, [0] * 4], dtype=torch.int32, device=DEV)
+    # a non-zero gradient offered to the leading segment must be ignored
+    dht = torch.ones(2, 4, 128, 128, device=DEV)
+    dht[1] = 0
+    part = ops.bwd_dh(d["q"], d["k"], A, g_cum, d["beta"], d["do"], scale, dht,
+                      tables=ops.SeqTables(1, T, seg_cu), operand_tiles=tiles, lead_chunks=lead)
+    torch.cuda.synchronize()
+    assert torch.equal(part["dh"], full["dh"])
+    assert torch.equal(part["dh0"][0], full["dh0"][0])
+    if tiles:
+        assert torch.equal(part["du"], full["du"])
+    else:
+        assert torch.equal(part["du"][:, :T], full["du"][:, :T])
+
+
 def test_longest_first_block_order_does_not_change_results():
     """Packed batches hand their sequences to the sequential kernels longest first (a block-index
     -> sequence table); the outputs must be the same bits as in index order."""
