@@ -47,7 +47,7 @@ WORKLOADS = {
     "c1_fwd": dict(B=4, T=8192, Hq=16, Hv=16, mode="fwd", varlen=None, h0=False),
     "c1_fwdbwd": dict(B=4, T=8192, Hq=16, Hv=16, mode="fwdbwd", varlen=None, h0=False),
     "c2_fwd": dict(B=1, T=None, Hq=8, Hv=8, mode="fwd", varlen="uniform64", h0=True),
-    "c3_fwdbwd": dict(B=1, T=32768, Hq=16, Hv=32, mode="fwdbwd", varlen="lognormal", h0=True),
+    "c3_fwdbwd": dict(B=1, T=32768, Hq=16, Hv=32, mode="fwdbwd", varlen="lognormal", h0="zeros"),
     "c4_fwdbwd": dict(B=1, T=262144, Hq=8, Hv=8, mode="fwdbwd", varlen=None, h0=False),
     "c4_fwd": dict(B=1, T=262144, Hq=8, Hv=8, mode="fwd", varlen=None, h0=False),
     # a quarter of c1 (one sequence): small enough for a full ncu capture, inputs still > L2
@@ -95,6 +95,8 @@ def make_batch(w, device, seed, batch=None):
     beta = torch.sigmoid(rn(B, T, Hv)).bfloat16()
     N = B if cu is None else len(cu) - 1
     h0 = 0.1 * rn(N, Hv, 128, 128) if w["h0"] else None
+    if w["h0"] == "zeros":  # an initial state that is present (its gradient is wanted) but zero
+        h0.zero_()
     do = rn(B, T, Hv, 128).bfloat16()
     dht = 0.1 * rn(N, Hv, 128, 128)
     cu_t = None if cu is None else torch.tensor(cu, dtype=torch.int32, device=device)

@@ -212,14 +212,21 @@ def chunk_gated_delta_rule_bwd(
     if initial_state is None:
         dh0 = None
     dh0 = _state_out(dh0, state_v_first)
-    if Hq < Hv:
+    dq, dk, dv, db, dg = finish_backward(dq, dk, dv, db, dg, Hq, beta.dtype, in_dtype, cu_seqlens)
+    return dq, dk, dv, db, dg, dh0
+
+
+def finish_backward(dq, dk, dv, db, dg, Hq, beta_dtype, in_dtype, cu_seqlens):
+    """What follows the chunk-parallel backward kernel: the sum of dq, dk over the value heads
+    of a group, the reverse chunk-local cumsum of dg, and the output dtypes."""
+    if Hq < dq.shape[2]:
         dq = ops.group_reduce_vector(dq, Hq)
         dk = ops.group_reduce_vector(dk, Hq)
     dg = ops.chunk_local_cumsum(dg, CHUNK_SIZE, cu_seqlens, reverse=True)
-    db = db.to(beta.dtype)
+    db = db.to(beta_dtype)
     if in_dtype != torch.bfloat16:
         dq, dk, dv = dq.to(in_dtype), dk.to(in_dtype), dv.to(in_dtype)
-    return dq, dk, dv, db, dg, dh0
+    return dq, dk, dv, db, dg
 
 
 class ChunkGatedDeltaRuleFunction(torch.autograd.Function):

@@ -17,8 +17,9 @@ P, I, LL, F = C.c_void_p, C.c_int, C.c_longlong, C.c_float
 SIGNATURES = {
     "fqla_chunk_local_cumsum": [P, P, I, I, I, P, I, I, P, LL, I, P],
     "fqla_kkt_solve": [P, P, I, P, P, P, I, I, I, I, I, P, I, P, LL, P],
-    "fqla_fwd_seq": [P, P, P, P, P, P, I, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, F, P, P, I, I, I, P],
-    "fqla_bwd_dh": [P, P, P, P, P, I, P, P, P, P, P, P, P, P, I, I, I, I, I, F, P, P, I, I, I, P],
+    "fqla_fwd_seq": [P] * 6 + [I] + [P] * 11 + [I] * 6 + [F, P, P, I, I, I, P],
+    "fqla_bwd_dh": [P, P, P, P, P, I, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, P, P, I, I, I,
+                    P],
     "fqla_bwd_main": [P] * 7 + [I] + [P] * 9 + [I, I, I, I, I, F, P, P, P, I, LL, I, P],
     "fqla_group_reduce": [P, P, LL, I, I, I, P],
     "fqla_warmup_scan": [P, I, I, P, I, I, F, I, P, P, P, P],

@@ -151,7 +151,10 @@ def _build_plan(bounds, Hv, device, idx_dtype, T_rows) -> SegmentPlan | None:
     res = split_sequences(bounds, Hv, sm_count(device))
     if res is None:
         return None
-    seg_bounds, seg_begin = res
+    return _plan_from_bounds(res[0], res[1], device, idx_dtype, T_rows)
+
+
+def _plan_from_bounds(seg_bounds, seg_begin, device, idx_dtype, T_rows) -> SegmentPlan:
     seg_cu = torch.tensor(seg_bounds, dtype=idx_dtype, device=device)
     begin = torch.tensor(seg_begin, dtype=torch.int32, device=device)
     tables = SeqTables(1, T_rows, seg_cu)
@@ -165,6 +168,33 @@ def _build_plan(bounds, Hv, device, idx_dtype, T_rows) -> SegmentPlan | None:
     return SegmentPlan(tables, begin, begin[:-1].long(), begin[1:].long() - 1,
                        torch.tensor(keep_fwd, dtype=torch.int32, device=device),
                        torch.tensor(keep_bwd, dtype=torch.int32, device=device), n_seg)
+
+
+_shard_plan_cache: dict = {}
+
+
+def shard_plan(T: int, Hv: int, device, short: str) -> SegmentPlan | None:
+    """Segment plan of ONE sequence of ``T`` tokens (a chunk multiple) whose edge segment has to
+    wait for a state from elsewhere (another GPU): as many segments as fit one CTA per SM, the
+    waiting one (``short`` = "first" for the forward direction, "last" for the reverse one) about
+    half as long as the others, so that it can start late and still finish with them.  ``None``
+    when fewer than three segments fit."""
+    key = (T, Hv, str(device), short)
+    if key not in _shard_plan_cache:
+        chunks = T // CHUNK_SIZE
+        n = min(sm_count(device) // Hv, chunks // MIN_SEGMENT_CHUNKS)
+        plan = None
+        if n >= 3:
+            short_len = max(MIN_SEGMENT_CHUNKS, int(chunks / (n - 0.5) / 2))
+            base, extra = divmod(chunks - short_len, n - 1)
+            lens = [base + (1 if i < extra else 0) for i in range(n - 1)]
+            lens = [short_len] + lens if short == "first" else lens + [short_len]
+            bounds = [0]
+            for c in lens:
+                bounds.append(bounds[-1] + c * CHUNK_SIZE)
+            plan = _plan_from_bounds(bounds, [0, n], torch.device(device), torch.int32, T)
+        _shard_plan_cache[key] = plan
+    return _shard_plan_cache[key]
 
 
 @tensor_cache

@@ -34,6 +34,8 @@ struct BwdDhParams {
   const int* warm;   // [N, Hv] or null: walk only the first warm[n,hv] chunks (dh0-only pass);
                      // a negative entry skips the (sequence, head) altogether
   const int* order;  // [N] or null: block index -> sequence (longest first shortens the tail)
+  const int* run_mask;  // [N, Hv] or null: pairs whose entry differs from run_value are skipped
+  int run_value;
   int N, Hq, Hv;
   float scale;
   SeqLayout lay;
@@ -87,6 +89,7 @@ __global__ void __launch_bounds__(256, 1) bwd_dh_kernel(const BwdDhParams p) {
   const int n = p.order ? p.order[blockIdx.x / p.Hv] : (int)(blockIdx.x / p.Hv);
   const int hq = hv / (p.Hv / p.Hq);
   const int v0 = blockIdx.y * BV;
+  if (p.run_mask && p.run_mask[n * p.Hv + hv] != p.run_value) return;  // uniform per CTA
   const SeqSpan sp = p.lay.span(n);
   int c_end = sp.n_chunks;  // exclusive
   if (p.warm) {
@@ -300,7 +303,8 @@ static int launch_bwd_dh(const BwdDhParams& p, cudaStream_t st) {
 // tcgen05 version for K = V = 128, full walks only (bwd_dh_tc.cu)
 int launch_bwd_dh_tc(const void* q, const void* k, const void* A, const float* g, const void* beta,
                      int beta_is_f32, const void* dO, const float* dht, void* dh, void* du,
-                     float* dh0, int tiled, const int* lead, const int* order, int N, int Hq, int Hv,
+                     float* dh0, int tiled, const int* lead, const int* order, const int* run_mask,
+                     int run_value, int N, int Hq, int Hv,
                      long long T_rows, float scale, SeqLayout lay, cudaStream_t st);
 
 }  // namespace fqla
@@ -310,7 +314,8 @@ using namespace fqla;
 extern "C" int fqla_bwd_dh(const void* q, const void* k, const void* A, const float* g_cum,
                            const void* beta, int beta_is_f32, const void* dO, const float* dht,
                            void* dh, void* du, float* dh0, const int* warm_chunks,
-                           const int* lead_chunks, const int* seq_order, int B, int T, int Hq, int Hv, int D, float scale,
+                           const int* lead_chunks, const int* seq_order, const int* run_mask,
+                           int run_value, int B, int T, int Hq, int Hv, int D, float scale,
                            const void* cu_seqlens,
                            const void* chunk_offsets, int idx_is64, int N, int operand_tiles,
                            void* stream) {
@@ -323,6 +328,7 @@ extern "C" int fqla_bwd_dh(const void* q, const void* k, const void* A, const fl
   p.q = (const bf16*)q; p.k = (const bf16*)k; p.A = (const bf16*)A; p.g = g_cum;
   p.beta = beta; p.beta_is_f32 = beta_is_f32; p.dO = (const bf16*)dO; p.dht = dht;
   p.dh = (bf16*)dh; p.du = (bf16*)du; p.dh0 = dh0; p.warm = warm_chunks; p.order = seq_order;
+  p.run_mask = run_mask; p.run_value = run_value;
   p.N = cu_seqlens ? N : B; p.Hq = Hq; p.Hv = Hv; p.scale = scale;
   p.lay = SeqLayout{{cu_seqlens, idx_is64}, {chunk_offsets, idx_is64}, T};
   if (p.N <= 0) return FQLA_OK;
@@ -330,7 +336,7 @@ extern "C" int fqla_bwd_dh(const void* q, const void* k, const void* A, const fl
   static const bool force_legacy = getenv("FQLA_FORCE_MMA_SYNC") != nullptr;
   if (D == 128 && !warm_chunks && !force_legacy)
     return launch_bwd_dh_tc(q, k, A, g_cum, beta, beta_is_f32, dO, dht, dh, du, dh0,
-                            operand_tiles, lead_chunks, seq_order, p.N, Hq, Hv, (long long)B * T, scale, p.lay,
+                            operand_tiles, lead_chunks, seq_order, run_mask, run_value, p.N, Hq, Hv, (long long)B * T, scale, p.lay,
                             st);
   // only the tcgen05 kernel writes tiles or leads out
   if (operand_tiles || lead_chunks) return FQLA_ERR_UNSUPPORTED_DIM;

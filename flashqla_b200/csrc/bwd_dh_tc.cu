@@ -48,6 +48,9 @@ struct BwdDhTcParams {
   // would have been handed, up to what the gates let through of anything later.  dht is ignored
   // for such a CTA.
   const int* lead;
+  // [N, Hv] or null: a CTA whose entry differs from run_value returns at once
+  const int* run_mask;
+  int run_value;
 };
 
 namespace bdtc {
@@ -98,6 +101,7 @@ bwd_dh_tc_kernel(const BwdDhTcParams p, const __grid_constant__ CUtensorMap map_
   const int hv = blockIdx.x % p.Hv;
   const int n = p.order ? p.order[blockIdx.x / p.Hv] : (int)(blockIdx.x / p.Hv);
   const int hq = hv / (p.Hv / p.Hq);
+  if (p.run_mask && p.run_mask[n * p.Hv + hv] != p.run_value) return;  // uniform per CTA
   const SeqSpan sp = p.lay.span(n);
   // iteration `it` handles chunk n_it - 1 - it of the segment; chunks >= sp.n_chunks are the
   // lead-out chunks (whole chunks, except possibly the very last one of the sequence)
@@ -601,7 +605,8 @@ int make_tile_map(CUtensorMap* m, const void* ptr, long long rows, long long col
 
 int launch_bwd_dh_tc(const void* q, const void* k, const void* A, const float* g, const void* beta,
                      int beta_is_f32, const void* dO, const float* dht, void* dh, void* du,
-                     float* dh0, int tiled, const int* lead, const int* order, int N, int Hq, int Hv,
+                     float* dh0, int tiled, const int* lead, const int* order, const int* run_mask,
+                     int run_value, int N, int Hq, int Hv,
                      long long T_rows, float scale, SeqLayout lay, cudaStream_t st) {
   using namespace bdtc;
   CUtensorMap mq, mk, mdo, ma, mdh, mdu;
@@ -622,6 +627,8 @@ int launch_bwd_dh_tc(const void* q, const void* k, const void* A, const float* g
   p.tiled = tiled;
   p.order = order;
   p.lead = lead;
+  p.run_mask = run_mask;
+  p.run_value = run_value;
   p.g = g; p.beta = beta; p.beta_is_f32 = beta_is_f32; p.dht = dht;
   p.dh = (bf16*)dh; p.du = (bf16*)du; p.dh0 = dh0;
   p.N = N; p.Hq = Hq; p.Hv = Hv; p.scale = scale; p.lay = lay;

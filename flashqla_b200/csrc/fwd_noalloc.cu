@@ -80,6 +80,6 @@ extern "C" int fqla_fwd_noalloc(const void* q, const void* k, const void* v, con
                       chunk_indices, num_chunks, stream);
   if (rc != FQLA_OK) return rc;
   return fqla_fwd_seq(q, k, v, A, g_cum, beta, beta_is_f32, h0, ht, o, nullptr, nullptr, nullptr,
-                      nullptr, nullptr, nullptr, nullptr, B, T, Hq, Hv, D, scale, cu_seqlens,
-                      chunk_offsets, idx_is64, N, 0, stream);
+                      nullptr, nullptr, nullptr, nullptr, nullptr, 0, B, T, Hq, Hv, D, scale,
+                      cu_seqlens, chunk_offsets, idx_is64, N, 0, stream);
 }

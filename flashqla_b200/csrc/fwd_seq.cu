@@ -26,8 +26,9 @@ namespace fqla {
 // tcgen05 implementation of the full forward (fwd_tc.cu)
 int launch_fwd_tc(const void* q, const void* k, const void* v, const void* A, const float* g,
                   const void* beta, int beta_is_f32, const float* h0, float* ht, void* o, void* h,
-                  void* vnew, int tiled, const int* lead, const int* order, int N, int Hq, int Hv,
-                  long long T_rows, float scale, SeqLayout lay, cudaStream_t st);
+                  void* vnew, int tiled, const int* lead, const int* order, const int* run_mask,
+                  int run_value, int N, int Hq, int Hv, long long T_rows, float scale,
+                  SeqLayout lay, cudaStream_t st);
 
 struct FwdSeqParams {
   const bf16* q;      // may be null (state-only pass)
@@ -46,6 +47,8 @@ struct FwdSeqParams {
   const int* warm;    // [N, Hv] or null: process only the last warm[n,hv] chunks (state-only)
   const int* m_mask;  // [N, Hv] or null: compute M only where non-zero
   const int* order;   // [N] or null: block index -> sequence (longest first shortens the tail)
+  const int* run_mask;  // [N, Hv] or null: pairs whose entry differs from run_value are skipped
+  int run_value;
   int N, Hq, Hv;
   long long T_rows;   // total rows of the token axis (for zero-filling the tail of o)
   float scale;
@@ -104,7 +107,8 @@ __global__ void __launch_bounds__(256, 1) fwd_seq_kernel(const FwdSeqParams p) {
   const int v0 = (m_slice ? (int)blockIdx.y - V_SLICES : (int)blockIdx.y) * BV;
   const bool with_q = p.q != nullptr && !m_slice;
   const SeqSpan sp = p.lay.span(n);
-  if (m_slice && p.m_mask && p.m_mask[n * p.Hv + hv] == 0) return;  // uniform per CTA
+  if (p.run_mask && p.run_mask[n * p.Hv + hv] != p.run_value) return;  // uniform per CTA
+  if (m_slice && p.m_mask && p.m_mask[n * p.Hv + hv] == 0) return;
   if (!m_slice && !p.ht && !p.o && !p.h && !p.vnew) return;          // nothing asked of this slice
 
   int c_begin = 0;
@@ -351,8 +355,8 @@ extern "C" int fqla_fwd_seq(const void* q, const void* k, const void* v, const v
                             const float* g_cum, const void* beta, int beta_is_f32,
                             const float* h0, float* ht, void* o, void* h, void* vnew, float* M,
                             const int* warm_chunks, const int* m_mask, const int* lead_chunks,
-                            const int* seq_order, int B, int T, int Hq, int Hv, int D, float scale,
-                            const void* cu_seqlens,
+                            const int* seq_order, const int* run_mask, int run_value, int B, int T,
+                            int Hq, int Hv, int D, float scale, const void* cu_seqlens,
                             const void* chunk_offsets, int idx_is64, int N, int operand_tiles,
                             void* stream) {
   if (!k || !v || !A || !g_cum || !beta || Hq <= 0 || Hv % Hq) return FQLA_ERR_INVALID_ARG;
@@ -367,6 +371,8 @@ extern "C" int fqla_fwd_seq(const void* q, const void* k, const void* v, const v
   p.warm = warm_chunks;
   p.m_mask = m_mask;
   p.order = seq_order;
+  p.run_mask = run_mask;
+  p.run_value = run_value;
   p.N = cu_seqlens ? N : B; p.Hq = Hq; p.Hv = Hv;
   p.T_rows = (long long)B * T;
   p.scale = scale;
@@ -380,7 +386,8 @@ extern "C" int fqla_fwd_seq(const void* q, const void* k, const void* v, const v
   const bool full = q && o, recompute = !q && !o && (h || vnew);
   if (D == 128 && (full || recompute) && !M && !warm_chunks && !m_mask && !force_legacy)
     return launch_fwd_tc(q, k, v, A, g_cum, beta, beta_is_f32, h0, ht, o, h, vnew, operand_tiles,
-                         lead_chunks, seq_order, p.N, Hq, Hv, p.T_rows, scale, p.lay, st);
+                         lead_chunks, seq_order, run_mask, run_value, p.N, Hq, Hv, p.T_rows, scale,
+                         p.lay, st);
   if (operand_tiles || lead_chunks) return FQLA_ERR_UNSUPPORTED_DIM;  // tcgen05 kernel only
   if (D == 128) return launch_fwd_seq<128>(p, st);
   if (D == 64) return launch_fwd_seq<64>(p, st);

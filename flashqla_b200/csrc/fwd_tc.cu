@@ -95,6 +95,10 @@ struct FwdTcParams {
   // the rows just before a segment are the tail of the segment before it, whose influence dies
   // out within `lead` chunks.  h0 is ignored for such a CTA.
   const int* lead;
+  // [N, Hv] or null: a CTA whose entry differs from run_value returns at once, reading and
+  // writing nothing (two launches can share one set of outputs, each taking its own pairs)
+  const int* run_mask;
+  int run_value;
   // [N] or null: the CTAs of block index i / Hv walk sequence order[i].  Blocks start in index
   // order, so a table that lists the longest sequences first shortens the tail of a ragged batch.
   const int* order;
@@ -174,6 +178,7 @@ fwd_tc_kernel(const FwdTcParams p, const __grid_constant__ CUtensorMap map_q,
   const int hv = blockIdx.x % p.Hv;
   const int n = p.order ? p.order[blockIdx.x / p.Hv] : (int)(blockIdx.x / p.Hv);
   const int hq = hv / (p.Hv / p.Hq);
+  if (p.run_mask && p.run_mask[n * p.Hv + hv] != p.run_value) return;  // uniform per CTA
   const SeqSpan sp = p.lay.span(n);
   // iteration j handles chunk c = j - lead of the sequence; c < 0 are the lead-in chunks
   const int lead = p.lead ? p.lead[n * p.Hv + hv] : 0;
@@ -882,8 +887,9 @@ static int make_map(CUtensorMap* m, const void* ptr, long long rows, long long c
 
 int launch_fwd_tc(const void* q, const void* k, const void* v, const void* A, const float* g,
                   const void* beta, int beta_is_f32, const float* h0, float* ht, void* o, void* h,
-                  void* vnew, int tiled, const int* lead, const int* order, int N, int Hq, int Hv,
-                  long long T_rows, float scale, SeqLayout lay, cudaStream_t st) {
+                  void* vnew, int tiled, const int* lead, const int* order, const int* run_mask,
+                  int run_value, int N, int Hq, int Hv, long long T_rows, float scale,
+                  SeqLayout lay, cudaStream_t st) {
   using namespace fwdtc;
   CUtensorMap mq, mk, mv, ma, mh, mvn, mo;
   int rc;
@@ -907,6 +913,8 @@ int launch_fwd_tc(const void* q, const void* k, const void* v, const void* A, co
   p.tiled = tiled;
   p.lead = lead;
   p.order = order;
+  p.run_mask = run_mask;
+  p.run_value = run_value;
   p.g = g; p.beta = beta; p.beta_is_f32 = beta_is_f32; p.h0 = h0; p.ht = ht;
   p.o = (bf16*)o; p.h = (bf16*)h; p.vnew = (bf16*)vnew;
   p.N = N; p.Hq = Hq; p.Hv = Hv; p.T_rows = T_rows; p.scale = scale; p.lay = lay;

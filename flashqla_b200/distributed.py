@@ -31,6 +31,37 @@ from . import cp, ops
 from .api import chunk_gated_delta_rule_bwd, run_forward
 from .ops import CHUNK_SIZE
 
+# True (K = V = 128, at least three segments per shard): the recurrence kernels of a T-sharded
+# call run in two launches.  The segments that can start from a zero state by themselves run at
+# once on a side stream; this rank's summary, the all-gather and the chains run beside them, and
+# only the edge segment (plus any head whose gates do not let the past die out) waits for the
+# exchanged state.  False: everything waits for the exchange.
+OVERLAP_EXCHANGE = True
+_side_streams: dict = {}
+
+
+def _side_stream(device) -> torch.cuda.Stream:
+    key = str(device)
+    if key not in _side_streams:
+        _side_streams[key] = torch.cuda.Stream(device=device)
+    return _side_streams[key]
+
+
+def _two_phase_plan(k, Hv: int, short: str):
+    import flash_qla.ops.gated_delta_rule.chunk as chunk_mod
+
+    if not (OVERLAP_EXCHANGE and cp.LEAD_IN and chunk_mod._tiles_ok(k.shape[-1])):
+        return None
+    return cp.shard_plan(k.shape[1], Hv, k.device, short)
+
+
+def _wait_mask(any_fb, n_seg: int, edge: int):
+    """int32 ``[n_seg, Hv]``: 1 where a (segment, head) needs the exchanged state (the edge
+    segment, and every segment of a head that falls back), 0 where it starts by itself."""
+    mask = any_fb.expand(n_seg, -1).contiguous()
+    mask[edge] = 1
+    return mask
+
 
 def shard_heads(q, k, v, g, beta, rank: int, world: int, initial_state=None):
     """Slice of a full problem owned by ``rank`` under value-head sharding (the matching q/k
@@ -151,13 +182,44 @@ def fwd_tsharded(q, k, v, g, beta, scale=None, initial_state=None, output_final_
     world = dist.get_world_size(group)
     g32 = g if g.dtype == torch.float32 else g.float()
     g_cum, A = ops.kkt_solve(k, beta, g32.contiguous(), None, raw_gate=True)
-    local, M, fallback = _local_summary_fwd(k, v, A, g_cum, beta, scale)
     h0 = None if initial_state is None else initial_state.float().contiguous()
-    start = exchange_forward(local, M, fallback, h0, group)
-    res, cache = run_forward(q, k, v, A, g_cum, beta, scale, start,
-                             ops.SeqTables(1, q.shape[1], None), output_final_state=True,
-                             enable_fwd_cp_cache=for_backward)
-    o, ht = res["o"], res["ht"]
+    plan = _two_phase_plan(k, v.shape[2], "first")
+    if plan is None:
+        local, M, fallback = _local_summary_fwd(k, v, A, g_cum, beta, scale)
+        start = exchange_forward(local, M, fallback, h0, group)
+        res, cache = run_forward(q, k, v, A, g_cum, beta, scale, start,
+                                 ops.SeqTables(1, q.shape[1], None), output_final_state=True,
+                                 enable_fwd_cp_cache=for_backward)
+        o, ht = res["o"], res["ht"]
+    else:
+        seg = plan.seg_tables
+        # nothing here depends on another rank: the scan, the exact local passes of heads that
+        # fall back (they return at once elsewhere), and the recurrence of every (segment, head)
+        # that leads in by itself
+        _, fallback, lead, exact_warm, any_fb = ops.segment_scan(
+            g_cum, seg.cu, plan.seg_begin, cp.THRESHOLD, from_start=False)
+        waits = _wait_mask(any_fb, plan.n_seg, 0)
+        exact = ops.fwd_seq(None, k, v, A, g_cum, beta, scale, None, output_o=False,
+                            output_final_state=True, output_m=True, warm_chunks=exact_warm,
+                            m_mask=fallback, tables=seg)
+        tiles = dict(output_h=True, output_vnew=True, operand_tiles=True) if for_backward else {}
+        out = ops.fwd_seq_outputs(k, v, seg, output_final_state=True, **tiles)
+        main, side = torch.cuda.current_stream(k.device), _side_stream(k.device)
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            ops.fwd_seq(q, k, v, A, g_cum, beta, scale, None, tables=seg, lead_chunks=lead,
+                        run_mask=waits, run_value=0, out=out, operand_tiles=for_backward)
+        # beside it: this rank's summary, the collective, the chain over the ranks and (for heads
+        # that fall back) over this rank's segments, then the (segment, head) pairs that waited
+        local, M, fb_shard = _local_summary_fwd(k, v, A, g_cum, beta, scale)
+        start = exchange_forward(local, M, fb_shard, h0, group)
+        seg_h0 = ops.merge_states(exact["ht"], exact["M"], fallback, start, plan.seg_begin,
+                                  reverse=False, any_fallback=any_fb)
+        ops.fwd_seq(q, k, v, A, g_cum, beta, scale, seg_h0, tables=seg, lead_chunks=lead,
+                    run_mask=waits, run_value=1, out=out, operand_tiles=for_backward)
+        main.wait_stream(side)
+        o, ht = out["o"], out["ht"][plan.n_seg - 1:plan.n_seg]
+        cache = (None, out["h"], out["vnew"], None) if for_backward else None
     final_state = None
     if output_final_state:
         final_state = ht.clone()
@@ -174,6 +236,23 @@ def bwd_tsharded(q, k, v, g_cum, beta, A, do, dht=None, scale=None, saved=None, 
     if scale is None:
         scale = k.shape[-1] ** -0.5
     start, _, cache = saved
+    have_tiles = cache is not None and cache[1] is not None and cache[2] is not None
+    plan = _two_phase_plan(k, v.shape[2], "last") if have_tiles else None
+    if plan is not None:
+        return _bwd_two_phase(plan, q, k, v, g_cum, beta, A, do, dht, scale, cache, group)
+    local, M, fallback = _local_summary_bwd(q, k, v, A, g_cum, beta, do, scale)
+    dht32 = None if dht is None else dht.float().contiguous()
+    end = exchange_backward(local, M, fallback, dht32, group)
+    dq, dk, dv, db, dg, dh0 = chunk_gated_delta_rule_bwd(q, k, v, g_cum, beta, A, do, end, scale,
+                                                         start, None, cp_cache=cache)
+    dh0 = dh0.clone()
+    dist.broadcast(dh0, src=dist.get_global_rank(group, 0) if group else 0, group=group)
+    return dq, dk, dv, db, dg, dh0
+
+
+def _local_summary_bwd(q, k, v, A, g_cum, beta, do, scale):
+    """(gradient entering the shard from a zero end gradient, M, fallback flag) of this rank's
+    whole shard, shapes [1,Hv,D,D] / [1,Hv]."""
     T = k.shape[1]
     seg_cu = _const_i32((0, T), k.device)
     tables = ops.SeqTables(1, T, seg_cu)
@@ -183,10 +262,43 @@ def bwd_tsharded(q, k, v, g_cum, beta, A, do, dht=None, scale=None, saved=None, 
     # the exact transition matrix of this shard is needed wherever the gradient survives it
     M = ops.fwd_seq(None, k, v, A, g_cum, beta, scale, None, output_o=False, output_m=True,
                     m_mask=fallback, tables=tables)["M"]
+    return local, M, fallback
+
+
+def _bwd_two_phase(plan, q, k, v, g_cum, beta, A, do, dht, scale, cache, group):
+    """Backward of a T-sharded sequence with the reverse recurrence in two launches (see
+    ``OVERLAP_EXCHANGE``); the forward's state and v_new tiles are at hand."""
+    import flash_qla.ops.gated_delta_rule.chunk as chunk_mod
+
+    in_dtype, beta_dtype = q.dtype, beta.dtype
+    Hq = k.shape[2]
+    seg = plan.seg_tables
+    last = plan.n_seg - 1
+    _, fallback, lead, exact_warm, any_fb = ops.segment_scan(
+        g_cum, seg.cu, plan.seg_begin, cp.THRESHOLD, from_start=True)
+    waits = _wait_mask(any_fb, plan.n_seg, last)
+    local_e = ops.bwd_dh(q, k, A, g_cum, beta, do, scale, None, output_dh=False, output_du=False,
+                         output_dh0=True, warm_chunks=exact_warm, tables=seg)["dh0"]
+    m_e = ops.fwd_seq(None, k, v, A, g_cum, beta, scale, None, output_o=False, output_m=True,
+                      m_mask=fallback, tables=seg)["M"]
+    out = ops.bwd_dh_outputs(k, do, seg, operand_tiles=True)
+    main, side = torch.cuda.current_stream(k.device), _side_stream(k.device)
+    side.wait_stream(main)
+    with torch.cuda.stream(side):
+        ops.bwd_dh(q, k, A, g_cum, beta, do, scale, None, tables=seg, operand_tiles=True,
+                   lead_chunks=lead, run_mask=waits, run_value=0, out=out)
+    local, M, fb_shard = _local_summary_bwd(q, k, v, A, g_cum, beta, do, scale)
     dht32 = None if dht is None else dht.float().contiguous()
-    end = exchange_backward(local, M, fallback, dht32, group)
-    dq, dk, dv, db, dg, dh0 = chunk_gated_delta_rule_bwd(q, k, v, g_cum, beta, A, do, end, scale,
-                                                         start, None, cp_cache=cache)
-    dh0 = dh0.clone()
+    end = exchange_backward(local, M, fb_shard, dht32, group)
+    seg_dht = ops.merge_states(local_e, m_e, fallback, end, plan.seg_begin, reverse=True,
+                               any_fallback=any_fb)
+    ops.bwd_dh(q, k, A, g_cum, beta, do, scale, seg_dht, tables=seg, operand_tiles=True,
+               lead_chunks=lead, run_mask=waits, run_value=1, out=out)
+    main.wait_stream(side)
+    dq, dk, dv, db, dg = ops.bwd_main(q, k, v, cache[2], A, g_cum, beta, do, out["du"], cache[1],
+                                      out["dh"], scale, tables=seg, operand_tiles=True)
+    dq, dk, dv, db, dg = chunk_mod.finish_backward(dq, dk, dv, db, dg, Hq, beta_dtype, in_dtype,
+                                                   None)
+    dh0 = out["dh0"][0:1].clone()
     dist.broadcast(dh0, src=dist.get_global_rank(group, 0) if group else 0, group=group)
     return dq, dk, dv, db, dg, dh0

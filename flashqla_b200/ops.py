@@ -176,27 +176,13 @@ def kkt_solve(k, b, g_cum, cu_seqlens=None, chunk_size: int = CHUNK_SIZE, raw_ga
     return (g_out, A) if raw_gate else A
 
 
-@on_tensor_device
-def fwd_seq(q, k, v, a, g_cum, b, scale, initial_state=None, *, output_final_state=False,
-            output_o=True, output_h=False, output_vnew=False, output_m=False,
-            warm_chunks=None, m_mask=None, cu_seqlens=None, tables: SeqTables | None = None,
-            operand_tiles: bool = False, lead_chunks=None):
-    """Sequential forward recurrence.  Returns a dict with the requested outputs among
-    ``o, h, vnew, ht, M`` (reference: ``blackwell/fused_fwd.py:775-915`` and
-    ``blackwell/prepare_h.py:669-784``).  With ``operand_tiles`` (K = V = 128 only) ``h`` comes
-    out as ``[chunks, Hv, V, K]`` and ``vnew`` as ``[chunks, Hv, V, 64]``: the layouts
-    ``bwd_main(..., operand_tiles=True)`` reads as tensor-core operands.  ``lead_chunks``
-    (int32 ``[N, Hv]``, K = V = 128): per (segment, head) the number of chunks before the segment
-    to walk first, state-only, from a zero state (see ``segment_scan``)."""
-    _require_cuda(k, v, a, g_cum, b)
-    _check_bf16(q=q, k=k, v=v, a=a)
-    B, T, Hq, D = k.shape
-    Hv = v.shape[2]
-    tb = tables or SeqTables(B, T, cu_seqlens)
-    dev = k.device
+def fwd_seq_outputs(k, v, tb: SeqTables, output_o=True, output_h=False, output_vnew=False,
+                    output_final_state=False, output_m=False, operand_tiles=False) -> dict:
+    """The output tensors of ``fwd_seq`` (allocated on the current stream), for callers that
+    fill them with more than one launch (``out=``)."""
+    D, Hv, dev = k.shape[-1], v.shape[2], k.device
     out = {}
     if output_o:
-        assert q is not None
         out["o"] = torch.empty_like(v)
     if output_h:
         out["h"] = torch.empty(tb.num_chunks, Hv, D, D, dtype=k.dtype, device=dev)
@@ -207,6 +193,34 @@ def fwd_seq(q, k, v, a, g_cum, b, scale, initial_state=None, *, output_final_sta
         out["ht"] = torch.empty(tb.N, Hv, D, D, dtype=torch.float32, device=dev)
     if output_m:
         out["M"] = torch.empty(tb.N, Hv, D, D, dtype=torch.float32, device=dev)
+    return out
+
+
+@on_tensor_device
+def fwd_seq(q, k, v, a, g_cum, b, scale, initial_state=None, *, output_final_state=False,
+            output_o=True, output_h=False, output_vnew=False, output_m=False,
+            warm_chunks=None, m_mask=None, cu_seqlens=None, tables: SeqTables | None = None,
+            operand_tiles: bool = False, lead_chunks=None, run_mask=None, run_value: int = 1,
+            out: dict | None = None):
+    """Sequential forward recurrence.  Returns a dict with the requested outputs among
+    ``o, h, vnew, ht, M`` (reference: ``blackwell/fused_fwd.py:775-915`` and
+    ``blackwell/prepare_h.py:669-784``).  With ``operand_tiles`` (K = V = 128 only) ``h`` comes
+    out as ``[chunks, Hv, V, K]`` and ``vnew`` as ``[chunks, Hv, V, 64]``: the layouts
+    ``bwd_main(..., operand_tiles=True)`` reads as tensor-core operands.  ``lead_chunks``
+    (int32 ``[N, Hv]``, K = V = 128): per (segment, head) the number of chunks before the segment
+    to walk first, state-only, from a zero state (see ``segment_scan``).  ``run_mask``
+    (int32 ``[N, Hv]``) with ``run_value``: only the pairs whose entry equals ``run_value`` are
+    walked; with ``out`` (the dict a first call returned) a second call with the other value
+    fills the rest of the same tensors."""
+    _require_cuda(k, v, a, g_cum, b)
+    _check_bf16(q=q, k=k, v=v, a=a)
+    B, T, Hq, D = k.shape
+    Hv = v.shape[2]
+    tb = tables or SeqTables(B, T, cu_seqlens)
+    if out is None:
+        assert q is not None or not output_o
+        out = fwd_seq_outputs(k, v, tb, output_o, output_h, output_vnew, output_final_state,
+                              output_m, operand_tiles)
     if initial_state is not None:
         assert initial_state.dtype == torch.float32 and initial_state.is_contiguous()
         assert tuple(initial_state.shape) == (tb.N, Hv, D, D), (
@@ -216,27 +230,16 @@ def fwd_seq(q, k, v, a, g_cum, b, scale, initial_state=None, *, output_final_sta
         _ptr(q) if output_o else None, _ptr(k), _ptr(v), _ptr(a), _ptr(g_cum), _ptr(b),
         _beta_flag(b), _ptr(initial_state), _ptr(out.get("ht")), _ptr(out.get("o")),
         _ptr(out.get("h")), _ptr(out.get("vnew")), _ptr(out.get("M")), _ptr(warm_chunks),
-        _ptr(m_mask), _ptr(lead_chunks), _ptr(tb.order), tb.B, tb.T, Hq, Hv, D, float(scale), cu,
-        offs, is64, N, int(operand_tiles), _stream(k))
+        _ptr(m_mask), _ptr(lead_chunks), _ptr(tb.order), _ptr(run_mask), int(run_value), tb.B,
+        tb.T, Hq, Hv, D, float(scale), cu, offs, is64, N, int(operand_tiles), _stream(k))
     _lib.check(st, "fwd_seq")
     return out
 
 
-@on_tensor_device
-def bwd_dh(q, k, a, g_cum, b, do, scale, dht=None, *, output_dh=True, output_du=True,
-           output_dh0=True, warm_chunks=None, lead_chunks=None, cu_seqlens=None,
-           tables: SeqTables | None = None, operand_tiles: bool = False):
-    """Reverse recurrence of the state gradient; returns a dict with ``dh, du, dh0``
-    (reference: ``blackwell/cp_bwd.py:592-701`` and the dS chain of ``blackwell/fused_bwd.py``).
-    ``operand_tiles``: ``dh`` as ``[chunks, Hv, V, K]``, ``du`` as ``[chunks, Hv, V, 64]``.
-    ``lead_chunks`` (``[N, Hv]`` int32, segments of a split plan): segment ``n`` starts that many
-    chunks after its end from a zero gradient instead of taking ``dht[n]``."""
-    _require_cuda(q, k, a, g_cum, b, do)
-    _check_bf16(q=q, k=k, a=a, do=do)
-    B, T, Hq, D = k.shape
-    Hv = do.shape[2]
-    tb = tables or SeqTables(B, T, cu_seqlens)
-    dev = k.device
+def bwd_dh_outputs(k, do, tb: SeqTables, output_dh=True, output_du=True, output_dh0=True,
+                   operand_tiles=False) -> dict:
+    """The output tensors of ``bwd_dh`` (allocated on the current stream), see ``out=``."""
+    D, Hv, dev = k.shape[-1], do.shape[2], k.device
     out = {}
     if output_dh:
         out["dh"] = torch.empty(tb.num_chunks, Hv, D, D, dtype=k.dtype, device=dev)
@@ -245,6 +248,27 @@ def bwd_dh(q, k, a, g_cum, b, do, scale, dht=None, *, output_dh=True, output_du=
                      if operand_tiles else torch.empty_like(do))
     if output_dh0:
         out["dh0"] = torch.empty(tb.N, Hv, D, D, dtype=torch.float32, device=dev)
+    return out
+
+
+@on_tensor_device
+def bwd_dh(q, k, a, g_cum, b, do, scale, dht=None, *, output_dh=True, output_du=True,
+           output_dh0=True, warm_chunks=None, lead_chunks=None, cu_seqlens=None,
+           tables: SeqTables | None = None, operand_tiles: bool = False, run_mask=None,
+           run_value: int = 1, out: dict | None = None):
+    """Reverse recurrence of the state gradient; returns a dict with ``dh, du, dh0``
+    (reference: ``blackwell/cp_bwd.py:592-701`` and the dS chain of ``blackwell/fused_bwd.py``).
+    ``operand_tiles``: ``dh`` as ``[chunks, Hv, V, K]``, ``du`` as ``[chunks, Hv, V, 64]``.
+    ``lead_chunks`` (``[N, Hv]`` int32, segments of a split plan): segment ``n`` starts that many
+    chunks after its end from a zero gradient instead of taking ``dht[n]``.  ``run_mask``,
+    ``run_value``, ``out``: as for ``fwd_seq``."""
+    _require_cuda(q, k, a, g_cum, b, do)
+    _check_bf16(q=q, k=k, a=a, do=do)
+    B, T, Hq, D = k.shape
+    Hv = do.shape[2]
+    tb = tables or SeqTables(B, T, cu_seqlens)
+    if out is None:
+        out = bwd_dh_outputs(k, do, tb, output_dh, output_du, output_dh0, operand_tiles)
     if dht is not None:
         assert dht.dtype == torch.float32 and dht.is_contiguous()
         assert tuple(dht.shape) == (tb.N, Hv, D, D)
@@ -252,7 +276,7 @@ def bwd_dh(q, k, a, g_cum, b, do, scale, dht=None, *, output_dh=True, output_du=
     st = _lib.load().fqla_bwd_dh(
         _ptr(q), _ptr(k), _ptr(a), _ptr(g_cum), _ptr(b), _beta_flag(b), _ptr(do), _ptr(dht),
         _ptr(out.get("dh")), _ptr(out.get("du")), _ptr(out.get("dh0")), _ptr(warm_chunks),
-        _ptr(lead_chunks), _ptr(tb.order), tb.B, tb.T, Hq, Hv, D, float(scale), cu, offs, is64, N, int(operand_tiles),
+        _ptr(lead_chunks), _ptr(tb.order), _ptr(run_mask), int(run_value), tb.B, tb.T, Hq, Hv, D, float(scale), cu, offs, is64, N, int(operand_tiles),
         _stream(k))
     _lib.check(st, "bwd_dh")
     return out

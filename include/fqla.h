@@ -78,14 +78,17 @@ int fqla_kkt_solve(const void* k, const void* beta, int beta_is_f32, const float
  * seq_order [N] (int32, optional; a permutation of 0..N-1): the CTAs of block index i / Hv walk
  * sequence seq_order[i].  Blocks start in index order, so listing the longest sequences first
  * shortens the tail of a ragged batch; the results do not depend on it.
+ * run_mask [N,Hv] (int32, optional) with run_value: only the (sequence, head) pairs with
+ * run_mask[n,hv] == run_value are walked; nothing of the others is read or written, so two calls
+ * with complementary values can fill one set of output buffers at different times.
  * Replaces fused_gdr_fwd (blackwell/fused_fwd.py:775-915) and fused_gdr_h
  * (blackwell/prepare_h.py:669-784). */
 int fqla_fwd_seq(const void* q, const void* k, const void* v, const void* A, const float* g_cum,
                  const void* beta, int beta_is_f32, const float* h0, float* ht, void* o, void* h,
                  void* vnew, float* M, const int* warm_chunks, const int* m_mask,
-                 const int* lead_chunks, const int* seq_order, int B, int T, int Hq, int Hv, int D,
-                 float scale, const void* cu_seqlens, const void* chunk_offsets, int idx_is64,
-                 int N, int operand_tiles, void* stream);
+                 const int* lead_chunks, const int* seq_order, const int* run_mask, int run_value,
+                 int B, int T, int Hq, int Hv, int D, float scale, const void* cu_seqlens,
+                 const void* chunk_offsets, int idx_is64, int N, int operand_tiles, void* stream);
 
 /* Sequential reverse recurrence of the state gradient.  Optional outputs: per-chunk dh, du (the
  * gradient of vnew), dh0.  warm_chunks (optional, dh0-only calls): walk only the first
@@ -95,13 +98,15 @@ int fqla_fwd_seq(const void* q, const void* k, const void* v, const void* A, con
  * (optional, [N, Hv] int32, K = V = 128, not with warm_chunks): the mirror image of
  * fqla_fwd_seq's lead_chunks; sequence n is a segment of a longer sequence, whose following rows
  * belong to segment n + 1, and starts lead_chunks[n,hv] chunks after its end from a zero
- * gradient (dht is ignored for it) instead of being handed one.  seq_order: as for fqla_fwd_seq.
+ * gradient (dht is ignored for it) instead of being handed one.  seq_order, run_mask,
+ * run_value: as for fqla_fwd_seq.
  * Replaces fused_gdr_dh_ws (blackwell/cp_bwd.py:592-701) and the dS chain of fused_gdr_bwd
  * (blackwell/fused_bwd.py:336-474). */
 int fqla_bwd_dh(const void* q, const void* k, const void* A, const float* g_cum, const void* beta,
                 int beta_is_f32, const void* dO, const float* dht, void* dh, void* du, float* dh0,
-                const int* warm_chunks, const int* lead_chunks, const int* seq_order, int B, int T,
-                int Hq, int Hv, int D, float scale, const void* cu_seqlens, const void* chunk_offsets, int idx_is64, int N,
+                const int* warm_chunks, const int* lead_chunks, const int* seq_order,
+                const int* run_mask, int run_value, int B, int T, int Hq, int Hv, int D,
+                float scale, const void* cu_seqlens, const void* chunk_offsets, int idx_is64, int N,
                 int operand_tiles, void* stream);
 
 /* Chunk-parallel backward: dq, dk (per VALUE head, [B,T,Hv,D] bf16), dv, dbeta and the

@@ -407,6 +407,36 @@ def test_lead_out_over_a_partial_last_chunk_is_exact(tiles):
         assert torch.equal(part["du"][:, :T], full["du"][:, :T])
 
 
+def test_two_launches_with_complementary_run_masks_equal_one_launch():
+    """``run_mask`` / ``run_value``: a launch walks only the (sequence, head) pairs selected; two
+    launches with the two values fill one set of outputs with the bits of a single launch."""
+    from flashqla_b200 import ops
+
+    d = _inputs(1500, 2, 4, seed=77, cu=[0, 70, 700, 701, 1100, 1500])
+    tables, g_cum, A = _prep(d)
+    scale = 128 ** -0.5
+    mask = (torch.arange(5 * 4, device=DEV).reshape(5, 4) % 3 == 0).to(torch.int32)
+    kw = dict(output_final_state=True, output_h=True, output_vnew=True, tables=tables,
+              operand_tiles=True)
+    one = ops.fwd_seq(d["q"], d["k"], d["v"], A, g_cum, d["beta"], scale, d["h0"], **kw)
+    out = ops.fwd_seq_outputs(d["k"], d["v"], tables, True, True, True, True, False, True)
+    for t in out.values():
+        t.fill_(float("nan"))
+    for value in (1, 0):
+        ops.fwd_seq(d["q"], d["k"], d["v"], A, g_cum, d["beta"], scale, d["h0"], run_mask=mask,
+                    run_value=value, out=out, **kw)
+    for name in ("o", "ht", "h", "vnew"):
+        assert torch.equal(out[name][..., :].nan_to_num(0.0), one[name].nan_to_num(0.0)), name
+    bone = ops.bwd_dh(d["q"], d["k"], A, g_cum, d["beta"], d["do"], scale, d["dht"], tables=tables,
+                      operand_tiles=True)
+    bout = ops.bwd_dh_outputs(d["k"], d["do"], tables, operand_tiles=True)
+    for value in (0, 1):
+        ops.bwd_dh(d["q"], d["k"], A, g_cum, d["beta"], d["do"], scale, d["dht"], tables=tables,
+                   operand_tiles=True, run_mask=mask, run_value=value, out=bout)
+    for name in ("dh", "du", "dh0"):
+        assert torch.equal(bout[name], bone[name]), name
+
+
 def test_longest_first_block_order_does_not_change_results():
     """Packed batches hand their sequences to the sequential kernels longest first (a block-index
     -> sequence table); the outputs must be the same bits as in index order."""
