@@ -23,7 +23,7 @@ SIGNATURES = {
     "fqla_bwd_main": [P] * 7 + [I] + [P] * 9 + [I, I, I, I, I, F, P, P, P, I, LL, I, P],
     "fqla_group_reduce": [P, P, LL, I, I, I, P],
     "fqla_warmup_scan": [P, I, I, P, I, I, F, I, P, P, P, P],
-    "fqla_merge_states": [P, P, P, P, P, P, P, I, I, I, I, P],
+    "fqla_merge_states": [P, P, P, P, P, P, P, I, I, I, I, LL, P],
     "fqla_segment_scan": [P, I, I, P, I, P, I, F, I, P, P, P, P, P, P],
     "fqla_device_status": [P, I],
     "fqla_selftest_wait_timeout": [I, P],

@@ -122,7 +122,11 @@ __global__ void __launch_bounds__(D) merge_kernel(const float* __restrict__ loca
                                                   const float* __restrict__ raw,
                                                   const int* __restrict__ seg_begin,
                                                   const int* __restrict__ any_fb,
-                                                  float* __restrict__ out, int Hv, int reverse) {
+                                                  float* __restrict__ out, int Hv, int reverse,
+                                                  long long seg_stride, long long use_stride) {
+  // seg_stride / use_stride: distance in 4-byte words between the entries of consecutive
+  // segments in local and M / in use_m (packed tensors, or the records of a gathered buffer);
+  // raw and out are always packed
   constexpr int BV = 32, BK = 32, LDC = BV + 1;
   // all global traffic is one 128-byte row segment per warp instruction; the padded row stride
   // keeps both the row-wise (warp = row) and the thread-owns-a-row accesses free of bank conflicts
@@ -136,6 +140,9 @@ __global__ void __launch_bounds__(D) merge_kernel(const float* __restrict__ loca
   if (s1 <= s0) return;
   auto state = [&](const float* base, int seg) {
     return base + (((long long)seg * Hv + hv) * D) * D;
+  };
+  auto strided = [&](const float* base, int seg) {
+    return base + (long long)seg * seg_stride + ((long long)hv * D) * D;
   };
   if (any_fb && any_fb[r * Hv + hv] == 0) {
     // no chain for this (sequence, head): the recurrence kernel leads in by itself; only the
@@ -161,10 +168,10 @@ __global__ void __launch_bounds__(D) merge_kernel(const float* __restrict__ loca
   int pre_m = 0;
   auto prefetch = [&](int step) {
     const int i = reverse ? s1 - 1 - step : s0 + step;
-    const float* loc = state(local, i);
+    const float* loc = strided(local, i);
 #pragma unroll
     for (int t = 0; t < RPW; ++t) pre[t] = loc[(long long)(warp + t * (D / 32)) * D + v0 + lane];
-    pre_m = use_m == nullptr ? 1 : use_m[i * Hv + hv];
+    pre_m = use_m == nullptr ? 1 : use_m[(long long)i * use_stride + hv];
   };
   if (n > 1) prefetch(0);
   for (int step = 0; step < n; ++step) {
@@ -181,7 +188,7 @@ __global__ void __launch_bounds__(D) merge_kernel(const float* __restrict__ loca
 #pragma unroll
     for (int j = 0; j < BV; ++j) acc[j] = panel[a * LDC + j];
     if (with_m) {
-      const float* m = state(M, i);
+      const float* m = strided(M, i);
       for (int b0 = 0; b0 < D; b0 += BK) {
         __syncthreads();  // the previous contents of the panel have been consumed
         if (!reverse) {
@@ -240,16 +247,19 @@ extern "C" int fqla_segment_scan(const float* g_cum, int T, int Hv, const void* 
 
 extern "C" int fqla_merge_states(const float* local, const float* M, const int* use_m,
                                  const float* raw, const int* seg_begin, const int* any_fb,
-                                 float* out, int n_raw, int Hv, int D, int reverse, void* stream) {
-  if (!local || !M || !seg_begin || !out || Hv <= 0) return FQLA_ERR_INVALID_ARG;
+                                 float* out, int n_raw, int Hv, int D, int reverse,
+                                 long long seg_stride, void* stream) {
+  if (!local || !M || !seg_begin || !out || Hv <= 0 || seg_stride < 0) return FQLA_ERR_INVALID_ARG;
   if (n_raw <= 0) return FQLA_OK;
   cudaStream_t st = (cudaStream_t)stream;
   if (D == 128) {
-    merge_kernel<128><<<dim3(128 / 32, Hv, n_raw), 128, 0, st>>>(local, M, use_m, raw, seg_begin,
-                                                                  any_fb, out, Hv, reverse);
+    merge_kernel<128><<<dim3(128 / 32, Hv, n_raw), 128, 0, st>>>(
+        local, M, use_m, raw, seg_begin, any_fb, out, Hv, reverse,
+        seg_stride ? seg_stride : (long long)Hv * D * D, seg_stride ? seg_stride : Hv);
   } else if (D == 64) {
-    merge_kernel<64><<<dim3(64 / 32, Hv, n_raw), 64, 0, st>>>(local, M, use_m, raw, seg_begin,
-                                                                any_fb, out, Hv, reverse);
+    merge_kernel<64><<<dim3(64 / 32, Hv, n_raw), 64, 0, st>>>(
+        local, M, use_m, raw, seg_begin, any_fb, out, Hv, reverse,
+        seg_stride ? seg_stride : (long long)Hv * D * D, seg_stride ? seg_stride : Hv);
   } else {
     return FQLA_ERR_UNSUPPORTED_DIM;
   }

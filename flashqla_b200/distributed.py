@@ -12,10 +12,15 @@ benchmark rows only emulate the head count one tensor-parallel shard would see):
   shard; one all-gather hands every rank all boundary summaries (``[Hv,K,V]`` + ``[Hv,K,K]`` fp32
   per rank, packed with the optional edge state into one record of about 1.5 MiB at Hv = 8 and
   moved by ONE collective per direction), every rank chains them locally
-  (``start[r+1] = local[r] + M[r] start[r]``) and then runs the ordinary forward on its tokens
-  with its start state.  The backward pass mirrors this for the state gradient with ``M^T`` in
-  the other direction.  The payload always lands in the receiving GPU's own memory (the
-  all-gather output) before any kernel reads it.
+  (``start[r+1] = local[r] + M[r] start[r]``; the step after the last rank is the final state of
+  the sequence, so no second collective is needed for it) and then runs the ordinary forward on
+  its tokens with its start state.  The backward pass mirrors this for the state gradient with
+  ``M^T`` in the other direction.  The payload always lands in the receiving GPU's own memory
+  (the all-gather output) before any kernel reads it, and the chain reads it where it landed.
+  A shard is itself cut into segments (one CTA per SM), and all but the edge segment start from
+  a zero state a few chunks early: those run on a side stream while the summary, the collective
+  and the chains are in flight, and only the edge segment waits for the exchanged state
+  (``OVERLAP_EXCHANGE``).
 
 The collective is issued through ``torch.distributed`` (NCCL over NVLink on GPUs, gloo in the
 CPU tests of the host logic); a rank that never joins surfaces as the process group's timeout
@@ -98,46 +103,60 @@ def _const_i32(values: tuple, device) -> torch.Tensor:
     return _const_cache[key]
 
 
-def chain_boundary_states(local, M, use_m, first, rank: int, reverse: bool = False,
-                          merge_fn=None):
-    """Start state (or, reversed, end gradient) of ``rank`` from the gathered per-rank
-    summaries.  ``local``, ``M``: ``[R, Hv, D, D]`` fp32; ``use_m``: ``[R, Hv]`` int32;
-    ``first``: ``[1, Hv, D, D]`` state entering rank 0 (leaving rank R-1 when reversed) or None.
-    ``merge_fn`` defaults to the CUDA merge kernel; the CPU tests pass a torch stand-in."""
+def _record_views(rec, Hv: int, D: int):
+    """The four parts of one rank's record ``[local | M | edge state | flags]`` as views."""
+    n = Hv * D * D
+    return (rec[:n].view(1, Hv, D, D), rec[n:2 * n].view(1, Hv, D, D),
+            rec[2 * n:3 * n].view(1, Hv, D, D), rec[3 * n:].view(1, Hv))
+
+
+def _new_record(Hv: int, D: int, dtype, device):
+    """A zeroed record for this rank's contribution.  Callers let their kernels write ``local``
+    and ``M`` straight into its views; flags are stored as numbers (0.0 / 1.0) of ``dtype``."""
+    return torch.zeros(3 * Hv * D * D + Hv, dtype=dtype, device=device)
+
+
+def _exchange(rec, Hv: int, D: int, edge_rank: int, reverse: bool, group, merge_fn):
+    """One all-gather per direction, the same on every rank whatever its local arguments, and
+    the chain over the ranks' summaries.  Returns ``[R + 1, Hv, D, D]``:
+
+    * forward: entry ``r`` is the state entering rank ``r``'s tokens, entry ``R`` the final state
+      of the whole sequence;
+    * reverse: entry ``r + 1`` is the gradient of the state leaving rank ``r``'s tokens, entry 0
+      the gradient of the sequence's initial state.
+
+    The edge state (the sequence's initial state for the forward direction, the gradient of its
+    final state for the reverse one) is read from the record of ``edge_rank`` only, and an owner
+    that was given none sends zeros, which chain exactly like "no state".  The records are
+    gathered into one buffer with a spare record at the far end of the chain (never read: it
+    only gives the chain its last step), and the chain reads local, M and the flags where the
+    all-gather put them."""
+    world = dist.get_world_size(group)
     merge_fn = merge_fn or ops.merge_states
-    R = local.shape[0]
-    seg_begin = _const_i32((0, R), local.device)
-    chained = merge_fn(local, M, use_m, first, seg_begin, reverse)
-    return chained[rank:rank + 1].contiguous()
+    size, n = rec.numel(), Hv * D * D
+    flat = torch.empty((world + 1) * size, dtype=rec.dtype, device=rec.device)
+    shift = 1 if reverse else 0  # the record of rank r lands in row r + shift
+    dist.all_gather_into_tensor(flat[shift * size:(shift + world) * size], rec, group=group)
+    rows = flat.view(world + 1, size)
+    local = rows[:, :n].unflatten(1, (Hv, D, D))
+    M = rows[:, n:2 * n].unflatten(1, (Hv, D, D))
+    edge = rows[edge_rank + shift, 2 * n:3 * n].view(1, Hv, D, D)
+    use = rows[:, 3 * n:]
+    if use.is_cuda:
+        use = use.view(torch.int32)  # 0.0 is all-zero bits, 1.0 is not: the kernel tests for zero
+    return merge_fn(local, M, use, edge, _const_i32((0, world + 1), rec.device), reverse)
 
 
-def _exchange(local, M, use_m, edge_state, edge_rank: int, reverse: bool, group, merge_fn):
-    """One all-gather per direction, the same on every rank whatever its local arguments.
-
-    Every rank contributes one record ``[local | M | edge state | use_m]``; the edge state (the
-    sequence's initial state for the forward direction, the gradient of its final state for the
-    reverse one) is read from the record of ``edge_rank`` only, and an owner that was given none
-    sends zeros, which chain exactly like "no state".  So a caller may pass the state on the
-    owning rank only, on every rank, or nowhere: the collective sequence is identical in all
-    three cases."""
-    rank, world = dist.get_rank(group), dist.get_world_size(group)
+def _record_from(local, M, use_m, edge_state, is_owner: bool):
     Hv, D = local.shape[1], local.shape[2]
-    n_state = Hv * D * D
-    rec = torch.zeros(3 * n_state + Hv, dtype=local.dtype, device=local.device)
-    rec[:n_state] = local.reshape(-1)
-    rec[n_state:2 * n_state] = M.reshape(-1)
-    if edge_state is not None and rank == edge_rank:
-        rec[2 * n_state:3 * n_state] = edge_state.reshape(-1)
-    rec[3 * n_state:] = use_m.reshape(-1).to(local.dtype)
-    flat = torch.empty(world * rec.numel(), dtype=local.dtype, device=local.device)
-    dist.all_gather_into_tensor(flat, rec, group=group)
-    everything = flat.view(world, rec.numel())
-    all_local = everything[:, :n_state].reshape(world, Hv, D, D)
-    all_m = everything[:, n_state:2 * n_state].reshape(world, Hv, D, D)
-    edge = everything[edge_rank, 2 * n_state:3 * n_state].reshape(1, Hv, D, D)
-    all_use = everything[:, 3 * n_state:].to(torch.int32)
-    return chain_boundary_states(all_local.contiguous(), all_m.contiguous(), all_use.contiguous(),
-                                 edge.contiguous(), rank, reverse, merge_fn)
+    rec = _new_record(Hv, D, local.dtype, local.device)
+    r_local, r_m, r_edge, r_flags = _record_views(rec, Hv, D)
+    r_local.copy_(local)
+    r_m.copy_(M)
+    r_flags.copy_(use_m)
+    if edge_state is not None and is_owner:
+        r_edge.copy_(edge_state)
+    return rec
 
 
 def exchange_forward(local, M, use_m, initial_state, group=None, merge_fn=None):
@@ -145,26 +164,57 @@ def exchange_forward(local, M, use_m, initial_state, group=None, merge_fn=None):
     ``[1, Hv, D, D]``.  ``local``/``M``: ``[1, Hv, D, D]``; ``use_m``: ``[1, Hv]`` int32;
     ``initial_state`` is the sequence's initial state: it is taken from rank 0, other ranks may
     pass it too or pass None."""
-    return _exchange(local, M, use_m, initial_state, 0, False, group, merge_fn)
+    rank = dist.get_rank(group)
+    rec = _record_from(local, M, use_m, initial_state, rank == 0)
+    return _exchange(rec, local.shape[1], local.shape[2], 0, False, group, merge_fn)[rank:rank + 1]
 
 
 def exchange_backward(local, M, use_m, dht, group=None, merge_fn=None):
     """Mirror of ``exchange_forward`` for the state gradient: returns the gradient of the state
     leaving this rank's tokens.  ``dht`` is the gradient of the sequence's final state: it is
     taken from the last rank, other ranks may pass it too or pass None."""
-    return _exchange(local, M, use_m, dht, dist.get_world_size(group) - 1, True, group, merge_fn)
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    rec = _record_from(local, M, use_m, dht, rank == world - 1)
+    return _exchange(rec, local.shape[1], local.shape[2], world - 1, True, group,
+                     merge_fn)[rank + 1:rank + 2]
 
 
-def _local_summary_fwd(k, v, A, g_cum, beta, scale):
-    """(end state from zero, M, fallback flag) of this rank's whole shard, shapes [1,Hv,D,D]."""
-    T = k.shape[1]
+def _summary_record_fwd(k, v, A, g_cum, beta, scale, edge_state, is_owner: bool):
+    """This rank's forward record: the end state of its whole shard from a zero state, the exact
+    transition matrix M where the gates do not let the past die out inside the shard (flag), and
+    the sequence's initial state if this rank owns it.  The kernels write into the record."""
+    T, Hv, D = k.shape[1], v.shape[2], k.shape[-1]
+    rec = _new_record(Hv, D, torch.float32, k.device)
+    r_local, r_m, r_edge, r_flags = _record_views(rec, Hv, D)
     seg_cu = _const_i32((0, T), k.device)
     warm, fallback = ops.warmup_scan(g_cum, seg_cu, cp.THRESHOLD, from_start=False)
+    ops.fwd_seq(None, k, v, A, g_cum, beta, scale, None, output_o=False, warm_chunks=warm,
+                m_mask=fallback, tables=ops.SeqTables(1, T, seg_cu),
+                out={"ht": r_local, "M": r_m})
+    r_flags.copy_(fallback)
+    if edge_state is not None and is_owner:
+        r_edge.copy_(edge_state)
+    return rec
+
+
+def _summary_record_bwd(q, k, v, A, g_cum, beta, do, scale, edge_state, is_owner: bool):
+    """Mirror of ``_summary_record_fwd``: the gradient entering the shard from a zero end
+    gradient, M where the gradient survives the shard, and the gradient of the sequence's final
+    state if this rank owns it."""
+    T, Hv, D = k.shape[1], v.shape[2], k.shape[-1]
+    rec = _new_record(Hv, D, torch.float32, k.device)
+    r_local, r_m, r_edge, r_flags = _record_views(rec, Hv, D)
+    seg_cu = _const_i32((0, T), k.device)
     tables = ops.SeqTables(1, T, seg_cu)
-    res = ops.fwd_seq(None, k, v, A, g_cum, beta, scale, None, output_o=False,
-                      output_final_state=True, output_m=True, warm_chunks=warm, m_mask=fallback,
-                      tables=tables)
-    return res["ht"], res["M"], fallback
+    warm, fallback = ops.warmup_scan(g_cum, seg_cu, cp.THRESHOLD, from_start=True)
+    ops.bwd_dh(q, k, A, g_cum, beta, do, scale, None, warm_chunks=warm, tables=tables,
+               out={"dh0": r_local})
+    ops.fwd_seq(None, k, v, A, g_cum, beta, scale, None, output_o=False, m_mask=fallback,
+                tables=tables, out={"M": r_m})
+    r_flags.copy_(fallback)
+    if edge_state is not None and is_owner:
+        r_edge.copy_(edge_state)
+    return rec
 
 
 def fwd_tsharded(q, k, v, g, beta, scale=None, initial_state=None, output_final_state=True,
@@ -172,25 +222,28 @@ def fwd_tsharded(q, k, v, g, beta, scale=None, initial_state=None, output_final_
     """Forward of ONE sequence whose tokens are split evenly over the ranks of ``group``
     (this rank passes its own ``[1, T/R, ...]`` slice, a multiple of 64 tokens).  Returns
     ``(g_cum, A, o, final_state, saved)``; ``final_state`` is the sequence's final state on every
-    rank, ``saved`` carries what ``bwd_tsharded`` needs.  ``initial_state`` is read on rank 0 only
-    (other ranks may pass None); ``output_final_state`` and ``for_backward`` must be the same on
-    every rank.  With ``for_backward`` the forward keeps the per-chunk state and v_new tiles so
-    that ``bwd_tsharded`` skips its recomputation pass."""
+    rank (the last step of the chain over the gathered summaries, so it costs no second
+    collective), ``saved`` carries what ``bwd_tsharded`` needs.  ``initial_state`` is read on
+    rank 0 only (other ranks may pass None); ``for_backward`` must be the same on every rank.
+    With ``for_backward`` the forward keeps the per-chunk state and v_new tiles so that
+    ``bwd_tsharded`` skips its recomputation pass."""
     assert q.shape[0] == 1 and q.shape[1] % CHUNK_SIZE == 0, "T shard must be a chunk multiple"
     if scale is None:
         scale = k.shape[-1] ** -0.5
-    world = dist.get_world_size(group)
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    Hv, D = v.shape[2], k.shape[-1]
     g32 = g if g.dtype == torch.float32 else g.float()
     g_cum, A = ops.kkt_solve(k, beta, g32.contiguous(), None, raw_gate=True)
     h0 = None if initial_state is None else initial_state.float().contiguous()
-    plan = _two_phase_plan(k, v.shape[2], "first")
+    plan = _two_phase_plan(k, Hv, "first")
     if plan is None:
-        local, M, fallback = _local_summary_fwd(k, v, A, g_cum, beta, scale)
-        start = exchange_forward(local, M, fallback, h0, group)
+        rec = _summary_record_fwd(k, v, A, g_cum, beta, scale, h0, rank == 0)
+        chained = _exchange(rec, Hv, D, 0, False, group, None)
+        start = chained[rank:rank + 1]
         res, cache = run_forward(q, k, v, A, g_cum, beta, scale, start,
-                                 ops.SeqTables(1, q.shape[1], None), output_final_state=True,
+                                 ops.SeqTables(1, q.shape[1], None), output_final_state=False,
                                  enable_fwd_cp_cache=for_backward)
-        o, ht = res["o"], res["ht"]
+        o = res["o"]
     else:
         seg = plan.seg_tables
         # nothing here depends on another rank: the scan, the exact local passes of heads that
@@ -203,7 +256,7 @@ def fwd_tsharded(q, k, v, g, beta, scale=None, initial_state=None, output_final_
                             output_final_state=True, output_m=True, warm_chunks=exact_warm,
                             m_mask=fallback, tables=seg)
         tiles = dict(output_h=True, output_vnew=True, operand_tiles=True) if for_backward else {}
-        out = ops.fwd_seq_outputs(k, v, seg, output_final_state=True, **tiles)
+        out = ops.fwd_seq_outputs(k, v, seg, **tiles)
         main, side = torch.cuda.current_stream(k.device), _side_stream(k.device)
         side.wait_stream(main)
         with torch.cuda.stream(side):
@@ -211,69 +264,45 @@ def fwd_tsharded(q, k, v, g, beta, scale=None, initial_state=None, output_final_
                         run_mask=waits, run_value=0, out=out, operand_tiles=for_backward)
         # beside it: this rank's summary, the collective, the chain over the ranks and (for heads
         # that fall back) over this rank's segments, then the (segment, head) pairs that waited
-        local, M, fb_shard = _local_summary_fwd(k, v, A, g_cum, beta, scale)
-        start = exchange_forward(local, M, fb_shard, h0, group)
+        rec = _summary_record_fwd(k, v, A, g_cum, beta, scale, h0, rank == 0)
+        chained = _exchange(rec, Hv, D, 0, False, group, None)
+        start = chained[rank:rank + 1]
         seg_h0 = ops.merge_states(exact["ht"], exact["M"], fallback, start, plan.seg_begin,
                                   reverse=False, any_fallback=any_fb)
         ops.fwd_seq(q, k, v, A, g_cum, beta, scale, seg_h0, tables=seg, lead_chunks=lead,
                     run_mask=waits, run_value=1, out=out, operand_tiles=for_backward)
         main.wait_stream(side)
-        o, ht = out["o"], out["ht"][plan.n_seg - 1:plan.n_seg]
+        o = out["o"]
         cache = (None, out["h"], out["vnew"], None) if for_backward else None
-    final_state = None
-    if output_final_state:
-        final_state = ht.clone()
-        src = world - 1
-        dist.broadcast(final_state, src=dist.get_global_rank(group, src) if group else src,
-                       group=group)
-    return g_cum, A, o, final_state, (start, M, cache)
+    final_state = chained[world:world + 1] if output_final_state else None
+    return g_cum, A, o, final_state, (start, None, cache)
 
 
 def bwd_tsharded(q, k, v, g_cum, beta, A, do, dht=None, scale=None, saved=None, group=None):
     """Backward of a T-sharded sequence.  ``saved`` is the tuple returned by ``fwd_tsharded``.
     Returns ``(dq, dk, dv, db, dg, dh0)`` for this rank's tokens; ``dh0`` (gradient of the
-    sequence's initial state) is valid on every rank.  ``dht`` is read on the last rank only."""
+    sequence's initial state: the last step of the reverse chain) is valid on every rank.
+    ``dht`` is read on the last rank only."""
     if scale is None:
         scale = k.shape[-1] ** -0.5
     start, _, cache = saved
-    have_tiles = cache is not None and cache[1] is not None and cache[2] is not None
-    plan = _two_phase_plan(k, v.shape[2], "last") if have_tiles else None
-    if plan is not None:
-        return _bwd_two_phase(plan, q, k, v, g_cum, beta, A, do, dht, scale, cache, group)
-    local, M, fallback = _local_summary_bwd(q, k, v, A, g_cum, beta, do, scale)
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    Hv, D = v.shape[2], k.shape[-1]
     dht32 = None if dht is None else dht.float().contiguous()
-    end = exchange_backward(local, M, fallback, dht32, group)
-    dq, dk, dv, db, dg, dh0 = chunk_gated_delta_rule_bwd(q, k, v, g_cum, beta, A, do, end, scale,
-                                                         start, None, cp_cache=cache)
-    dh0 = dh0.clone()
-    dist.broadcast(dh0, src=dist.get_global_rank(group, 0) if group else 0, group=group)
-    return dq, dk, dv, db, dg, dh0
-
-
-def _local_summary_bwd(q, k, v, A, g_cum, beta, do, scale):
-    """(gradient entering the shard from a zero end gradient, M, fallback flag) of this rank's
-    whole shard, shapes [1,Hv,D,D] / [1,Hv]."""
-    T = k.shape[1]
-    seg_cu = _const_i32((0, T), k.device)
-    tables = ops.SeqTables(1, T, seg_cu)
-    warm, fallback = ops.warmup_scan(g_cum, seg_cu, cp.THRESHOLD, from_start=True)
-    local = ops.bwd_dh(q, k, A, g_cum, beta, do, scale, None, output_dh=False, output_du=False,
-                       output_dh0=True, warm_chunks=warm, tables=tables)["dh0"]
-    # the exact transition matrix of this shard is needed wherever the gradient survives it
-    M = ops.fwd_seq(None, k, v, A, g_cum, beta, scale, None, output_o=False, output_m=True,
-                    m_mask=fallback, tables=tables)["M"]
-    return local, M, fallback
-
-
-def _bwd_two_phase(plan, q, k, v, g_cum, beta, A, do, dht, scale, cache, group):
-    """Backward of a T-sharded sequence with the reverse recurrence in two launches (see
-    ``OVERLAP_EXCHANGE``); the forward's state and v_new tiles are at hand."""
+    have_tiles = cache is not None and cache[1] is not None and cache[2] is not None
+    plan = _two_phase_plan(k, Hv, "last") if have_tiles else None
+    if plan is None:
+        rec = _summary_record_bwd(q, k, v, A, g_cum, beta, do, scale, dht32, rank == world - 1)
+        chained = _exchange(rec, Hv, D, world - 1, True, group, None)
+        grads = chunk_gated_delta_rule_bwd(q, k, v, g_cum, beta, A, do,
+                                           chained[rank + 1:rank + 2], scale, start, None,
+                                           cp_cache=cache)
+        return grads[:5] + (chained[0:1],)
+    # the reverse recurrence in two launches (see OVERLAP_EXCHANGE); the forward's state and
+    # v_new tiles are at hand
     import flash_qla.ops.gated_delta_rule.chunk as chunk_mod
 
-    in_dtype, beta_dtype = q.dtype, beta.dtype
-    Hq = k.shape[2]
-    seg = plan.seg_tables
-    last = plan.n_seg - 1
+    seg, last = plan.seg_tables, plan.n_seg - 1
     _, fallback, lead, exact_warm, any_fb = ops.segment_scan(
         g_cum, seg.cu, plan.seg_begin, cp.THRESHOLD, from_start=True)
     waits = _wait_mask(any_fb, plan.n_seg, last)
@@ -281,24 +310,21 @@ def _bwd_two_phase(plan, q, k, v, g_cum, beta, A, do, dht, scale, cache, group):
                          output_dh0=True, warm_chunks=exact_warm, tables=seg)["dh0"]
     m_e = ops.fwd_seq(None, k, v, A, g_cum, beta, scale, None, output_o=False, output_m=True,
                       m_mask=fallback, tables=seg)["M"]
-    out = ops.bwd_dh_outputs(k, do, seg, operand_tiles=True)
+    out = ops.bwd_dh_outputs(k, do, seg, output_dh0=False, operand_tiles=True)
     main, side = torch.cuda.current_stream(k.device), _side_stream(k.device)
     side.wait_stream(main)
     with torch.cuda.stream(side):
         ops.bwd_dh(q, k, A, g_cum, beta, do, scale, None, tables=seg, operand_tiles=True,
                    lead_chunks=lead, run_mask=waits, run_value=0, out=out)
-    local, M, fb_shard = _local_summary_bwd(q, k, v, A, g_cum, beta, do, scale)
-    dht32 = None if dht is None else dht.float().contiguous()
-    end = exchange_backward(local, M, fb_shard, dht32, group)
-    seg_dht = ops.merge_states(local_e, m_e, fallback, end, plan.seg_begin, reverse=True,
-                               any_fallback=any_fb)
+    rec = _summary_record_bwd(q, k, v, A, g_cum, beta, do, scale, dht32, rank == world - 1)
+    chained = _exchange(rec, Hv, D, world - 1, True, group, None)
+    seg_dht = ops.merge_states(local_e, m_e, fallback, chained[rank + 1:rank + 2], plan.seg_begin,
+                               reverse=True, any_fallback=any_fb)
     ops.bwd_dh(q, k, A, g_cum, beta, do, scale, seg_dht, tables=seg, operand_tiles=True,
                lead_chunks=lead, run_mask=waits, run_value=1, out=out)
     main.wait_stream(side)
     dq, dk, dv, db, dg = ops.bwd_main(q, k, v, cache[2], A, g_cum, beta, do, out["du"], cache[1],
                                       out["dh"], scale, tables=seg, operand_tiles=True)
-    dq, dk, dv, db, dg = chunk_mod.finish_backward(dq, dk, dv, db, dg, Hq, beta_dtype, in_dtype,
-                                                   None)
-    dh0 = out["dh0"][0:1].clone()
-    dist.broadcast(dh0, src=dist.get_global_rank(group, 0) if group else 0, group=group)
-    return dq, dk, dv, db, dg, dh0
+    dq, dk, dv, db, dg = chunk_mod.finish_backward(dq, dk, dv, db, dg, k.shape[2], beta.dtype,
+                                                   q.dtype, None)
+    return dq, dk, dv, db, dg, chained[0:1]

@@ -374,14 +374,24 @@ def merge_states(local, M, use_m, raw, seg_begin, reverse: bool = False, any_fal
     (or, reversed, end gradients) fp32 ``[n_seg, Hv, D, D]``
     (reference: ``blackwell/cp_fwd.py:483-610``).  With ``any_fallback`` (from ``segment_scan``)
     sequences without a chain only get their edge entry written; the other entries of the result
-    are then undefined (their segments lead in by themselves)."""
+    are then undefined (their segments lead in by themselves).  ``local``, ``M`` and ``use_m``
+    may be views into the records of one buffer (the output of an all-gather): their entries must
+    be contiguous per segment and share one stride between segments."""
     _require_cuda(local, M, seg_begin)
     n_seg, Hv, D, _ = local.shape
     n_raw = seg_begin.numel() - 1
     assert seg_begin.dtype == torch.int32
-    out = torch.empty_like(local)
+    seg_stride = 0
+    if not local.is_contiguous():
+        seg_stride = local.stride(0)
+        assert local[0].is_contiguous() and M[0].is_contiguous() and M.stride(0) == seg_stride
+        assert use_m is None or (use_m.stride(0) == seg_stride and use_m.stride(1) == 1
+                                 and use_m.element_size() == 4)
+    else:
+        assert M.is_contiguous() and (use_m is None or use_m.is_contiguous())
+    out = torch.empty(n_seg, Hv, D, D, dtype=local.dtype, device=local.device)
     st = _lib.load().fqla_merge_states(
         _ptr(local), _ptr(M), _ptr(use_m), _ptr(raw), _ptr(seg_begin), _ptr(any_fallback),
-        _ptr(out), n_raw, Hv, D, int(reverse), _stream(local))
+        _ptr(out), n_raw, Hv, D, int(reverse), seg_stride, _stream(local))
     _lib.check(st, "merge_states")
     return out

@@ -142,10 +142,13 @@ int fqla_warmup_scan(const float* g_cum, int T, int Hv, const void* seg_cu_seqle
  * All states fp32 [*, Hv, D, D]; use_m int32 [n_seg, Hv] or NULL (always apply M).
  * any_fallback (int32 [n_raw, Hv] or NULL, from fqla_segment_scan): where 0, only the edge
  * segment's entry of out is written (raw[r] or 0) and the chain is skipped.
+ * seg_stride: 0 for packed local, M and use_m; otherwise the distance, in 4-byte words, between
+ * the entries of consecutive segments in each of the three (they then point into the records of
+ * one gathered buffer: no copy into packed tensors is needed).  raw and out are always packed.
  * Replaces correct_initial_states / correct_terminal_states, blackwell/cp_fwd.py:483-610. */
 int fqla_merge_states(const float* local, const float* M, const int* use_m, const float* raw,
                       const int* seg_begin, const int* any_fallback, float* out, int n_raw, int Hv,
-                      int D, int reverse, void* stream);
+                      int D, int reverse, long long seg_stride, void* stream);
 
 /* The scan of fqla_warmup_scan for a whole split plan in one launch, plus the decision how each
  * segment gets its start state.  seg_begin [n_raw+1] (int32): first segment of every raw

@@ -176,6 +176,18 @@ def test_merge_states_against_host_chain():
                 assert orc.rel_err(out[i], cur) < 1e-5, (reverse, r, i)
                 m = M[i].transpose(-1, -2) if reverse else M[i]
                 cur = local[i] + use[i].view(Hv, 1, 1) * (m @ cur)
+        # the same inputs as views into the records of one buffer (what an all-gather leaves),
+        # flags stored as the numbers 0.0 / 1.0 and read as bits: the same result, bit for bit
+        n = Hv * D * D
+        rows = torch.full((n_seg, 3 * n + Hv), float("nan"), device=DEV)
+        rows[:, :n] = local.to(DEV).reshape(n_seg, n)
+        rows[:, n:2 * n] = M.to(DEV).reshape(n_seg, n)
+        rows[:, 3 * n:] = use.to(DEV).float()
+        strided = ops.merge_states(rows[:, :n].unflatten(1, (Hv, D, D)),
+                                   rows[:, n:2 * n].unflatten(1, (Hv, D, D)),
+                                   rows[:, 3 * n:].view(torch.int32), raw.to(DEV),
+                                   seg_begin.to(DEV), reverse=reverse).cpu()
+        assert torch.equal(strided, out)
 
 
 @pytest.mark.parametrize("cu", [None, [0, 130, 130, 777, 1000]], ids=["fixed", "varlen"])

@@ -51,7 +51,7 @@ def test_invalid_arguments_are_rejected_before_any_launch(lib):
     # null pointers / bad head grouping: negative status, no CUDA call needed
     assert lib.fqla_chunk_local_cumsum(None, None, 1, 64, 1, None, 0, 1, None, 1, 0, None) == -1
     assert lib.fqla_group_reduce(None, None, 1, 1, 1, 128, None) == -1
-    assert lib.fqla_merge_states(None, None, None, None, None, None, None, 1, 1, 128, 0, None) == -1
+    assert lib.fqla_merge_states(None, None, None, None, None, None, None, 1, 1, 128, 0, 0, None) == -1
     assert lib.fqla_segment_scan(None, 64, 1, None, 0, None, 1, -10.0, 0, None, None, None, None,
                                  None, None) == -1
 
