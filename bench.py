@@ -406,6 +406,10 @@ def run_ours(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        from flashqla_b200 import distributed as fd
+
+        if args.reserve_sms is not None:
+            fd.RESERVE_SMS = args.reserve_sms
         dist.init_process_group("nccl", device_id=dev)
     timer = Timer(dev, world)
     w = WORKLOADS[args.workload]
@@ -446,7 +450,7 @@ def run_ours(args):
                 step()
                 torch.cuda.synchronize()
         ms_per_step, mode, launches = time_step(timer, step, x, args.steps, args.warmup,
-                                                use_graph=not args.eager and sharding != "T")
+                                                use_graph=not args.eager)
         if not args.kernel_only:
             t_up = time.time() + 0.3  # a few more samples under load after the timed steps
             while time.time() < t_up:
@@ -774,6 +778,9 @@ def main():
     ap.add_argument("--eager", action="store_true", help="time eager launches, no CUDA graph")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the fwd+bwd and long-sequence blocks of the default line")
+    ap.add_argument("--reserve-sms", type=int, default=None,
+                    help="N > 1: SMs the T-sharded recurrence leaves to the exchange "
+                         "(default: the library's RESERVE_SMS)")
     ap.add_argument("--no-tilelang", action="store_true",
                     help="skip timing the reference's TileLang kernels")
     ap.add_argument("--cpu-seconds", type=float, default=10.0,

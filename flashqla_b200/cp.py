@@ -173,16 +173,18 @@ def _plan_from_bounds(seg_bounds, seg_begin, device, idx_dtype, T_rows) -> Segme
 _shard_plan_cache: dict = {}
 
 
-def shard_plan(T: int, Hv: int, device, short: str) -> SegmentPlan | None:
+def shard_plan(T: int, Hv: int, device, short: str, reserve_sms: int = 0) -> SegmentPlan | None:
     """Segment plan of ONE sequence of ``T`` tokens (a chunk multiple) whose edge segment has to
     wait for a state from elsewhere (another GPU): as many segments as fit one CTA per SM, the
     waiting one (``short`` = "first" for the forward direction, "last" for the reverse one) about
-    half as long as the others, so that it can start late and still finish with them.  ``None``
-    when fewer than three segments fit."""
-    key = (T, Hv, str(device), short)
+    half as long as the others, so that it can start late and still finish with them.
+    ``reserve_sms`` SMs are left without a CTA: the kernels of the exchange (the collective's
+    own, the summary pass, the chains) run there while the recurrence occupies the rest.
+    ``None`` when fewer than three segments fit."""
+    key = (T, Hv, str(device), short, reserve_sms)
     if key not in _shard_plan_cache:
         chunks = T // CHUNK_SIZE
-        n = min(sm_count(device) // Hv, chunks // MIN_SEGMENT_CHUNKS)
+        n = min((sm_count(device) - reserve_sms) // Hv, chunks // MIN_SEGMENT_CHUNKS)
         plan = None
         if n >= 3:
             short_len = max(MIN_SEGMENT_CHUNKS, int(chunks / (n - 0.5) / 2))

@@ -3,7 +3,7 @@
 
 #include "fqla_internal.h"
 
-extern "C" int fqla_version(void) { return 2; }
+extern "C" int fqla_version(void) { return 3; }
 
 extern "C" const char* fqla_status_string(int status) {
   switch (status) {

@@ -31,7 +31,7 @@ def test_library_exports_every_declared_symbol(lib):
 
     assert set(SIGNATURES) | {"fqla_version", "fqla_status_string",
                               "fqla_fwd_noalloc_max_pairs"} == declared
-    assert lib.fqla_version() >= 2
+    assert lib.fqla_version() >= 3
     assert lib.fqla_status_string(0) == b"ok"
     assert b"invalid" in lib.fqla_status_string(-1)
 
