@@ -173,6 +173,20 @@ def _plan_from_bounds(seg_bounds, seg_begin, device, idx_dtype, T_rows) -> Segme
 _shard_plan_cache: dict = {}
 
 
+def shard_segment_chunks(chunks: int, n_sm: int, Hv: int, short: str,
+                         min_chunks: int = MIN_SEGMENT_CHUNKS) -> list[int] | None:
+    """Chunks per segment of a shard of ``chunks`` chunks for ``shard_plan``: ``n`` segments with
+    ``n * Hv <= n_sm``, the waiting one (first or last) about half as long as the others and no
+    segment shorter than ``min_chunks``; ``None`` when fewer than three fit."""
+    n = min(n_sm // Hv, chunks // min_chunks)
+    if n < 3:
+        return None
+    short_len = max(min_chunks, int(chunks / (n - 0.5) / 2))
+    base, extra = divmod(chunks - short_len, n - 1)
+    lens = [base + (1 if i < extra else 0) for i in range(n - 1)]
+    return [short_len] + lens if short == "first" else lens + [short_len]
+
+
 def shard_plan(T: int, Hv: int, device, short: str, reserve_sms: int = 0) -> SegmentPlan | None:
     """Segment plan of ONE sequence of ``T`` tokens (a chunk multiple) whose edge segment has to
     wait for a state from elsewhere (another GPU): as many segments as fit one CTA per SM, the
@@ -183,14 +197,10 @@ def shard_plan(T: int, Hv: int, device, short: str, reserve_sms: int = 0) -> Seg
     ``None`` when fewer than three segments fit."""
     key = (T, Hv, str(device), short, reserve_sms)
     if key not in _shard_plan_cache:
-        chunks = T // CHUNK_SIZE
-        n = min((sm_count(device) - reserve_sms) // Hv, chunks // MIN_SEGMENT_CHUNKS)
+        lens = shard_segment_chunks(T // CHUNK_SIZE, sm_count(device) - reserve_sms, Hv, short)
         plan = None
-        if n >= 3:
-            short_len = max(MIN_SEGMENT_CHUNKS, int(chunks / (n - 0.5) / 2))
-            base, extra = divmod(chunks - short_len, n - 1)
-            lens = [base + (1 if i < extra else 0) for i in range(n - 1)]
-            lens = [short_len] + lens if short == "first" else lens + [short_len]
+        if lens is not None:
+            n = len(lens)
             bounds = [0]
             for c in lens:
                 bounds.append(bounds[-1] + c * CHUNK_SIZE)

@@ -87,7 +87,20 @@ def _worker_tshard(rank, world, port, out):
     for r in range(world - 1, rank, -1):
         cur = locs[r] + Ms[r].transpose(-1, -2) @ cur
     err_b = float((end - cur).norm() / cur.norm())
-    out[rank] = (err_state, err_o, err_ht, err_b)
+    # the spare step of the chain: the final state of the sequence (forward) and the gradient of
+    # its initial state (reverse) on EVERY rank, without a second collective
+    rec = fd._record_from(local, M, use_m, x["h0"] if rank == 0 else None, rank == 0)
+    chained = fd._exchange(rec, H, D, 0, False, None, cpu_merge)
+    assert chained.shape[0] == world + 1
+    err_final = float((chained[world] - ht_full[0]).norm() / ht_full.norm())
+    rec_b = fd._record_from(loc_b, M, use_m, dht if rank == world - 1 else None,
+                            rank == world - 1)
+    chained_b = fd._exchange(rec_b, H, D, world - 1, True, None, cpu_merge)
+    first = dht
+    for r in range(world - 1, -1, -1):
+        first = locs[r] + Ms[r].transpose(-1, -2) @ first
+    err_first = float((chained_b[0] - first[0]).norm() / first.norm())
+    out[rank] = (err_state, err_o, err_ht, err_b, err_final, err_first)
     dist.destroy_process_group()
 
 

@@ -100,6 +100,23 @@ def test_segment_planner_properties():
         assert set(bounds) <= set(seg)
 
 
+def test_shard_segments_for_the_overlapped_exchange():
+    from flashqla_b200.cp import shard_segment_chunks
+
+    # config 4 on 8 / 4 / 2 GPUs (Hv = 8), 16 SMs left to the exchange
+    for chunks in (512, 1024, 2048):
+        for short in ("first", "last"):
+            lens = shard_segment_chunks(chunks, 148 - 16, 8, short)
+            assert sum(lens) == chunks and len(lens) == 16 and min(lens) >= 8
+            edge, rest = (lens[0], lens[1:]) if short == "first" else (lens[-1], lens[:-1])
+            assert max(rest) - min(rest) <= 1 and 0.4 * max(rest) <= edge <= 0.6 * max(rest)
+    # too short to overlap anything, or too many heads for three segments
+    assert shard_segment_chunks(16, 148, 4, "first") is None
+    assert shard_segment_chunks(512, 148, 64, "first") is None
+    # no segment below the minimum even when the half would be
+    assert min(shard_segment_chunks(40, 148, 4, "first")) >= 8
+
+
 def test_tensor_cache_identity_and_eviction():
     from flashqla_b200.utils import tensor_cache
 
