@@ -24,6 +24,8 @@ SIGNATURES = {
     "fqla_group_reduce": [P, P, LL, I, I, I, P],
     "fqla_warmup_scan": [P, I, I, P, I, I, F, I, P, P, P, P],
     "fqla_merge_states": [P, P, P, P, P, P, P, I, I, I, I, LL, P],
+    "fqla_l2norm_fwd": [P, P, P, LL, I, I, F, P],
+    "fqla_l2norm_bwd": [P, P, P, P, LL, I, I, I, P],
     "fqla_segment_scan": [P, I, I, P, I, P, I, F, I, P, P, P, P, P, P],
     "fqla_device_status": [P, I],
     "fqla_selftest_wait_timeout": [I, P],

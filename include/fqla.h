@@ -150,6 +150,16 @@ int fqla_merge_states(const float* local, const float* M, const int* use_m, cons
                       const int* seg_begin, const int* any_fallback, float* out, int n_raw, int Hv,
                       int D, int reverse, long long seg_stride, void* stream);
 
+/* Row-wise L2 normalisation (the optional pre-op of q and k): y = x * rsqrt(sum x^2 + eps) in
+ * the dtype of x, rstd [rows] fp32; and its gradient dx = (dy - <dy, y> y) * rstd, fp32.
+ * Rows are contiguous, D even and <= 512.  dtype codes: 0 bf16, 1 fp16, 2 fp32.
+ * Replaces l2norm_fwd / l2norm_bwd, flash_qla/utils/math.py:22-67 (torch.compile'd expressions
+ * in the reference). */
+int fqla_l2norm_fwd(const void* x, void* y, float* rstd, long long rows, int D, int dtype,
+                    float eps, void* stream);
+int fqla_l2norm_bwd(const void* y, const float* rstd, const void* dy, float* dx, long long rows,
+                    int D, int y_dtype, int dy_dtype, void* stream);
+
 /* The scan of fqla_warmup_scan for a whole split plan in one launch, plus the decision how each
  * segment gets its start state.  seg_begin [n_raw+1] (int32): first segment of every raw
  * sequence.  Outputs, all int32: warm, fallback [n_seg,Hv] as for fqla_warmup_scan (the segment

@@ -419,6 +419,35 @@ def test_lead_out_over_a_partial_last_chunk_is_exact(tiles):
         assert torch.equal(part["du"][:, :T], full["du"][:, :T])
 
 
+@pytest.mark.parametrize("dtype,D", [(torch.bfloat16, 128), (torch.float16, 96),
+                                     (torch.float32, 64), (torch.bfloat16, 322)])
+def test_l2norm_kernels_against_torch(dtype, D):
+    """The one-pass L2-normalisation kernels against the reference's expressions
+    (``flash_qla/utils/math.py:9-51``) evaluated with torch ops in fp32."""
+    from flashqla_b200.utils import l2norm_bwd, l2norm_fwd
+
+    gen = torch.Generator(device=DEV).manual_seed(5)
+    x = torch.randn(3, 37, 5, D, device=DEV, generator=gen).to(dtype)
+    dy = torch.randn(3, 37, 5, D, device=DEV, generator=gen).to(dtype)
+    y, rstd = l2norm_fwd(x)
+    assert y.dtype == dtype and y.shape == x.shape
+    assert rstd.dtype == torch.float32 and rstd.shape == x.shape[:-1]
+    xf = x.float()
+    rstd_ref = torch.rsqrt((xf * xf).sum(-1, keepdim=True) + 1e-6)
+    assert orc.rel_err(rstd, rstd_ref.squeeze(-1)) < 1e-6
+    # the product is rounded once to the output dtype, as in the reference
+    tol = {torch.float32: 1e-6, torch.float16: 1e-3, torch.bfloat16: 6e-3}[dtype]
+    assert orc.rel_err(y.float(), xf * rstd_ref) < tol
+    dx = l2norm_bwd(y, rstd, dy)
+    assert dx.dtype == torch.float32 and dx.shape == x.shape
+    yf, dyf = y.float(), dy.float()
+    dx_ref = (dyf - (dyf * yf).sum(-1, keepdim=True) * yf) * rstd.unsqueeze(-1)
+    assert orc.rel_err(dx, dx_ref) < 1e-5
+    # mixed dtypes: y in the input dtype, the incoming gradient in fp32
+    dx32 = l2norm_bwd(y, rstd, dyf)
+    assert orc.rel_err(dx32, dx_ref) < 1e-5
+
+
 def test_two_launches_with_complementary_run_masks_equal_one_launch():
     """``run_mask`` / ``run_value``: a launch walks only the (sequence, head) pairs selected; two
     launches with the two values fill one set of outputs with the bits of a single launch."""
