@@ -74,7 +74,10 @@ int fqla_kkt_solve(const void* k, const void* beta, int beta_is_f32, const float
  * lead-in of a segment of a longer sequence.  Where lead_chunks[n,hv] > 0 the walk starts that
  * many chunks BEFORE the segment (those rows are the tail of the segment before it) from a zero
  * state, state-only, and only then enters the segment: the start state needs no separate pass.
- * h0 is ignored for such a (segment, head); outputs cover the segment's own rows only.
+ * h0 is ignored for such a (segment, head); outputs cover the segment's own rows only.  The
+ * segment must start a whole number of chunks after the start of the sequence it was cut from
+ * (A and g_cum are chunk-local quantities of that sequence) and at least lead_chunks[n,hv]
+ * chunks after it.
  * seq_order [N] (int32, optional; a permutation of 0..N-1): the CTAs of block index i / Hv walk
  * sequence seq_order[i].  Blocks start in index order, so listing the longest sequences first
  * shortens the tail of a ragged batch; the results do not depend on it.
@@ -98,8 +101,9 @@ int fqla_fwd_seq(const void* q, const void* k, const void* v, const void* A, con
  * (optional, [N, Hv] int32, K = V = 128, not with warm_chunks): the mirror image of
  * fqla_fwd_seq's lead_chunks; sequence n is a segment of a longer sequence, whose following rows
  * belong to segment n + 1, and starts lead_chunks[n,hv] chunks after its end from a zero
- * gradient (dht is ignored for it) instead of being handed one.  seq_order, run_mask,
- * run_value: as for fqla_fwd_seq.
+ * gradient (dht is ignored for it) instead of being handed one; such a segment must end on a
+ * chunk boundary, and segment n + 1 must hold at least lead_chunks[n,hv] chunks (its last one
+ * may be partial).  seq_order, run_mask, run_value: as for fqla_fwd_seq.
  * Replaces fused_gdr_dh_ws (blackwell/cp_bwd.py:592-701) and the dS chain of fused_gdr_bwd
  * (blackwell/fused_bwd.py:336-474). */
 int fqla_bwd_dh(const void* q, const void* k, const void* A, const float* g_cum, const void* beta,
